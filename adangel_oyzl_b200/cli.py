@@ -1,0 +1,61 @@
+"""Command-line entry point: ``python -m adangel_oyzl_b200 {doctor,verify-layout,show-config}``.
+
+Mirrors the reference CLI (``python/adangel/cli.py:12-18,46-53,56-91``) for the commands that belong
+to the native hot path.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+
+def _doctor(args) -> None:
+    from .ops.extension import native_status, require_native
+
+    status = native_status()
+    print(json.dumps({"available": status.available, "reason": status.reason,
+                      "capabilities": status.capabilities}, indent=2))
+    if args.require_native:
+        require_native()
+
+
+def _verify_layout(args) -> None:
+    from .ops.extension import require_sm100_extension
+
+    native = require_sm100_extension()
+    result = dict(native.verify_layout())
+    print(json.dumps(result, indent=2))
+    if not result.get("passed", False):
+        raise RuntimeError("SM100 microscale layout verification failed")
+
+
+def _show_config(args) -> None:
+    import yaml
+
+    config = yaml.safe_load(Path(args.config).read_text(encoding="utf-8"))
+    print(yaml.safe_dump(config, sort_keys=False))
+
+
+def build_parser() -> argparse.ArgumentParser:
+    parser = argparse.ArgumentParser(prog="adangel_oyzl_b200")
+    commands = parser.add_subparsers(dest="command", required=True)
+
+    doctor = commands.add_parser("doctor", help="inspect CUDA/GPU/native backend readiness")
+    doctor.add_argument("--require-native", action="store_true")
+    doctor.set_defaults(func=_doctor)
+
+    verify = commands.add_parser("verify-layout", help="run the block-scaled MMA scale-layout known-answer test")
+    verify.add_argument("--require-native", action="store_true")
+    verify.set_defaults(func=_verify_layout)
+
+    show = commands.add_parser("show-config", help="parse and print a YAML config")
+    show.add_argument("--config", required=True)
+    show.set_defaults(func=_show_config)
+    return parser
+
+
+def main(argv=None) -> None:
+    args = build_parser().parse_args(argv)
+    args.func(args)

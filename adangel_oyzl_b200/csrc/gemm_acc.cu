@@ -1,0 +1,319 @@
+// Persistent, warp-specialised tcgen05 GEMMs that accumulate over the whole K extent in tensor
+// memory: the O0 FP16 GEMM (kind::f16) and the O2 block-scaled MXFP4 GEMM (kind::mxf4.block_scale).
+// They replace the reference's cuBLASLt plan (csrc/sm120/o0_gemm.cu:86-298) and its CUTLASS
+// block-scaled GEMM (csrc/sm120/o2_cutlass.cu:35-93, :394-472).
+//
+//   Y[M,N] (f32) = A[M,K] . W[N,K]^T        both operands K-major, W is used as stored
+//
+// One CTA per SM walks output tiles of 128 x BLOCK_N.  Roles:
+//   warp 0      TMA producer: A/W tiles (128-byte-wide K slabs, 128-byte swizzle) and, for O2, the
+//               scale-factor atoms, into a multi-stage shared-memory ring guarded by mbarriers
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (and, for O2, the shared ->
+//               tensor-memory scale-factor copies) and commits completion to the mbarriers
+//   warps 2-5   epilogue: tcgen05.ld the FP32 accumulator (each warp owns one 32-lane quarter),
+//               stage 32x32 blocks in swizzled shared memory and write them with TMA stores
+// All waits are bounded (see common.cuh); on a timeout the kernel records an error and returns.
+#include "common.cuh"
+#include "launch.h"
+
+namespace adg {
+
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kAccThreads = 192;
+constexpr int kEpiWarps = 4;
+constexpr int kGroupM = 8;  // tile rasterisation: sweep 8 row-blocks before moving to the next column-block
+
+enum : uint32_t {  // wait tags reported on timeout
+  kTagEmpty = 0x100,
+  kTagFull = 0x200,
+  kTagTmemEmpty = 0x300,
+  kTagTmemFull = 0x400,
+};
+
+template <int KIND, int BLOCK_N>
+struct AccCfg {
+  static constexpr bool kScaled = KIND == 2;
+  static constexpr int kStages = BLOCK_N == 256 ? 4 : 5;
+  static constexpr int kElemsPerStage = kScaled ? 256 : 64;  // K elements covered by 128 bytes
+  static constexpr int kTileA = kBlockM * 128;
+  static constexpr int kTileB = BLOCK_N * 128;
+  static constexpr int kSfa = kScaled ? 1024 : 0;                    // two 512-byte atoms (8 K32 blocks)
+  static constexpr int kSfb = kScaled ? (BLOCK_N / 128) * 1024 : 0;  // per 128 rows: two atoms
+  static constexpr int kStageBytes = kTileA + kTileB + kSfa + kSfb;
+  static constexpr int kAccStages = (kScaled && BLOCK_N == 256) ? 1 : 2;
+  static constexpr int kStagingBufs = (kScaled && BLOCK_N == 256) ? 1 : 2;
+  static constexpr int kStagingBytes = kEpiWarps * kStagingBufs * 4096;
+  static constexpr int kSfColsPerStage = kScaled ? 8 + 2 * (BLOCK_N / 32) : 0;
+  static constexpr int kSfColBase = kAccStages * BLOCK_N;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
+  static_assert(kSfColBase + kStages * kSfColsPerStage <= kTmemCols, "tensor memory over-subscribed");
+  static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
+};
+
+struct TileCoord {
+  int m_blk, n_blk;
+};
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) {
+  const int per_group = kGroupM * num_n;
+  const int group = tile / per_group;
+  const int first_m = group * kGroupM;
+  const int gsize = min(num_m - first_m, kGroupM);
+  const int in_group = tile - group * per_group;
+  TileCoord t;
+  t.m_blk = first_m + in_group % gsize;
+  t.n_blk = in_group / gsize;
+  return t;
+}
+
+template <int KIND, int BLOCK_N>
+__global__ void __launch_bounds__(kAccThreads, 1)
+gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                const __grid_constant__ CUtensorMap tm_y, const uint8_t* __restrict__ sfa,
+                const uint8_t* __restrict__ sfb, float* __restrict__ y, int M, int N, int K, int ldy,
+                int use_tma_store, uint32_t* status) {
+  using Cfg = AccCfg<KIND, BLOCK_N>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* staging = smem + Cfg::kStages * Cfg::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + Cfg::kStagingBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + Cfg::kStages;
+  uint64_t* tmem_full_bar = bars + 2 * Cfg::kStages;
+  uint64_t* tmem_empty_bar = tmem_full_bar + Cfg::kAccStages;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + Cfg::kAccStages);
+  volatile uint32_t* abort_flag = tmem_base_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const WaitEnv env{status, abort_flag};
+
+  const int num_m = (M + kBlockM - 1) / kBlockM;
+  const int num_n = (N + BLOCK_N - 1) / BLOCK_N;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (K + Cfg::kElemsPerStage - 1) / Cfg::kElemsPerStage;
+  const int katoms = static_cast<int>(((K / 32 + 7) / 8) * 2);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < Cfg::kAccStages; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], kEpiWarps);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+    tma_prefetch_desc(&tm_y);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, num_m, num_n);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage);
+          if (!ok) break;
+          uint8_t* st = smem + stage * Cfg::kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          const int x = kb * (KIND == 0 ? 64 : 128);  // tensor-map elements: halves or bytes
+          tma_load_2d(st, &tm_a, &full_bar[stage], x, tc.m_blk * kBlockM);
+          tma_load_2d(st + Cfg::kTileA, &tm_b, &full_bar[stage], x, tc.n_blk * BLOCK_N);
+          if constexpr (Cfg::kScaled) {
+            uint8_t* sfa_s = st + Cfg::kTileA + Cfg::kTileB;
+            uint8_t* sfb_s = sfa_s + Cfg::kSfa;
+            bulk_load(sfa_s, sfa + (static_cast<long>(tc.m_blk) * katoms + kb * 2) * 512, 1024, &full_bar[stage]);
+#pragma unroll
+            for (int rb = 0; rb < BLOCK_N / 128; ++rb) {
+              const long row_blk = static_cast<long>(tc.n_blk) * (BLOCK_N / 128) + rb;
+              bulk_load(sfb_s + rb * 1024, sfb + (row_blk * katoms + kb * 2) * 512, 1024, &full_bar[stage]);
+            }
+          }
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -----------------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+        const int acc = local_tile % Cfg::kAccStages;
+        const uint32_t acc_phase = static_cast<uint32_t>(local_tile / Cfg::kAccStages) & 1u;
+        ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, env, kTagTmemEmpty | acc);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | stage);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint64_t adesc = make_desc_sw128(st);
+          const uint64_t bdesc = make_desc_sw128(st + Cfg::kTileA);
+          if constexpr (Cfg::kScaled) {
+            const uint32_t sfa_s = st + Cfg::kTileA + Cfg::kTileB;
+            const uint32_t sfb_s = sfa_s + Cfg::kSfa;
+            const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
+            const uint32_t sfb_t = sfa_t + 8;
+#pragma unroll
+            for (int ka = 0; ka < 2; ++ka) {
+              tmem_cp_32x128b_warpx4(sfa_t + ka * 4, make_desc_sf(sfa_s + ka * 512));
+#pragma unroll
+              for (int rb = 0; rb < BLOCK_N / 128; ++rb) {
+                tmem_cp_32x128b_warpx4(sfb_t + ka * (BLOCK_N / 32) + rb * 4, make_desc_sf(sfb_s + rb * 1024 + ka * 512));
+              }
+            }
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              const uint32_t sf_id = (ks & 1) * 2;
+              const uint32_t idesc = make_idesc_mxf4(kBlockM, BLOCK_N, sf_id, sf_id);
+              umma_mxf4(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u,
+                        sfa_t + (ks >> 1) * 4, sfb_t + (ks >> 1) * (BLOCK_N / 32));
+            }
+          } else {
+            constexpr uint32_t idesc = make_idesc(1, kFmtF16, kFmtF16, kBlockM, BLOCK_N);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              umma_f16(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
+            }
+          }
+          umma_commit(&empty_bar[stage]);  // the stage may be refilled once these MMAs have read it
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(&tmem_full_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------- epilogue ---------------------------------------------------
+    const int q = warp & 3;  // the 32-lane quarter of tensor memory this warp can read
+    const int epi = warp - 2;
+    uint8_t* my_staging = staging + epi * Cfg::kStagingBufs * 4096;
+    int local_tile = 0;
+    uint32_t chunk_counter = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+      const TileCoord tc = tile_coord(tile, num_m, num_n);
+      const int acc = local_tile % Cfg::kAccStages;
+      const uint32_t acc_phase = static_cast<uint32_t>(local_tile / Cfg::kAccStages) & 1u;
+      ok = mbar_wait(&tmem_full_bar[acc], acc_phase, env, kTagTmemFull | acc);
+      if (!ok) break;
+      tc_fence_after();
+      const int row0 = tc.m_blk * kBlockM + q * 32;
+      const int col0 = tc.n_blk * BLOCK_N;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BLOCK_N);
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + c * 32, r);
+        tmem_wait_ld();
+        if (c == BLOCK_N / 32 - 1) {
+          // every accumulator column of this warp's quarter is now in registers
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+        }
+        const int col = col0 + c * 32;
+        if (use_tma_store) {
+          uint8_t* buf = my_staging + (chunk_counter % Cfg::kStagingBufs) * 4096;
+          ++chunk_counter;
+          if (lane == 0) bulk_wait_group_read<Cfg::kStagingBufs - 1>();
+          __syncwarp();
+          const uint32_t row_addr = smem_u32(buf) + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t addr = row_addr + ((j ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r[4 * j]), "r"(r[4 * j + 1]),
+                         "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (row0 < M && col < N) tma_store_2d(&tm_y, buf, col, row0);
+            bulk_commit_group();
+          }
+        } else {
+          const int row = row0 + lane;
+          if (row < M) {
+            float* dst = y + static_cast<long>(row) * ldy + col;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col + j < N) dst[j] = __uint_as_float(r[j]);
+            }
+          }
+        }
+      }
+    }
+    if (lane == 0) bulk_wait_group<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <int KIND, int BLOCK_N>
+int set_attr() {
+  using Cfg = AccCfg<KIND, BLOCK_N>;
+  return check_cuda(cudaFuncSetAttribute(gemm_acc_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm_acc_kernel)");
+}
+
+template <int KIND, int BLOCK_N>
+int launch(const GemmPlan& p, cudaStream_t stream) {
+  using Cfg = AccCfg<KIND, BLOCK_N>;
+  gemm_acc_kernel<KIND, BLOCK_N><<<p.grid, kAccThreads, Cfg::kSmemBytes, stream>>>(
+      p.tm_a, p.tm_b, p.tm_y, static_cast<const uint8_t*>(p.sfa), static_cast<const uint8_t*>(p.sfb), p.y, p.M, p.N,
+      p.K, p.ldy, p.use_tma_store, p.status);
+  return check_cuda(cudaGetLastError(), "gemm_acc_kernel launch");
+}
+
+}  // namespace
+
+int init_gemm_acc_attributes() {
+  if (int rc = set_attr<0, 256>()) return rc;
+  if (int rc = set_attr<0, 128>()) return rc;
+  if (int rc = set_attr<2, 256>()) return rc;
+  if (int rc = set_attr<2, 128>()) return rc;
+  return 0;
+}
+
+int run_gemm_acc(const GemmPlan& p, cudaStream_t stream) {
+  if (p.variant == 0) return p.block_n == 256 ? launch<0, 256>(p, stream) : launch<0, 128>(p, stream);
+  if (p.variant == 2) return p.block_n == 256 ? launch<2, 256>(p, stream) : launch<2, 128>(p, stream);
+  return fail("run_gemm_acc: plan is not an O0/O2 plan");
+}
+
+}  // namespace adg

@@ -1,0 +1,86 @@
+// Host-side declarations shared by the translation units of the library: per-device context,
+// tensor-map encoding, kernel launchers and GEMM plans.  Nothing here is part of the C ABI.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+namespace adg {
+
+// ---- errors -----------------------------------------------------------------------------------
+// Library calls return 0 on success; a non-zero return leaves a message for adg_last_error().
+void set_error(const std::string& message);
+int fail(const std::string& message);
+int check_cuda(cudaError_t err, const char* what);
+const char* last_error_cstr();
+
+// ---- per-device context -------------------------------------------------------------------------
+struct DeviceCtx {
+  int device = -1;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  uint32_t* status = nullptr;  // kStatusWords device words, zero when healthy
+};
+// Context of the current device (created on first use; allocates the status words once).
+int device_ctx(DeviceCtx** out);
+// Reads the device status words of the current device (synchronises the device's work on
+// `stream` first), clears them, and returns non-zero with a message if a kernel reported an error.
+int check_device_status(cudaStream_t stream);
+
+// ---- scale-factor tiled layout ---------------------------------------------------------------------
+// 512-byte atoms of 128 rows x 4 K32 blocks, ordered row-block major / K-atom minor; rows are
+// padded to a multiple of 256 and K32 blocks to a multiple of 8 (zero bytes).
+inline long tiled_scale_rows(long rows) { return (rows + 255) / 256 * 256; }
+inline long tiled_scale_katoms(long k) { return ((k / 32 + 7) / 8) * 2; }
+inline long tiled_scale_bytes(long rows, long k) { return tiled_scale_rows(rows) * tiled_scale_katoms(k) * 4; }
+
+// ---- conversion launchers (device pointers) ----------------------------------------------------------
+int launch_mxfp4_to_fp16(const void* packed, const void* scales, void* out, long rows, long k, cudaStream_t stream);
+int launch_int8_to_fp16(const void* in, const void* row_scale, void* out, long rows, long k, cudaStream_t stream);
+int launch_mxfp4_to_int8(const void* packed, void* out, long rows, long k, cudaStream_t stream);
+int launch_o2_quantize(const void* a_int8, const void* row_scale, void* codes, void* sf_natural, void* sf_tiled,
+                       long rows, long k, cudaStream_t stream);
+int launch_o2_tile_scales(const void* natural, void* tiled, long rows, long k, cudaStream_t stream);
+
+// ---- tensor maps ---------------------------------------------------------------------------------
+// 2-D row-major tensor [rows, cols] of `elem_bytes`-wide elements with a row pitch of `pitch_bytes`;
+// the box is box_cols x box_rows elements and shared memory uses the 128-byte swizzle.
+int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, const void* base, uint64_t rows,
+                         uint64_t cols, uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols);
+
+// ---- GEMM plans ----------------------------------------------------------------------------------
+// A plan holds the encoded tensor maps and launch geometry of one GEMM on fixed buffers; running it
+// only launches the kernel.
+struct GemmPlan {
+  int variant = -1;  // 0 = O0 (f16), 1 = O1 (i8 + per-K32 rescale), 2 = O2 (mxf4 block-scaled)
+  int M = 0, N = 0, K = 0, ldy = 0;
+  int block_n = 0;
+  int grid = 0;
+  int use_tma_store = 0;
+  CUtensorMap tm_a, tm_b, tm_y;
+  const void* a_scale = nullptr;   // O1: float [M]
+  const void* w_scale = nullptr;   // O1: natural UE8M0 [N, K/32]
+  const void* sfa = nullptr;       // O2: tiled A scales
+  const void* sfb = nullptr;       // O2: tiled W scales
+  float* y = nullptr;
+  int32_t* partial_dump = nullptr;  // O1 debug: INT32 partials [M, N, K/32]
+  uint32_t* status = nullptr;
+};
+
+int plan_o0(GemmPlan* plan, const void* a_fp16, const void* w_fp16, float* y, int M, int N, int K, int ldy);
+int plan_o1(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale, float* y,
+            int32_t* partial_dump, int M, int N, int K, int ldy);
+int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const void* w_mxfp4, const void* sfb_tiled,
+            float* y, int M, int N, int K, int ldy);
+int run_plan(const GemmPlan& plan, cudaStream_t stream);
+
+// Kernel entry points behind run_plan (defined in gemm_acc.cu / gemm_o1.cu).
+int run_gemm_acc(const GemmPlan& plan, cudaStream_t stream);
+int run_gemm_o1(const GemmPlan& plan, cudaStream_t stream);
+int init_gemm_acc_attributes();
+int init_gemm_o1_attributes();
+
+}  // namespace adg

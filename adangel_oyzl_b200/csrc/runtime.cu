@@ -1,0 +1,206 @@
+// Host runtime of the library: error reporting, the per-device context, tensor-map encoding through
+// the driver entry point (no link-time dependency on the driver library) and GEMM plan construction.
+#include <cudaTypedefs.h>
+
+#include <cstdio>
+#include <mutex>
+#include <string>
+
+#include "common.cuh"
+#include "launch.h"
+
+namespace adg {
+
+namespace {
+thread_local std::string g_last_error;
+std::mutex g_ctx_mutex;
+constexpr int kMaxDevices = 64;
+DeviceCtx g_ctx[kMaxDevices];
+bool g_ctx_ready[kMaxDevices] = {};
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+}  // namespace
+
+const char* last_error_cstr() { return g_last_error.c_str(); }
+
+void set_error(const std::string& message) { g_last_error = message; }
+
+int fail(const std::string& message) {
+  g_last_error = message;
+  return 1;
+}
+
+int check_cuda(cudaError_t err, const char* what) {
+  if (err == cudaSuccess) return 0;
+  g_last_error = std::string(what) + ": " + cudaGetErrorString(err);
+  return 1;
+}
+
+int device_ctx(DeviceCtx** out) {
+  int dev = -1;
+  if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+  if (dev < 0 || dev >= kMaxDevices) return fail("device index out of range");
+  std::lock_guard<std::mutex> lock(g_ctx_mutex);
+  if (!g_ctx_ready[dev]) {
+    DeviceCtx ctx;
+    ctx.device = dev;
+    cudaDeviceProp prop;
+    if (int rc = check_cuda(cudaGetDeviceProperties(&prop, dev), "cudaGetDeviceProperties")) return rc;
+    ctx.sm_count = prop.multiProcessorCount;
+    ctx.cc_major = prop.major;
+    ctx.cc_minor = prop.minor;
+    if (prop.major != 10) {
+      return fail("this library contains sm_100a kernels only; device '" + std::string(prop.name) +
+                  "' has compute capability " + std::to_string(prop.major) + "." + std::to_string(prop.minor));
+    }
+    if (int rc = check_cuda(cudaMalloc(&ctx.status, kStatusWords * sizeof(uint32_t)), "cudaMalloc(status)")) return rc;
+    if (int rc = check_cuda(cudaMemset(ctx.status, 0, kStatusWords * sizeof(uint32_t)), "cudaMemset(status)")) return rc;
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      if (int rc = check_cuda(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres),
+                              "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)"))
+        return rc;
+      if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return fail("cuTensorMapEncodeTiled is unavailable");
+      g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    }
+    if (int rc = init_gemm_acc_attributes()) return rc;
+    if (int rc = init_gemm_o1_attributes()) return rc;
+    g_ctx[dev] = ctx;
+    g_ctx_ready[dev] = true;
+  }
+  *out = &g_ctx[dev];
+  return 0;
+}
+
+int check_device_status(cudaStream_t stream) {
+  DeviceCtx* ctx = nullptr;
+  if (int rc = device_ctx(&ctx)) return rc;
+  if (int rc = check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize")) return rc;
+  uint32_t words[kStatusWords] = {};
+  if (int rc = check_cuda(cudaMemcpy(words, ctx->status, sizeof(words), cudaMemcpyDeviceToHost), "cudaMemcpy(status)"))
+    return rc;
+  if (words[0] == kStatusOk) return 0;
+  check_cuda(cudaMemset(ctx->status, 0, sizeof(words)), "cudaMemset(status)");
+  char buf[256];
+  snprintf(buf, sizeof(buf), "kernel wait timeout: code=%u tag=0x%x block=%u detail=%u", words[0], words[1], words[2],
+           words[3]);
+  return fail(buf);
+}
+
+int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, const void* base, uint64_t rows,
+                         uint64_t cols, uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols) {
+  if (g_encode == nullptr) return fail("tensor-map encoder not initialised");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return fail("tensor base address must be 16-byte aligned");
+  if ((pitch_bytes & 15u) != 0) return fail("tensor row pitch must be a multiple of 16 bytes");
+  if (box_cols * static_cast<uint32_t>(elem_bytes) != 128u) return fail("box width must be 128 bytes");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {pitch_bytes};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult res = g_encode(map, dtype, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(res)));
+  return 0;
+}
+
+namespace {
+
+int check_shape(int M, int N, int K, int ldy) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail("M, N, and K must be positive");
+  if (K % 64 != 0) return fail("K must be divisible by 64");
+  if (ldy < N) return fail("ldy must be at least N");
+  return 0;
+}
+
+// The epilogue writes Y through a TMA store when the tensor map's constraints hold, otherwise
+// through predicated scalar stores.
+int plan_output(GemmPlan* plan, float* y) {
+  plan->y = y;
+  const bool aligned = (reinterpret_cast<uintptr_t>(y) & 15u) == 0 && (static_cast<uint64_t>(plan->ldy) * 4u) % 16u == 0;
+  plan->use_tma_store = aligned ? 1 : 0;
+  if (aligned) {
+    return encode_tensor_map_2d(&plan->tm_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, y, plan->M, plan->N,
+                                static_cast<uint64_t>(plan->ldy) * 4u, 32, 32);
+  }
+  // a valid (unused) map keeps the kernel's prefetch harmless
+  plan->tm_y = plan->tm_a;
+  return 0;
+}
+
+int finish_plan(GemmPlan* plan, int block_n) {
+  DeviceCtx* ctx = nullptr;
+  if (int rc = device_ctx(&ctx)) return rc;
+  plan->block_n = block_n;
+  const long tiles = static_cast<long>((plan->M + 127) / 128) * ((plan->N + block_n - 1) / block_n);
+  plan->grid = static_cast<int>(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  plan->status = ctx->status;
+  return 0;
+}
+
+}  // namespace
+
+int plan_o0(GemmPlan* plan, const void* a_fp16, const void* w_fp16, float* y, int M, int N, int K, int ldy) {
+  DeviceCtx* ctx = nullptr;
+  if (int rc = device_ctx(&ctx)) return rc;
+  if (int rc = check_shape(M, N, K, ldy)) return rc;
+  *plan = GemmPlan{};
+  plan->variant = 0;
+  plan->M = M, plan->N = N, plan->K = K, plan->ldy = ldy;
+  const int block_n = N > 128 ? 256 : 128;
+  if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a_fp16, M, K,
+                                    static_cast<uint64_t>(K) * 2, 128, 64))
+    return rc;
+  if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, w_fp16, N, K,
+                                    static_cast<uint64_t>(K) * 2, block_n, 64))
+    return rc;
+  if (int rc = plan_output(plan, y)) return rc;
+  return finish_plan(plan, block_n);
+}
+
+int plan_o1(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale, float* y,
+            int32_t* partial_dump, int M, int N, int K, int ldy) {
+  DeviceCtx* ctx = nullptr;
+  if (int rc = device_ctx(&ctx)) return rc;
+  if (int rc = check_shape(M, N, K, ldy)) return rc;
+  *plan = GemmPlan{};
+  plan->variant = 1;
+  plan->M = M, plan->N = N, plan->K = K, plan->ldy = ldy;
+  plan->a_scale = a_scale;
+  plan->w_scale = w_scale;
+  plan->partial_dump = partial_dump;
+  plan->y = y;
+  if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_int8, M, K, K, 128, 128)) return rc;
+  if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_int8, N, K, K, 128, 128)) return rc;
+  plan->tm_y = plan->tm_a;
+  return finish_plan(plan, 128);
+}
+
+int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const void* w_mxfp4, const void* sfb_tiled,
+            float* y, int M, int N, int K, int ldy) {
+  DeviceCtx* ctx = nullptr;
+  if (int rc = device_ctx(&ctx)) return rc;
+  if (int rc = check_shape(M, N, K, ldy)) return rc;
+  if ((reinterpret_cast<uintptr_t>(sfa_tiled) & 15u) != 0 || (reinterpret_cast<uintptr_t>(sfb_tiled) & 15u) != 0)
+    return fail("tiled scale buffers must be 16-byte aligned");
+  *plan = GemmPlan{};
+  plan->variant = 2;
+  plan->M = M, plan->N = N, plan->K = K, plan->ldy = ldy;
+  plan->sfa = sfa_tiled;
+  plan->sfb = sfb_tiled;
+  const int block_n = N > 128 ? 256 : 128;
+  const uint64_t kbytes = static_cast<uint64_t>(K) / 2;
+  if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_mxfp4, M, kbytes, kbytes, 128, 128))
+    return rc;
+  if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_mxfp4, N, kbytes, kbytes, block_n, 128))
+    return rc;
+  if (int rc = plan_output(plan, y)) return rc;
+  return finish_plan(plan, block_n);
+}
+
+int run_plan(const GemmPlan& plan, cudaStream_t stream) {
+  if (plan.variant == 1) return run_gemm_o1(plan, stream);
+  return run_gemm_acc(plan, stream);
+}
+
+}  // namespace adg

@@ -1,0 +1,191 @@
+"""Tensor-level wrappers of the individual C-ABI kernels (conversions and GEMMs).
+
+Each function validates shapes/dtypes, allocates the output on the inputs' device, enqueues the
+kernel on torch's current stream and returns the output tensor(s) without synchronising.  These are
+the building blocks behind :mod:`adangel_oyzl_b200.ops` and the N-sharded multi-GPU driver.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+from .ops import _sm100
+
+
+def _stream(t):
+    import torch
+
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _lib():
+    return _sm100.library()
+
+
+def _require(cond, message):
+    if not cond:
+        raise RuntimeError(message)
+
+
+def mxfp4_to_fp16(w_mxfp4, w_scale):
+    import torch
+
+    n, kh = w_mxfp4.shape
+    k = kh * 2
+    _require(w_mxfp4.is_cuda and w_mxfp4.dtype == torch.uint8 and w_mxfp4.is_contiguous(), "W_mxfp4 must be contiguous CUDA uint8")
+    _require(w_scale.dtype == torch.uint8 and tuple(w_scale.shape) == (n, k // 32) and w_scale.is_contiguous(), "invalid W_scale")
+    out = torch.empty((n, k), dtype=torch.float16, device=w_mxfp4.device)
+    with torch.cuda.device(w_mxfp4.device):
+        _sm100._check(_lib().adg_mxfp4_to_fp16(w_mxfp4.data_ptr(), w_scale.data_ptr(), out.data_ptr(), n, k, _stream(out)))
+    return out
+
+
+def int8_to_fp16(a_int8, a_scale):
+    import torch
+
+    m, k = a_int8.shape
+    _require(a_int8.is_cuda and a_int8.dtype == torch.int8 and a_int8.is_contiguous(), "A_int8 must be contiguous CUDA int8")
+    _require(a_scale.dtype == torch.float32 and tuple(a_scale.shape) == (m,), "invalid A_scale")
+    out = torch.empty((m, k), dtype=torch.float16, device=a_int8.device)
+    with torch.cuda.device(a_int8.device):
+        _sm100._check(_lib().adg_int8_to_fp16(a_int8.data_ptr(), a_scale.data_ptr(), out.data_ptr(), m, k, _stream(out)))
+    return out
+
+
+def mxfp4_to_int8(w_mxfp4):
+    import torch
+
+    n, kh = w_mxfp4.shape
+    _require(w_mxfp4.is_cuda and w_mxfp4.dtype == torch.uint8 and w_mxfp4.is_contiguous(), "W_mxfp4 must be contiguous CUDA uint8")
+    out = torch.empty((n, kh * 2), dtype=torch.int8, device=w_mxfp4.device)
+    with torch.cuda.device(w_mxfp4.device):
+        _sm100._check(_lib().adg_mxfp4_to_int8(w_mxfp4.data_ptr(), out.data_ptr(), n, kh * 2, _stream(out)))
+    return out
+
+
+def tiled_scale_bytes(rows: int, k: int) -> int:
+    return int(_lib().adg_o2_tiled_scale_bytes(rows, k))
+
+
+def o2_quantize_activation(a_int8, a_scale, want_natural=True):
+    """Returns (codes [M,K/2] u8, natural scales [M,K/32] u8 or None, tiled scales u8)."""
+    import torch
+
+    m, k = a_int8.shape
+    _require(a_int8.is_cuda and a_int8.dtype == torch.int8 and a_int8.is_contiguous(), "A_int8 must be contiguous CUDA int8")
+    _require(a_scale.dtype == torch.float32 and tuple(a_scale.shape) == (m,), "invalid A_scale")
+    dev = a_int8.device
+    codes = torch.empty((m, k // 2), dtype=torch.uint8, device=dev)
+    natural = torch.empty((m, k // 32), dtype=torch.uint8, device=dev) if want_natural else None
+    tiled = torch.zeros((tiled_scale_bytes(m, k),), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _sm100._check(_lib().adg_o2_quantize_activation(
+            a_int8.data_ptr(), a_scale.data_ptr(), codes.data_ptr(),
+            natural.data_ptr() if natural is not None else None, tiled.data_ptr(), m, k, _stream(codes)))
+    return codes, natural, tiled
+
+
+def o2_tile_scales(scales):
+    import torch
+
+    rows, groups = scales.shape
+    _require(scales.is_cuda and scales.dtype == torch.uint8 and scales.is_contiguous(), "scales must be contiguous CUDA uint8")
+    tiled = torch.empty((tiled_scale_bytes(rows, groups * 32),), dtype=torch.uint8, device=scales.device)
+    with torch.cuda.device(scales.device):
+        _sm100._check(_lib().adg_o2_tile_scales(scales.data_ptr(), tiled.data_ptr(), rows, groups * 32, _stream(tiled)))
+    return tiled
+
+
+def _output(out, m, n, device):
+    import torch
+
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=device)
+    _require(out.dtype == torch.float32 and tuple(out.shape) == (m, n) and out.stride(1) == 1, "invalid output tensor")
+    return out, int(out.stride(0))
+
+
+def gemm_o0(a_fp16, w_fp16, out=None):
+    m, k = a_fp16.shape
+    n = w_fp16.shape[0]
+    out, ldy = _output(out, m, n, a_fp16.device)
+    import torch
+
+    with torch.cuda.device(a_fp16.device):
+        _sm100._check(_lib().adg_gemm_o0(a_fp16.data_ptr(), w_fp16.data_ptr(), out.data_ptr(), m, n, k, ldy, _stream(out)))
+    return out
+
+
+def gemm_o1(a_int8, a_scale, w_int8, w_scale, out=None, dump_partials=False):
+    import torch
+
+    m, k = a_int8.shape
+    n = w_int8.shape[0]
+    out, ldy = _output(out, m, n, a_int8.device)
+    partials = torch.empty((m, n, k // 32), dtype=torch.int32, device=a_int8.device) if dump_partials else None
+    with torch.cuda.device(a_int8.device):
+        _sm100._check(_lib().adg_gemm_o1(
+            a_int8.data_ptr(), a_scale.data_ptr(), w_int8.data_ptr(), w_scale.data_ptr(), out.data_ptr(),
+            partials.data_ptr() if partials is not None else None, m, n, k, ldy, _stream(out)))
+    return (out, partials) if dump_partials else out
+
+
+def gemm_o2(a_mxfp4, a_sf_tiled, w_mxfp4, w_sf_tiled, out=None):
+    import torch
+
+    m, kh = a_mxfp4.shape
+    n = w_mxfp4.shape[0]
+    out, ldy = _output(out, m, n, a_mxfp4.device)
+    with torch.cuda.device(a_mxfp4.device):
+        _sm100._check(_lib().adg_gemm_o2(
+            a_mxfp4.data_ptr(), a_sf_tiled.data_ptr(), w_mxfp4.data_ptr(), w_sf_tiled.data_ptr(), out.data_ptr(),
+            m, n, kh * 2, ldy, _stream(out)))
+    return out
+
+
+def check_status(device=None):
+    """Synchronise torch's current stream and raise if a kernel reported a bounded-wait timeout."""
+    import torch
+
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    with torch.cuda.device(dev):
+        _sm100._check(_lib().adg_check_status(torch.cuda.current_stream(dev).cuda_stream))
+
+
+class HostSession:
+    """Weights resident on the device, activations and results in host memory
+    (``adg_session_*`` of the C ABI).  numpy arrays or CPU torch tensors are accepted."""
+
+    def __init__(self, variant: str, max_m: int, w_mxfp4, w_scale):
+        self._handle = ctypes.c_void_p()
+        self.variant = variant
+        self.n, kh = w_mxfp4.shape
+        self.k = kh * 2
+        self.max_m = max_m
+        _sm100._check(_lib().adg_session_create(
+            ctypes.byref(self._handle), _sm100._VARIANTS[variant], max_m, self.n, self.k,
+            _host_ptr(w_mxfp4), _host_ptr(w_scale)))
+
+    def run(self, a_int8, a_scale, y_out):
+        m = a_int8.shape[0]
+        _sm100._check(_lib().adg_session_run(self._handle, _host_ptr(a_int8), _host_ptr(a_scale), m, _host_ptr(y_out)))
+        return y_out
+
+    def close(self):
+        if self._handle:
+            _lib().adg_session_destroy(self._handle)
+            self._handle = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _host_ptr(x):
+    if hasattr(x, "data_ptr"):
+        _require(not x.is_cuda and x.is_contiguous(), "expected a contiguous host tensor")
+        return x.data_ptr()
+    _require(x.flags["C_CONTIGUOUS"], "expected a C-contiguous array")
+    return x.ctypes.data

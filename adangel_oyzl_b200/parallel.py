@@ -1,0 +1,117 @@
+"""N-sharded execution of ``Y = A @ W.T`` over several GPUs of one node.
+
+W's rows (the output columns) are split into contiguous, tile-aligned blocks, one per rank; each
+rank holds only its slice of ``W_mxfp4`` / ``W_scale``, A and ``A_scale`` are replicated (broadcast
+once), and every rank computes ``Y[:, n0:n1] = A @ W[n0:n1].T`` with the same kernels as the
+single-GPU path.  K is not split, so there is no reduction and every output element is computed by
+exactly the same instruction sequence as on one GPU.  A collective is needed only when a caller
+wants the contiguous ``[M, N]`` result on every rank (``gather_columns``).
+
+One process per GPU (``torchrun``); ``torch.distributed`` carries the broadcast and the optional
+gather (NCCL on GPUs, gloo in the CPU tests of the partition/gather logic).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+TILE_ALIGN = 128  # shard boundaries fall on output-tile boundaries
+
+
+def shard_range(n: int, world_size: int, rank: int, align: int = TILE_ALIGN) -> tuple[int, int]:
+    """Rows ``[n0, n1)`` of W owned by ``rank``: blocks of ``align`` rows dealt as evenly as possible,
+    earlier ranks taking the remainder; the last block may be ragged.  Empty for surplus ranks."""
+    if world_size <= 0 or not 0 <= rank < world_size:
+        raise ValueError("invalid rank/world_size")
+    blocks = (n + align - 1) // align
+    base, extra = divmod(blocks, world_size)
+    first = rank * base + min(rank, extra)
+    count = base + (1 if rank < extra else 0)
+    return min(first * align, n), min((first + count) * align, n)
+
+
+def all_ranges(n: int, world_size: int, align: int = TILE_ALIGN) -> list[tuple[int, int]]:
+    return [shard_range(n, world_size, r, align) for r in range(world_size)]
+
+
+def broadcast_activations(a_int8, a_scale, src: int = 0, group=None):
+    """Replicate A and its row scales from ``src`` (in place on the other ranks)."""
+    import torch.distributed as dist
+
+    dist.broadcast(a_int8, src=src, group=group)
+    dist.broadcast(a_scale, src=src, group=group)
+    return a_int8, a_scale
+
+
+def gather_columns(y_local, n: int, group=None, align: int = TILE_ALIGN):
+    """All-gather the ranks' column blocks ``[M, n_r]`` into the contiguous ``[M, N]`` matrix."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    ranges = all_ranges(n, world, align)
+    m = y_local.shape[0]
+    widest = max(n1 - n0 for n0, n1 in ranges)
+    # collectives want equal-sized pieces: ragged blocks travel padded to the widest one
+    mine = y_local
+    if y_local.shape[1] != widest:
+        mine = torch.zeros((m, widest), dtype=y_local.dtype, device=y_local.device)
+        mine[:, : y_local.shape[1]] = y_local
+    pieces = [torch.empty((m, widest), dtype=y_local.dtype, device=y_local.device) for _ in ranges]
+    dist.all_gather(pieces, mine.contiguous(), group=group)
+    return torch.cat([p[:, : n1 - n0] for p, (n0, n1) in zip(pieces, ranges)], dim=1)
+
+
+@dataclass
+class ShardedWeights:
+    """One rank's slice of the weights in the forms the three variants consume."""
+
+    n0: int
+    n1: int
+    w_mxfp4: object
+    w_scale: object
+    w_fp16: object = None    # O0
+    w_int8: object = None    # O1
+    w_sf_tiled: object = None  # O2
+
+    @property
+    def rows(self) -> int:
+        return self.n1 - self.n0
+
+
+def shard_weights(w_mxfp4, w_scale, world_size: int, rank: int, variants=("o0", "o1", "o2"), device=None):
+    """Slice W for ``rank`` (moving it to ``device``) and run the weight conversions once."""
+    from . import kernels
+
+    n = w_mxfp4.shape[0]
+    n0, n1 = shard_range(n, world_size, rank)
+    wm = w_mxfp4[n0:n1].contiguous()
+    ws = w_scale[n0:n1].contiguous()
+    if device is not None:
+        wm, ws = wm.to(device), ws.to(device)
+    shard = ShardedWeights(n0, n1, wm, ws)
+    if shard.rows == 0:
+        return shard
+    if "o0" in variants:
+        shard.w_fp16 = kernels.mxfp4_to_fp16(wm, ws)
+    if "o1" in variants:
+        shard.w_int8 = kernels.mxfp4_to_int8(wm)
+    if "o2" in variants:
+        shard.w_sf_tiled = kernels.o2_tile_scales(ws)
+    return shard
+
+
+def sharded_gemm(variant: str, a_int8, a_scale, shard: ShardedWeights, out=None):
+    """This rank's column block of Y for ``variant`` (activation conversion included)."""
+    from . import kernels
+
+    if shard.rows == 0:
+        return out
+    if variant == "o0":
+        return kernels.gemm_o0(kernels.int8_to_fp16(a_int8, a_scale), shard.w_fp16, out=out)
+    if variant == "o1":
+        return kernels.gemm_o1(a_int8, a_scale, shard.w_int8, shard.w_scale, out=out)
+    if variant == "o2":
+        codes, _, sfa = kernels.o2_quantize_activation(a_int8, a_scale, want_natural=False)
+        return kernels.gemm_o2(codes, sfa, shard.w_mxfp4, shard.w_sf_tiled, out=out)
+    raise ValueError(f"unknown variant: {variant}")

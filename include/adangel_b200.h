@@ -1,0 +1,178 @@
+/*
+ * adangel_b200 — C ABI of the B200 (sm_100a) backend for ADAngel's O0/O1/O2 quantized GEMMs
+ *
+ *     Y[M,N] (fp32) = (A_int8[M,K] * A_scale[M]) @ (W_mxfp4[N,K/2] * 2^(W_scale[N,K/32]-127))^T
+ *
+ * This is the drop-in boundary: plain pointers and sizes, no framework types.  The reference
+ * project exposes the same operations through a pybind11/torch extension module
+ * (csrc/bindings.cpp:84-103, prototypes in include/adangel/kernel_api.h:13-86); each entry point
+ * below names the reference interface it replaces.
+ *
+ * Conventions
+ *   - Every function returns 0 on success and a non-zero code on failure; adg_last_error()
+ *     returns the message of the calling thread's last failure.
+ *   - "device" pointers are CUDA device pointers valid on the current device; work is enqueued on
+ *     the given stream (a cudaStream_t passed as void*, NULL = the default stream) and the call
+ *     returns without synchronising unless stated otherwise.
+ *   - Tensors are dense row-major.  K must be a multiple of 64; M, N, K > 0.
+ *   - E2M1 nibbles: even k in the low nibble.  UE8M0 code c means 2^(c-127); code 255 is forbidden.
+ *   - There is no CPU fallback: on a machine without a B200-class GPU the compute calls fail.
+ */
+#ifndef ADANGEL_B200_H_
+#define ADANGEL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- library ------------------------------------------------------------------------------- */
+
+/* ABI version of this header (major * 100 + minor). */
+int adg_abi_version(void);
+
+/* Message of the calling thread's last failed call ("" if none). */
+const char* adg_last_error(void);
+
+/* Capability bits; replaces capabilities() of the reference module (csrc/bindings.cpp:11-20).
+ * Bit set = the production kernel for that capability is compiled into this library. */
+#define ADG_CAP_COMPILED_SM100A 0x01u
+#define ADG_CAP_O0_FP16_TC 0x02u
+#define ADG_CAP_O1_INT8_TC 0x04u
+#define ADG_CAP_O2_MXF4_BLOCK_SCALE 0x08u
+#define ADG_CAP_O2_TILED 0x10u
+uint32_t adg_capabilities(void);
+
+/* Fills name (NUL-terminated, at most name_len bytes), compute capability and SM count of the
+ * current CUDA device.  Fails if no CUDA device is usable. */
+int adg_device_info(char* name, int name_len, int* cc_major, int* cc_minor, int* sm_count);
+
+/* Waits for the work enqueued on `stream`, then reads and clears the device status words written
+ * by kernels whose bounded waits gave up; fails with a description if one did. */
+int adg_check_status(void* stream);
+
+/* ---- conversion kernels (device pointers) -------------------------------------------------- */
+
+/* O0 weight conversion: out_fp16[rows,K] = half(e2m1(nibble) * 2^(scale-127)).
+ * Replaces adangel_launch_mxfp4_to_fp16 (include/adangel/kernel_api.h:21-25,
+ * kernel csrc/sm120/conversion.cu:10-23). */
+int adg_mxfp4_to_fp16(const void* w_mxfp4, const void* w_scale, void* out_fp16, int64_t rows, int64_t K, void* stream);
+
+/* O0 activation conversion: out_fp16[rows,K] = half(float(a) * a_scale[row]).
+ * Replaces adangel_launch_int8_to_fp16 (kernel_api.h:27-31, conversion.cu:25-37). */
+int adg_int8_to_fp16(const void* a_int8, const void* a_scale, void* out_fp16, int64_t rows, int64_t K, void* stream);
+
+/* O1 weight conversion: out_int8[rows,K] = 2 * e2m1(nibble), exact.
+ * Replaces adangel_launch_mxfp4_to_int8 (kernel_api.h:33-36, conversion.cu:39-50). */
+int adg_mxfp4_to_int8(const void* w_mxfp4, void* out_int8, int64_t rows, int64_t K, void* stream);
+
+/* Size in bytes of the tiled scale-factor buffer for a [rows, K/32] scale matrix (512-byte atoms
+ * of 128 rows x 4 blocks, zero padded to 256 rows / 8 blocks). */
+int64_t adg_o2_tiled_scale_bytes(int64_t rows, int64_t K);
+
+/* O2 activation re-quantization, fused with the scale re-layout: per (row, K32 block) of
+ * float(a)*a_scale[row]: UE8M0 scale floor(log2(amax))-2 (0 for a zero block) and E2M1
+ * round-to-nearest-even codes.  Writes packed codes [M,K/2], optionally the natural scales
+ * [M,K/32] (sf_natural may be NULL) and the tiled scales (sf_tiled, which the caller zero-filled
+ * once so that padding is zero).  Replaces adangel_o2_quantize_activation +
+ * adangel_o2_repack_scale (csrc/sm120/o2_cutlass.cu:207-274). */
+int adg_o2_quantize_activation(const void* a_int8, const void* a_scale, void* a_mxfp4, void* sf_natural,
+                               void* sf_tiled, int64_t M, int64_t K, void* stream);
+
+/* O2 weight-scale re-layout: natural [rows,K/32] -> tiled buffer (padding written as zero).
+ * Replaces adangel_o2_repack_scale for SFB (o2_cutlass.cu:261-274, :298-316). */
+int adg_o2_tile_scales(const void* sf_natural, void* sf_tiled, int64_t rows, int64_t K, void* stream);
+
+/* ---- GEMM kernels (device pointers) ---------------------------------------------------------- */
+/* ldy is the row pitch of Y in elements (>= N); Y may be a column block of a wider matrix. */
+
+/* O0 GEMM: Y = A_fp16 @ W_fp16^T, FP32 accumulate (tcgen05 kind::f16).
+ * Replaces the cuBLASLt plan O0LtPlan::run (csrc/sm120/o0_gemm.cu:86-298). */
+int adg_gemm_o0(const void* a_fp16, const void* w_fp16, float* y, int M, int N, int K, int ldy, void* stream);
+
+/* O1 GEMM: per K32 group INT32 partial (tcgen05 kind::i8) scaled by
+ * (A_scale[m] * 2^(W_scale[n,g]-127)) * 0.5 and accumulated in FP32 in ascending group order.
+ * partial_dump, if not NULL, receives the INT32 partials as [M,N,K/32] (debug/parity aid).
+ * Replaces adangel_o1_tma_warp_specialized (csrc/sm120/o1_gemm.cu:167-392). */
+int adg_gemm_o1(const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale, float* y,
+                int32_t* partial_dump, int M, int N, int K, int ldy, void* stream);
+
+/* O2 GEMM: block-scaled MXFP4 x MXFP4 (tcgen05 kind::mxf4.block_scale), scales in tiled layout.
+ * Replaces the CUTLASS block-scaled GEMM (csrc/sm120/o2_cutlass.cu:35-93, :394-472). */
+int adg_gemm_o2(const void* a_mxfp4, const void* a_sf_tiled, const void* w_mxfp4, const void* w_sf_tiled, float* y,
+                int M, int N, int K, int ldy, void* stream);
+
+/* ---- timing harness -------------------------------------------------------------------------- */
+
+#define ADG_MODE_CONVERSION_ONLY 0
+#define ADG_MODE_COMPUTE_ONLY 1
+#define ADG_MODE_COLD 2
+#define ADG_MODE_STEADY_STATE 3
+
+#define ADG_STAGE_WEIGHT 0x1u
+#define ADG_STAGE_ACTIVATION 0x2u
+#define ADG_STAGE_GEMM 0x4u
+#define ADG_STAGE_TOTAL 0x8u
+
+typedef struct adg_bench_args {
+  int32_t variant; /* 0, 1, 2 */
+  int32_t mode;    /* ADG_MODE_* */
+  int32_t M, N, K;
+  int32_t warmup, repeats, conversion_inner_repeats;
+  /* inputs (device) */
+  const void* a_int8;
+  const void* a_scale;
+  const void* w_mxfp4;
+  const void* w_scale;
+  /* caller-owned device buffers */
+  float* output;        /* [M,N] */
+  void* conv_weight;    /* O0: fp16 [N,K]; O1: int8 [N,K]; O2: tiled W scales */
+  void* conv_act;       /* O0: fp16 [M,K]; O2: packed codes [M,K/2]; O1: unused */
+  void* conv_act_sf;    /* O2: natural scales [M,K/32] */
+  void* conv_act_sf_tiled; /* O2: tiled A scales, zero-filled by the caller */
+  /* host result arrays, each `repeats` floats (milliseconds); filled for the stages in stages_out */
+  float* t_weight;
+  float* t_activation;
+  float* t_gemm;
+  float* t_total;
+  uint32_t stages_out;
+  void* stream;
+} adg_bench_args;
+
+/* Runs the reference's timing protocol for one variant and mode (warm-up, `repeats` directly timed
+ * iterations with CUDA events, conversions additionally timed as isolated batches of
+ * conversion_inner_repeats launches) and leaves a valid output in args->output.  Synchronises.
+ * Replaces adangel_benchmark_o0/o1/o2 (csrc/sm120/o0_gemm.cu:351-531, o1_gemm.cu:431-566,
+ * o2_cutlass.cu:364-617). */
+int adg_benchmark(adg_bench_args* args);
+
+/* Known-answer probe of the block-scaled MMA's scale-factor layout: one tile, all nibbles +0.5,
+ * a distinct scale per row/column/block.  Replaces adangel_verify_o2_layout_cuda
+ * (csrc/sm120/o2_microkernel.cu:49-115).  Synchronises. */
+int adg_verify_layout(int* passed, float* max_abs_error);
+
+/* ---- host-buffer sessions ---------------------------------------------------------------------- */
+/* A session keeps one weight matrix resident on the device in the form a variant's GEMM consumes
+ * (the steady-state case: weights converted once, activations arriving from the host each call). */
+
+typedef struct adg_session adg_session;
+
+/* Uploads W (host pointers) for `variant`, converts it and sizes activation/output buffers for up
+ * to max_M rows.  Synchronises. */
+int adg_session_create(adg_session** out, int variant, int max_M, int N, int K, const void* w_mxfp4_host,
+                       const void* w_scale_host);
+
+/* One end-to-end pass: host A -> device, activation conversion, GEMM, device Y -> host (y_host is
+ * [M,N] fp32).  Pinned host buffers make the copies asynchronous; the call returns after the
+ * result is in y_host. */
+int adg_session_run(adg_session* session, const void* a_int8_host, const void* a_scale_host, int M, float* y_host);
+
+void adg_session_destroy(adg_session* session);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ADANGEL_B200_H_ */

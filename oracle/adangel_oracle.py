@@ -239,6 +239,37 @@ def run_o2(a_int8, a_scale, w_mxfp4, w_scale, exponent=block_exponent):
     return {"output": y, "converted_weight": None, "converted_activation": (a_mx, a_sc)}
 
 
+def prepare_weights(w_mxfp4, w_scale):
+    """The weight-side work of the three variants, done once (the steady-state case): FP16-rounded
+    W for O0, the INT8 image and FP32 group scales for O1, FP32 dequantized W for O2."""
+    w_int8 = mxfp4_to_int8_base(w_mxfp4)
+    return {
+        "w16": dequantize_mxfp4(w_mxfp4, w_scale, np.float16).astype(np.float32),
+        "w_int8_f32": w_int8.astype(np.float32),
+        "w_scales": decode_ue8m0(w_scale),
+        "w_deq": dequantize_mxfp4(w_mxfp4, w_scale, np.float32),
+    }
+
+
+def steady_state_step(a_int8, a_scale, prepared):
+    """One steady-state pass of O0, O1 and O2 on prepared weights: per variant the activation-side
+    conversion plus the GEMM, exactly the arithmetic of run_o0 / run_o1 / run_o2."""
+    a16 = dequantize_int8_per_row(a_int8, a_scale, np.float16)
+    y0 = a16.astype(np.float32) @ prepared["w16"].T
+    m, k = a_int8.shape
+    y1 = np.zeros((m, prepared["w16"].shape[0]), dtype=np.float32)
+    a_f = a_int8.astype(np.float32)
+    half = np.float32(0.5)
+    for g in range(k // GROUP_SIZE):
+        sl = slice(g * GROUP_SIZE, (g + 1) * GROUP_SIZE)
+        partial = a_f[:, sl] @ prepared["w_int8_f32"][:, sl].T
+        y1 += partial * ((a_scale[:, None] * prepared["w_scales"][:, g][None, :]) * half)
+    act = dequantize_int8_per_row(a_int8, a_scale, np.float32)
+    a_mx, a_sc = quantize_mxfp4(act)
+    y2 = dequantize_mxfp4(a_mx, a_sc, np.float32) @ prepared["w_deq"].T
+    return y0, y1, y2
+
+
 def mse_fp64(output, reference) -> float:
     """python/adangel/benchmark/metrics.py:42-50."""
     if output.shape != reference.shape:

@@ -1,0 +1,137 @@
+"""Parity of the three GEMM variants with the CPU oracle, through the C ABI and the ops surface.
+
+Tolerances: INT32 K32 partials exact; O1 output bit-identical to the oracle (same operation order);
+O0/O2 outputs within rtol = atol = 1e-3 (the tolerance of the reference's own GPU tests,
+tests/integration/test_sm120_o{0,1,2}.py); MSE vs O0 within 2 % of the oracle's.
+"""
+
+import numpy as np
+import pytest
+
+from oracle import adangel_oracle as orc
+from tests.gpu_util import golden_inputs, to_cuda
+
+pytestmark = pytest.mark.gpu
+
+RTOL = ATOL = 1e-3
+GOLDEN = ["canonical_128x128x128", "canonical_68x36x64", "fp16_seed2026_128x128x256", "fp16_seed2026_132x132x256",
+          "edge_zero_128x128x256", "edge_alternating_128x128x256", "edge_saturated_128x128x256", "seed7_16x8x64"]
+
+
+@pytest.fixture(scope="module")
+def K():
+    from adangel_oyzl_b200 import kernels
+
+    return kernels
+
+
+def _gpu_all(K, a_int8, a_scale, w_mx, w_sc, dump=False):
+    da, ds, dw, dws = to_cuda(a_int8, a_scale, w_mx, w_sc)
+    y0 = K.gemm_o0(K.int8_to_fp16(da, ds), K.mxfp4_to_fp16(dw, dws))
+    r1 = K.gemm_o1(da, ds, K.mxfp4_to_int8(dw), dws, dump_partials=dump)
+    codes, _, sfa = K.o2_quantize_activation(da, ds)
+    y2 = K.gemm_o2(codes, sfa, dw, K.o2_tile_scales(dws))
+    K.check_status()
+    y1, partials = r1 if dump else (r1, None)
+    return y0.cpu().numpy(), y1.cpu().numpy(), y2.cpu().numpy(), (partials.cpu().numpy() if dump else None)
+
+
+def _compare(K, a_int8, a_scale, w_mx, w_sc, dump=True):
+    y0, y1, y2, partials = _gpu_all(K, a_int8, a_scale, w_mx, w_sc, dump)
+    o0 = orc.run_o0(a_int8, a_scale, w_mx, w_sc)["output"]
+    o1 = orc.run_o1(a_int8, a_scale, w_mx, w_sc)["output"]
+    o2 = orc.run_o2(a_int8, a_scale, w_mx, w_sc)["output"]
+    if dump:
+        np.testing.assert_array_equal(partials, orc.o1_partials(a_int8, orc.mxfp4_to_int8_base(w_mx)))
+    np.testing.assert_allclose(y0, o0, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(y1, o1, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(y2, o2, rtol=RTOL, atol=ATOL)
+    np.testing.assert_array_equal(y1, o1)
+    for got, want in ((orc.mse_fp64(y1, y0), orc.mse_fp64(o1, o0)), (orc.mse_fp64(y2, y0), orc.mse_fp64(o2, o0))):
+        assert got == pytest.approx(want, rel=0.02, abs=1e-12)
+    return y0, y1, y2
+
+
+def test_layout_probe():
+    from adangel_oyzl_b200.ops import _sm100
+
+    result = _sm100.verify_layout()
+    assert result["passed"], result
+    assert result["max_abs_error"] <= 1e-3
+
+
+@pytest.mark.parametrize("name", GOLDEN)
+def test_golden_files(K, golden_dir, name):
+    ref, args = golden_inputs(golden_dir, name)
+    y0, y1, y2 = _compare(K, *args)
+    # and against the reference's own stored outputs
+    np.testing.assert_allclose(y0, ref["o0_output"], rtol=RTOL, atol=ATOL)
+    np.testing.assert_array_equal(y1, ref["o1_output"])
+    np.testing.assert_allclose(y2, ref["o2_output"], rtol=RTOL, atol=ATOL)
+    assert orc.mse_fp64(y1, y0) == pytest.approx(float(ref["mse_o1"]), rel=0.02, abs=1e-12)
+    assert orc.mse_fp64(y2, y0) == pytest.approx(float(ref["mse_o2"]), rel=0.02, abs=1e-12)
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 128), (256, 512, 1024), (1000, 768, 2048)])
+def test_canonical_grid(K, shape):
+    _compare(K, *orc.canonical_inputs(*shape), dump=shape[0] <= 256)
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 64), (16, 256, 192), (64, 384, 320), (129, 257 * 4, 448), (300, 40, 128)])
+def test_ragged_shapes(K, shape):
+    # K not a multiple of the kernels' K slab, M/N not multiples of the tile, single-row A
+    m, n, k = shape
+    _compare(K, *orc.canonical_inputs(m, n, k, seed=11))
+
+
+def test_output_column_block(K):
+    # Y written as a column block of a wider matrix (the N-sharded layout): ldy > N
+    import torch
+
+    a_int8, a_scale, w_mx, w_sc = orc.canonical_inputs(200, 384, 256, seed=5)
+    da, ds, dw, dws = to_cuda(a_int8, a_scale, w_mx, w_sc)
+    wide = torch.full((200, 1024), -7.0, device="cuda")
+    K.gemm_o0(K.int8_to_fp16(da, ds), K.mxfp4_to_fp16(dw, dws), out=wide[:, 128:512])
+    K.gemm_o1(da, ds, K.mxfp4_to_int8(dw), dws, out=wide[:, 512:896])
+    K.check_status()
+    got = wide.cpu().numpy()
+    np.testing.assert_allclose(got[:, 128:512], orc.run_o0(a_int8, a_scale, w_mx, w_sc)["output"], rtol=RTOL, atol=ATOL)
+    np.testing.assert_array_equal(got[:, 512:896], orc.run_o1(a_int8, a_scale, w_mx, w_sc)["output"])
+    assert (got[:, :128] == -7.0).all() and (got[:, 896:] == -7.0).all()
+
+
+def test_deterministic_rerun(K):
+    # the same launch twice must give the same bits (a difference would indicate a race)
+    args = orc.canonical_inputs(384, 512, 512, seed=3)
+    first = _gpu_all(K, *args)
+    second = _gpu_all(K, *args)
+    for a, b in zip(first[:3], second[:3]):
+        np.testing.assert_array_equal(a, b)
+
+
+def test_full_size_4096(K):
+    """4096^3: sampled rows against the oracle (rows of Y are independent), plus MSE vs O0."""
+    import torch
+
+    from adangel_oyzl_b200 import synthetic
+
+    p = synthetic.canonical_inputs(4096, 4096, 4096, device="cuda")
+    y0 = K.gemm_o0(K.int8_to_fp16(p.A_int8, p.A_scale), K.mxfp4_to_fp16(p.W_mxfp4, p.W_scale))
+    y1 = K.gemm_o1(p.A_int8, p.A_scale, K.mxfp4_to_int8(p.W_mxfp4), p.W_scale)
+    codes, _, sfa = K.o2_quantize_activation(p.A_int8, p.A_scale)
+    y2 = K.gemm_o2(codes, sfa, p.W_mxfp4, K.o2_tile_scales(p.W_scale))
+    K.check_status()
+    rows = torch.arange(5, 4096, 127, device="cuda")
+    a_np, s_np = p.A_int8[rows].cpu().numpy(), p.A_scale[rows].cpu().numpy()
+    w_np, ws_np = p.W_mxfp4.cpu().numpy(), p.W_scale.cpu().numpy()
+    o0 = orc.run_o0(a_np, s_np, w_np, ws_np)["output"]
+    o1 = orc.run_o1(a_np, s_np, w_np, ws_np)["output"]
+    o2 = orc.run_o2(a_np, s_np, w_np, ws_np)["output"]
+    np.testing.assert_allclose(y0[rows].cpu().numpy(), o0, rtol=RTOL, atol=ATOL)
+    np.testing.assert_array_equal(y1[rows].cpu().numpy(), o1)
+    np.testing.assert_allclose(y2[rows].cpu().numpy(), o2, rtol=RTOL, atol=ATOL)
+    assert torch.isfinite(y0).all() and torch.isfinite(y1).all() and torch.isfinite(y2).all()
+    mse1 = float(((y1.double() - y0.double()) ** 2).mean())
+    mse2 = float(((y2.double() - y0.double()) ** 2).mean())
+    assert mse1 == pytest.approx(orc.mse_fp64(o1, o0), rel=0.25)
+    assert mse2 == pytest.approx(orc.mse_fp64(o2, o0), rel=0.25)
