@@ -50,6 +50,14 @@ __device__ __forceinline__ uint32_t float2_to_e2m1x2(float first, float second) 
   return out;
 }
 
+// prmt.b32 in its default mode: selector nibble bits [2:0] pick one of the eight source bytes
+// {b:a}; bit 3 replaces the picked byte by eight copies of its most significant bit.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
+  return d;
+}
+
 // Eight E2M1 nibbles of one 32-bit word -> eight INT8 values 2*E2M1 (two 32-bit words).
 // Magnitudes come from a byte-permute lookup, signs from a sign-replicating byte permute.
 __device__ __forceinline__ void e2m1x8_to_int8x8(uint32_t w, uint32_t& lo4, uint32_t& hi4) {
@@ -59,12 +67,12 @@ __device__ __forceinline__ void e2m1x8_to_int8x8(uint32_t w, uint32_t& lo4, uint
   const uint32_t sel1 = (w >> 16) & 0x7777u;
   const uint32_t ws = w << 4;  // bit 3 of every even nibble becomes the MSB of its byte
   // elements 0..3 live in bytes 0,1 of w; elements 4..7 in bytes 2,3
-  const uint32_t m0 = __byte_perm(ws, w, 0xD9C8u);
-  const uint32_t m1 = __byte_perm(ws, w, 0xFBEAu);
-  const uint32_t p0 = __byte_perm(pos_lo, pos_hi, sel0);
-  const uint32_t p1 = __byte_perm(pos_lo, pos_hi, sel1);
-  const uint32_t n0 = __byte_perm(neg_lo, neg_hi, sel0);
-  const uint32_t n1 = __byte_perm(neg_lo, neg_hi, sel1);
+  const uint32_t m0 = prmt(ws, w, 0xD9C8u);
+  const uint32_t m1 = prmt(ws, w, 0xFBEAu);
+  const uint32_t p0 = prmt(pos_lo, pos_hi, sel0);
+  const uint32_t p1 = prmt(pos_lo, pos_hi, sel1);
+  const uint32_t n0 = prmt(neg_lo, neg_hi, sel0);
+  const uint32_t n1 = prmt(neg_lo, neg_hi, sel1);
   lo4 = (p0 & ~m0) | (n0 & m0);
   hi4 = (p1 & ~m1) | (n1 & m1);
 }

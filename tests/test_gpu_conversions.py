@@ -116,12 +116,12 @@ def test_full_size_conversion_properties(K):
     codes, nat, tiled = K.o2_quantize_activation(p.A_int8, p.A_scale)
     K.check_status()
     # 2*E2M1 image: w16 == w8 * 2^(s-128) exactly wherever that product is a normal half
-    scale = torch.ldexp(torch.ones((), device="cuda"), p.W_scale.to(torch.int32) - 128)
+    exps = p.W_scale.to(torch.int32) - 128
+    scale = torch.ldexp(torch.ones_like(exps, dtype=torch.float32), exps)
     recon = (w8.float().reshape(4096, 128, 32) * scale[:, :, None]).reshape(4096, 4096)
     assert torch.equal(recon.half(), w16)
     # dequantize(requantize(A)) stays within half an E2M1 step of A in every block
     rows = torch.arange(0, 4096, 61, device="cuda")
-    sel = rows.cpu().numpy()
     a_np, s_np = p.A_int8[rows].cpu().numpy(), p.A_scale[rows].cpu().numpy()
     assert_requant_matches(codes[rows].cpu().numpy(), nat[rows].cpu().numpy(), a_np, s_np, orc)
     np.testing.assert_array_equal(a16[rows].cpu().numpy().view(np.uint16),
@@ -130,4 +130,3 @@ def test_full_size_conversion_properties(K):
     np.testing.assert_array_equal(w16[rows].cpu().numpy().view(np.uint16), orc.dequantize_mxfp4(w_np, ws_np, np.float16).view(np.uint16))
     np.testing.assert_array_equal(w8[rows].cpu().numpy(), orc.mxfp4_to_int8_base(w_np))
     np.testing.assert_array_equal(tiled.cpu().numpy(), orc.tile_scale_factors(nat.cpu().numpy()))
-    del sel
