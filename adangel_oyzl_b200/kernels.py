@@ -143,6 +143,24 @@ def gemm_o2(a_mxfp4, a_sf_tiled, w_mxfp4, w_sf_tiled, out=None):
     return out
 
 
+def o2_linear_noalloc(a_int8, a_scale, w_mxfp4, w_sf_tiled, out, synchronize=True):
+    """O2 for callers that cannot allocate device memory: activation re-quantization and GEMM using
+    the library's built-in scratch array (``adg_o2_linear_noalloc``).  ``out`` must be provided by
+    the caller; nothing is allocated here or in the library.  Calls share the scratch array, so
+    they must not overlap on the GPU."""
+    import torch
+
+    m, k = a_int8.shape
+    n = w_mxfp4.shape[0]
+    _require(out is not None and out.dtype == torch.float32 and tuple(out.shape) == (m, n) and out.stride(1) == 1,
+             "invalid output tensor")
+    with torch.cuda.device(a_int8.device):
+        _sm100._check(_lib().adg_o2_linear_noalloc(
+            a_int8.data_ptr(), a_scale.data_ptr(), w_mxfp4.data_ptr(), w_sf_tiled.data_ptr(), out.data_ptr(),
+            m, n, k, int(out.stride(0)), _stream(out), 1 if synchronize else 0))
+    return out
+
+
 def check_status(device=None):
     """Synchronise torch's current stream and raise if a kernel reported a bounded-wait timeout."""
     import torch

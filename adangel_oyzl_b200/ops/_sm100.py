@@ -52,6 +52,7 @@ _SIGNATURES = {
     "adg_gemm_o0": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "adg_gemm_o1": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "adg_gemm_o2": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "adg_o2_linear_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int]),
     "adg_benchmark": (c_int, [POINTER(BenchArgs)]),
     "adg_verify_layout": (c_int, [POINTER(c_int), POINTER(c_float)]),
     "adg_session_create": (c_int, [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_void_p, c_void_p]),

@@ -104,6 +104,25 @@ int adg_gemm_o1(const void* a_int8, const void* a_scale, const void* w_int8, con
 int adg_gemm_o2(const void* a_mxfp4, const void* a_sf_tiled, const void* w_mxfp4, const void* w_sf_tiled, float* y,
                 int M, int N, int K, int ldy, void* stream);
 
+/* O2 without device allocations: Y = requantize(A) @ W^T in one call, for callers that cannot
+ * allocate (a server whose memory pool already owns all of the GPU's memory, or a latency-critical
+ * loop that must avoid the device-wide synchronisation of cudaMalloc/cudaFree).  The packed codes
+ * and tiled scales of A and the kernels' status words live in a fixed array inside the library
+ * (about 4.5 MiB held on every GPU that loads it, until the process exits); the caller passes only
+ * inputs and the output.  This entry point has no counterpart in the reference.
+ *   - Limits: M*K/2 <= 4 MiB of codes and adg_o2_tiled_scale_bytes(M, K) <= 512 KiB (for example
+ *     1024 x 8192 or 512 x 16384); larger activations are rejected with an error.
+ *   - w_sf_tiled is W's scales in tiled form (adg_o2_tile_scales, done once per weight).
+ *   - The first call on a device performs one-time set-up (address look-up of the array, kernel
+ *     attributes); make that first call before starting any stream capture.
+ *   - All calls share the one array: two calls that overlap on the GPU (different streams, or
+ *     different host threads) race on it.  Issue them on one stream or order them yourself.
+ *   - synchronize != 0: wait for the result and report a kernel wait timeout as an error;
+ *     synchronize == 0: return after enqueueing.
+ * It calls no cudaMalloc/cudaFree and no allocating library routine. */
+int adg_o2_linear_noalloc(const void* a_int8, const void* a_scale, const void* w_mxfp4, const void* w_sf_tiled,
+                          float* y, int M, int N, int K, int ldy, void* stream, int synchronize);
+
 /* ---- timing harness -------------------------------------------------------------------------- */
 
 #define ADG_MODE_CONVERSION_ONLY 0
