@@ -10,8 +10,10 @@
 //               scale-factor atoms, into a multi-stage shared-memory ring guarded by mbarriers
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (and, for O2, the shared ->
 //               tensor-memory scale-factor copies) and commits completion to the mbarriers
-//   warps 2-5   epilogue: tcgen05.ld the FP32 accumulator (each warp owns one 32-lane quarter),
-//               stage 32x32 blocks in swizzled shared memory and write them with TMA stores
+//   warps 2-9   epilogue: two warps per 32-lane quarter of tensor memory, each draining half of the
+//               accumulator's columns into registers in one go (so the accumulator is released
+//               after a few hundred cycles), then writing 32x16 blocks through swizzled
+//               shared-memory staging with TMA stores while the next tile's MMAs already run
 // All waits are bounded (see common.cuh); on a timeout the kernel records an error and returns.
 #include "common.cuh"
 #include "launch.h"
@@ -21,8 +23,9 @@ namespace adg {
 namespace {
 
 constexpr int kBlockM = 128;
-constexpr int kAccThreads = 192;
-constexpr int kEpiWarps = 4;
+constexpr int kEpiWarps = 8;
+constexpr int kAccThreads = (2 + kEpiWarps) * 32;
+constexpr int kStagingPerWarp = 2048;  // one 32-row x 16-column FP32 block
 constexpr int kGroupM = 8;  // tile rasterisation: sweep 8 row-blocks before moving to the next column-block
 
 enum : uint32_t {  // wait tags reported on timeout
@@ -35,7 +38,7 @@ enum : uint32_t {  // wait tags reported on timeout
 template <int KIND, int BLOCK_N>
 struct AccCfg {
   static constexpr bool kScaled = KIND == 2;
-  static constexpr int kStages = BLOCK_N == 256 ? 4 : 5;
+  static constexpr int kStages = BLOCK_N == 256 ? 4 : 6;
   static constexpr int kElemsPerStage = kScaled ? 256 : 64;  // K elements covered by 128 bytes
   static constexpr int kTileA = kBlockM * 128;
   static constexpr int kTileB = BLOCK_N * 128;
@@ -43,8 +46,8 @@ struct AccCfg {
   static constexpr int kSfb = kScaled ? (BLOCK_N / 128) * 1024 : 0;  // per 128 rows: two atoms
   static constexpr int kStageBytes = kTileA + kTileB + kSfa + kSfb;
   static constexpr int kAccStages = (kScaled && BLOCK_N == 256) ? 1 : 2;
-  static constexpr int kStagingBufs = (kScaled && BLOCK_N == 256) ? 1 : 2;
-  static constexpr int kStagingBytes = kEpiWarps * kStagingBufs * 4096;
+  static constexpr int kStagingBytes = kEpiWarps * kStagingPerWarp;
+  static constexpr int kColsPerWarp = BLOCK_N / 2;  // accumulator columns drained by one epilogue warp
   static constexpr int kSfColsPerStage = kScaled ? 8 + 2 * (BLOCK_N / 32) : 0;
   static constexpr int kSfColBase = kAccStages * BLOCK_N;
   static constexpr int kTmemCols = 512;
@@ -215,11 +218,13 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     }
   } else {
     // ------------------------------- epilogue ---------------------------------------------------
-    const int q = warp & 3;  // the 32-lane quarter of tensor memory this warp can read
-    const int epi = warp - 2;
-    uint8_t* my_staging = staging + epi * Cfg::kStagingBufs * 4096;
+    const int q = warp & 3;         // the 32-lane quarter of tensor memory this warp can read
+    const int h = (warp - 2) >> 2;  // which half of the accumulator's columns this warp drains
+    constexpr int CW = Cfg::kColsPerWarp;
+    uint8_t* buf = staging + (warp - 2) * kStagingPerWarp;
+    const uint32_t buf_row = smem_u32(buf) + lane * 64;
+    const uint32_t swz = static_cast<uint32_t>((lane >> 1) & 3);
     int local_tile = 0;
-    uint32_t chunk_counter = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
       const TileCoord tc = tile_coord(tile, num_m, num_n);
@@ -229,47 +234,45 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const int row0 = tc.m_blk * kBlockM + q * 32;
-      const int col0 = tc.n_blk * BLOCK_N;
-      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BLOCK_N);
-#pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_addr + c * 32, r);
-        tmem_wait_ld();
-        if (c == BLOCK_N / 32 - 1) {
-          // every accumulator column of this warp's quarter is now in registers
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
-        }
-        const int col = col0 + c * 32;
-        if (use_tma_store) {
-          uint8_t* buf = my_staging + (chunk_counter % Cfg::kStagingBufs) * 4096;
-          ++chunk_counter;
-          if (lane == 0) bulk_wait_group_read<Cfg::kStagingBufs - 1>();
-          __syncwarp();
-          const uint32_t row_addr = smem_u32(buf) + lane * 128;
+      const int col0 = tc.n_blk * BLOCK_N + h * CW;
+      const uint32_t t_addr =
+          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BLOCK_N + h * CW);
+      uint32_t r[CW / 32][32];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t addr = row_addr + ((j ^ (lane & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r[4 * j]), "r"(r[4 * j + 1]),
-                         "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
+      for (int i = 0; i < CW / 32; ++i) tmem_ld_32x32(t_addr + i * 32, r[i]);
+      tmem_wait_ld();
+      // this warp's share of the accumulator is in registers: hand the columns back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+      if (use_tma_store) {
+#pragma unroll
+        for (int c = 0; c < CW / 16; ++c) {
+          if (lane == 0) bulk_wait_group_read<0>();  // the previous block has left the staging buffer
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int e = (c & 1) * 16 + 4 * j;
+            const uint32_t addr = buf_row + ((static_cast<uint32_t>(j) ^ swz) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r[c >> 1][e]),
+                         "r"(r[c >> 1][e + 1]), "r"(r[c >> 1][e + 2]), "r"(r[c >> 1][e + 3])
                          : "memory");
           }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
+            const int col = col0 + c * 16;
             if (row0 < M && col < N) tma_store_2d(&tm_y, buf, col, row0);
             bulk_commit_group();
           }
-        } else {
-          const int row = row0 + lane;
-          if (row < M) {
-            float* dst = y + static_cast<long>(row) * ldy + col;
+        }
+      } else {
+        const int row = row0 + lane;
+        if (row < M) {
+          float* dst = y + static_cast<long>(row) * ldy + col0;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (col + j < N) dst[j] = __uint_as_float(r[j]);
-            }
+          for (int j = 0; j < CW; ++j) {
+            if (col0 + j < N) dst[j] = __uint_as_float(r[j >> 5][j & 31]);
           }
         }
       }

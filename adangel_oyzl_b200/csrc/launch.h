@@ -47,7 +47,8 @@ int launch_o2_tile_scales(const void* natural, void* tiled, long rows, long k, c
 
 // ---- tensor maps ---------------------------------------------------------------------------------
 // 2-D row-major tensor [rows, cols] of `elem_bytes`-wide elements with a row pitch of `pitch_bytes`;
-// the box is box_cols x box_rows elements and shared memory uses the 128-byte swizzle.
+// the box is box_cols x box_rows elements; its width in bytes (64 or 128) selects the shared-memory
+// swizzle of the same width.
 int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, const void* base, uint64_t rows,
                          uint64_t cols, uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols);
 

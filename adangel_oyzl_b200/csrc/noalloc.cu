@@ -86,7 +86,8 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, ui
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t elem_strides[2] = {1, 1};
   const CUresult res = g_encode_fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   box_cols * (dtype == CU_TENSOR_MAP_DATA_TYPE_FLOAT32 ? 4u : 1u) == 128u ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (res != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(res)));
   return 0;
@@ -135,7 +136,7 @@ extern "C" int adg_o2_linear_noalloc(const void* a_int8, const void* a_scale, co
   const bool aligned = (reinterpret_cast<uintptr_t>(y) & 15u) == 0 && (static_cast<uint64_t>(ldy) * 4u) % 16u == 0;
   plan.use_tma_store = aligned ? 1 : 0;
   if (aligned) {
-    if (int rc = encode_map(&plan.tm_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, y, M, N, static_cast<uint64_t>(ldy) * 4u, 32, 32))
+    if (int rc = encode_map(&plan.tm_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, y, M, N, static_cast<uint64_t>(ldy) * 4u, 32, 16))
       return rc;
   } else {
     plan.tm_y = plan.tm_a;

@@ -92,13 +92,15 @@ int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_b
   if (g_encode == nullptr) return fail("tensor-map encoder not initialised");
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return fail("tensor base address must be 16-byte aligned");
   if ((pitch_bytes & 15u) != 0) return fail("tensor row pitch must be a multiple of 16 bytes");
-  if (box_cols * static_cast<uint32_t>(elem_bytes) != 128u) return fail("box width must be 128 bytes");
+  const uint32_t box_bytes = box_cols * static_cast<uint32_t>(elem_bytes);
+  if (box_bytes != 128u && box_bytes != 64u) return fail("box width must be 64 or 128 bytes");
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {pitch_bytes};
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t elem_strides[2] = {1, 1};
   const CUresult res = g_encode(map, dtype, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                box_bytes == 128u ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (res != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(res)));
   return 0;
@@ -121,7 +123,7 @@ int plan_output(GemmPlan* plan, float* y) {
   plan->use_tma_store = aligned ? 1 : 0;
   if (aligned) {
     return encode_tensor_map_2d(&plan->tm_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, y, plan->M, plan->N,
-                                static_cast<uint64_t>(plan->ldy) * 4u, 32, 32);
+                                static_cast<uint64_t>(plan->ldy) * 4u, 32, 16);
   }
   // a valid (unused) map keeps the kernel's prefetch harmless
   plan->tm_y = plan->tm_a;
