@@ -58,6 +58,18 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t select
   return d;
 }
 
+// Four packed INT8 values -> four FP32 values without the (slow) integer-to-float conversion unit:
+// each byte, biased by 128, is spliced into the mantissa of 2**23, and 2**23 + 128 is subtracted.
+// Exact for every INT8 value.
+__device__ __forceinline__ void int8x4_to_float4(uint32_t w, float (&f)[4]) {
+  const uint32_t biased = w ^ 0x80808080u;
+  const float bias = 8388736.0f;  // 2**23 + 128
+  f[0] = __uint_as_float(prmt(biased, 0x4B000000u, 0x7540u)) - bias;
+  f[1] = __uint_as_float(prmt(biased, 0x4B000000u, 0x7541u)) - bias;
+  f[2] = __uint_as_float(prmt(biased, 0x4B000000u, 0x7542u)) - bias;
+  f[3] = __uint_as_float(prmt(biased, 0x4B000000u, 0x7543u)) - bias;
+}
+
 // Eight E2M1 nibbles of one 32-bit word -> eight INT8 values 2*E2M1 (two 32-bit words).
 // Magnitudes come from a byte-permute lookup, signs from a sign-replicating byte permute.
 __device__ __forceinline__ void e2m1x8_to_int8x8(uint32_t w, uint32_t& lo4, uint32_t& hi4) {

@@ -89,16 +89,17 @@ __global__ void __launch_bounds__(kThreads) int8_to_fp16_kernel(const uint2* __r
     const long i = base + static_cast<long>(u) * kThreads;
     if (i >= octs) continue;
     uint32_t o[4];
-    const uint32_t words[2] = {v[u].x, v[u].y};
-#pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      const uint32_t word = words[p >> 1];
-      const int sh = (p & 1) * 16;
-      const float a = static_cast<float>(static_cast<int8_t>(word >> sh));
-      const float b = static_cast<float>(static_cast<int8_t>(word >> (sh + 8)));
-      const __half2 h = __floats2half2_rn(a * s[u], b * s[u]);
-      o[p] = *reinterpret_cast<const uint32_t*>(&h);
-    }
+    float lo[4], hi[4];
+    int8x4_to_float4(v[u].x, lo);
+    int8x4_to_float4(v[u].y, hi);
+    const __half2 h0 = __floats2half2_rn(lo[0] * s[u], lo[1] * s[u]);
+    const __half2 h1 = __floats2half2_rn(lo[2] * s[u], lo[3] * s[u]);
+    const __half2 h2 = __floats2half2_rn(hi[0] * s[u], hi[1] * s[u]);
+    const __half2 h3 = __floats2half2_rn(hi[2] * s[u], hi[3] * s[u]);
+    o[0] = *reinterpret_cast<const uint32_t*>(&h0);
+    o[1] = *reinterpret_cast<const uint32_t*>(&h1);
+    o[2] = *reinterpret_cast<const uint32_t*>(&h2);
+    o[3] = *reinterpret_cast<const uint32_t*>(&h3);
     out[i] = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
@@ -138,19 +139,25 @@ __global__ void __launch_bounds__(kThreads) o2_quantize_kernel(const uint4* __re
                                                                uint8_t* __restrict__ sf_tiled, long blocks, int groups,
                                                                int katoms) {
   const long gid = static_cast<long>(blockIdx.x) * kThreads + threadIdx.x;
-  if (gid >= blocks) return;
-  const int row = static_cast<int>(gid / groups);
-  const int g = static_cast<int>(gid - static_cast<long>(row) * groups);
-  const uint4 lo = __ldg(in + 2 * gid);
-  const uint4 hi = __ldg(in + 2 * gid + 1);
+  const bool valid = gid < blocks;
+  const long g_safe = valid ? gid : 0;
+  const int row = static_cast<int>(g_safe / groups);
+  const int g = static_cast<int>(g_safe - static_cast<long>(row) * groups);
+  const uint4 lo = __ldg(in + 2 * g_safe);
+  const uint4 hi = __ldg(in + 2 * g_safe + 1);
   const float s = __ldg(row_scale + row);
   const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
   float v[32];
   float amax = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    v[i] = static_cast<float>(static_cast<int8_t>(words[i >> 2] >> (8 * (i & 3)))) * s;
-    amax = fmaxf(amax, fabsf(v[i]));
+  for (int wi = 0; wi < 8; ++wi) {
+    float f[4];
+    int8x4_to_float4(words[wi], f);
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      v[wi * 4 + b] = f[b] * s;
+      amax = fmaxf(amax, fabsf(v[wi * 4 + b]));
+    }
   }
   // exact floor(log2(amax)) - 2, clamped; an all-zero block uses exponent 0
   int e = 0;
@@ -173,10 +180,20 @@ __global__ void __launch_bounds__(kThreads) o2_quantize_kernel(const uint4* __re
     }
     o[q] = word;
   }
-  codes[gid] = make_uint4(o[0], o[1], o[2], o[3]);
-  const uint8_t code = static_cast<uint8_t>(e + 127);
-  if (sf_natural != nullptr) sf_natural[gid] = code;
-  sf_tiled[tiled_sf_offset(row, g, katoms)] = code;
+  if (valid) codes[gid] = make_uint4(o[0], o[1], o[2], o[3]);
+  const uint32_t code = static_cast<uint32_t>(e + 127);
+  if ((groups & 3) == 0) {
+    // four consecutive lanes hold the four blocks of one tiled-layout word: gather and store once
+    uint32_t packed = code | (__shfl_down_sync(0xffffffffu, code, 1) << 8);
+    packed |= __shfl_down_sync(0xffffffffu, packed, 2) << 16;
+    if (valid && (threadIdx.x & 3) == 0) {
+      if (sf_natural != nullptr) *reinterpret_cast<uint32_t*>(sf_natural + gid) = packed;
+      *reinterpret_cast<uint32_t*>(sf_tiled + tiled_sf_offset(row, g, katoms)) = packed;
+    }
+  } else if (valid) {
+    if (sf_natural != nullptr) sf_natural[gid] = static_cast<uint8_t>(code);
+    sf_tiled[tiled_sf_offset(row, g, katoms)] = static_cast<uint8_t>(code);
+  }
 }
 
 // ---- O2 weight scales: natural [rows, K/32] -> 512-byte atoms, zero padding included -----------

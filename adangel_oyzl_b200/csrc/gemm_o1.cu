@@ -220,8 +220,12 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
   } else if (warp >= kFirstEpiWarp) {
     // ------------------------------- epilogue ---------------------------------------------------
+    // Each warp owns 32 columns of one lane quarter.  A partial is fetched in two 16-column halves
+    // into two register buffers so that the tensor-memory load of the next half is in flight while
+    // the current half is scaled and accumulated.
     const int q = warp & 3;                     // tensor-memory lane quarter
     const int cs = (warp - kFirstEpiWarp) >> 2;  // 32-column slice of the 128-column partial
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(cs * 32);
     int slot = 0, scs = 0;
     uint32_t slot_phase = 0, sc_phase = 0;
     bool ok = true;
@@ -230,53 +234,79 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const int row = tc.m_blk * kBlockM + q * 32 + lane;
       const int col0 = tc.n_blk * kBlockN + cs * 32;
       const float a_m = row < M ? __ldg(a_scale + row) : 0.0f;
-      float acc[32];
+      const float2 a2 = make_float2(a_m, a_m);
+      float2 acc[16];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
-      for (int kb = 0; ok && kb < num_kb; ++kb) {
-        ok = mbar_wait(&sc_full_bar[scs], sc_phase, env, kTagScFull | scs);
-        if (!ok) break;
-        const int ng = min(4, groups - kb * 4);
-        for (int g = 0; g < ng; ++g) {
+      for (int j = 0; j < 16; ++j) acc[j] = make_float2(0.0f, 0.0f);
+      uint32_t lo[16], hi[16];
+      // prologue: both halves of the tile's first partial
+      ok = mbar_wait(&tmem_full_bar[slot], slot_phase, env, kTagTmemFull | slot);
+      if (!ok) break;
+      tc_fence_after();
+      tmem_ld_32x16(t_lane + slot * kBlockN, lo);
+      tmem_ld_32x16(t_lane + slot * kBlockN + 16, hi);
+      tmem_wait_ld_for(lo);
+      for (int g = 0; ok && g < groups; ++g) {
+        if ((g & 3) == 0) {
+          ok = mbar_wait(&sc_full_bar[scs], sc_phase, env, kTagScFull | scs);
+          if (!ok) break;
+        }
+        const float4* sc = reinterpret_cast<const float4*>(sc_ring + scs * (kScBytes / 4) + (g & 3) * kBlockN + cs * 32);
+        if (partial_dump != nullptr) {  // warp-uniform: the wait below is a warp-wide instruction
+          tmem_wait_ld_for(hi);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (row >= M) break;
+            if (col0 + j < N) partial_dump[(static_cast<long>(row) * N + col0 + j) * groups + g] = static_cast<int>(lo[j]);
+            if (col0 + 16 + j < N)
+              partial_dump[(static_cast<long>(row) * N + col0 + 16 + j) * groups + g] = static_cast<int>(hi[j]);
+          }
+        }
+        // ---- first half: columns 0..15 of this warp's slice
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+          const float4 s = sc[j4];
+          const float2 f0 = make_float2(__int2float_rn(static_cast<int>(lo[4 * j4])), __int2float_rn(static_cast<int>(lo[4 * j4 + 1])));
+          const float2 f1 = make_float2(__int2float_rn(static_cast<int>(lo[4 * j4 + 2])), __int2float_rn(static_cast<int>(lo[4 * j4 + 3])));
+          acc[2 * j4] = __ffma2_rn(__fmul2_rn(f0, a2), make_float2(s.x, s.y), acc[2 * j4]);
+          acc[2 * j4 + 1] = __ffma2_rn(__fmul2_rn(f1, a2), make_float2(s.z, s.w), acc[2 * j4 + 1]);
+        }
+        // the second half has arrived: the slot is fully read and can take a new partial
+        tmem_wait_ld_for(hi);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty_bar[slot]);
+        if (++slot == kSlots) {
+          slot = 0;
+          slot_phase ^= 1u;
+        }
+        const bool more = g + 1 < groups;
+        if (more) {
           ok = mbar_wait(&tmem_full_bar[slot], slot_phase, env, kTagTmemFull | slot);
           if (!ok) break;
           tc_fence_after();
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(slot * kBlockN + cs * 32),
-                        r);
-          tmem_wait_ld();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty_bar[slot]);
-          const float4* sc = reinterpret_cast<const float4*>(sc_ring + scs * (kScBytes / 4) + g * kBlockN + cs * 32);
-#pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            const float4 s = sc[j4];
-            const float sv[4] = {s.x, s.y, s.z, s.w};
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              const int j = j4 * 4 + t;
-              const float u = __fmul_rn(__int2float_rn(static_cast<int>(r[j])), a_m);
-              acc[j] = __fmaf_rn(u, sv[t], acc[j]);
-            }
-          }
-          if (partial_dump != nullptr && row < M) {
-            const int gi = kb * 4 + g;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (col0 + j < N) partial_dump[(static_cast<long>(row) * N + col0 + j) * groups + gi] = static_cast<int>(r[j]);
-            }
-          }
-          if (++slot == kSlots) {
-            slot = 0;
-            slot_phase ^= 1u;
-          }
+          tmem_ld_32x16(t_lane + slot * kBlockN, lo);  // in flight during the second half's arithmetic
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sc_empty_bar[scs]);
-        if (++scs == kScStages) {
-          scs = 0;
-          sc_phase ^= 1u;
+        // ---- second half: columns 16..31
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+          const float4 s = sc[4 + j4];
+          const float2 f0 = make_float2(__int2float_rn(static_cast<int>(hi[4 * j4])), __int2float_rn(static_cast<int>(hi[4 * j4 + 1])));
+          const float2 f1 = make_float2(__int2float_rn(static_cast<int>(hi[4 * j4 + 2])), __int2float_rn(static_cast<int>(hi[4 * j4 + 3])));
+          acc[8 + 2 * j4] = __ffma2_rn(__fmul2_rn(f0, a2), make_float2(s.x, s.y), acc[8 + 2 * j4]);
+          acc[8 + 2 * j4 + 1] = __ffma2_rn(__fmul2_rn(f1, a2), make_float2(s.z, s.w), acc[8 + 2 * j4 + 1]);
+        }
+        if (more) {
+          tmem_wait_ld_for(lo);
+          tmem_ld_32x16(t_lane + slot * kBlockN + 16, hi);  // in flight during the next first half
+        }
+        if ((g & 3) == 3 || !more) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sc_empty_bar[scs]);
+          if (++scs == kScStages) {
+            scs = 0;
+            sc_phase ^= 1u;
+          }
         }
       }
       if (ok && row < M) {
@@ -284,12 +314,13 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (col0 + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
           for (int j4 = 0; j4 < 8; ++j4) {
-            reinterpret_cast<float4*>(dst)[j4] = make_float4(acc[4 * j4], acc[4 * j4 + 1], acc[4 * j4 + 2], acc[4 * j4 + 3]);
+            reinterpret_cast<float4*>(dst)[j4] = make_float4(acc[2 * j4].x, acc[2 * j4].y, acc[2 * j4 + 1].x, acc[2 * j4 + 1].y);
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (col0 + j < N) dst[j] = acc[j];
+          for (int j = 0; j < 16; ++j) {
+            if (col0 + 2 * j < N) dst[2 * j] = acc[j].x;
+            if (col0 + 2 * j + 1 < N) dst[2 * j + 1] = acc[j].y;
           }
         }
       }

@@ -248,24 +248,56 @@ def run_native_arm(args) -> None:
         step()
     kernels.check_status(dev)
 
-    events = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(args.steps)]
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
+    # timed region: exactly `steps` steps between two events, barrier + synchronize on both sides
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t_begin.record(stream)
+    for _ in range(args.steps):
+        step()
+    t_end.record(stream)
+    barrier()
+    total_ms = t_begin.elapsed_time(t_end)
+    # breakdown pass: the same steps again with an event between consecutive kernels
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(args.steps)]
     for i in range(args.steps):
         step(events[i])
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     kernels.check_status(dev)
-    total_ms = events[0][0].elapsed_time(events[-1][5])
     if distributed:
         t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
     value = world * len(VARIANTS) * FLOP_PER_VARIANT / (ms_per_step * 1e-3) / 1e12
+
+    # conversion kernels are a few microseconds long: also time them as the reference's protocol
+    # does, as batches of back-to-back launches, rotating over buffers so that L2 does not serve them
+    def batched(fn, reps=50):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn(0)
+        e0.record(stream)
+        for i in range(reps):
+            fn(i)
+        e1.record(stream)
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / reps
+
+    n_rot = 6  # 6 x (16 MiB in + 32 MiB out) > L2
+    a_rot = [a_int8.clone() for _ in range(n_rot)]
+    a16_rot = [torch.empty_like(a16) for _ in range(n_rot)]
+    codes_rot = [torch.empty_like(codes) for _ in range(n_rot)]
+    batched_ms = {
+        "o0_int8_to_fp16": batched(lambda i: check(lib.adg_int8_to_fp16(
+            a_rot[i % n_rot].data_ptr(), a_scale.data_ptr(), a16_rot[i % n_rot].data_ptr(), M, K, sp))),
+        "o2_quantize": batched(lambda i: check(lib.adg_o2_quantize_activation(
+            a_rot[i % n_rot].data_ptr(), a_scale.data_ptr(), codes_rot[i % n_rot].data_ptr(), None, sfa.data_ptr(), M, K, sp))),
+    }
+    del a_rot, a16_rot, codes_rot
 
     # per-kernel durations from the events recorded inside the timed steps
     kernel_ms = {name: statistics.fmean(events[i][j].elapsed_time(events[i][j + 1]) for i in range(args.steps))
@@ -284,8 +316,11 @@ def run_native_arm(args) -> None:
     for name, ms in kernel_ms.items():
         if name in conv_bytes:
             ach = conv_bytes[name] / (ms * 1e-3) / 1e9
+            bms = batched_ms[name]
+            bach = conv_bytes[name] / (bms * 1e-3) / 1e9
             kernels_out[name] = {"ms": ms, "bound": "hbm", "achieved": ach, "unit": "GB/s", "peak": peaks["hbm_gbs"],
-                                 "frac": ach / peaks["hbm_gbs"], "algorithmic_bytes": conv_bytes[name]}
+                                 "frac": ach / peaks["hbm_gbs"], "algorithmic_bytes": conv_bytes[name],
+                                 "batched_ms": bms, "batched_achieved": bach, "batched_frac": bach / peaks["hbm_gbs"]}
         else:
             v = gemm_variant[name]
             ach = FLOP_PER_VARIANT / (ms * 1e-3) / 1e12
@@ -354,6 +389,8 @@ def run_native_arm(args) -> None:
         "e2e": e2e,
         "cpu_baseline": cpu,
         "gpu_launches": 5 * args.steps,
+        "timing": "value: two CUDA events around all steps; kernels: a second pass with an event between kernels "
+                  "(adds about a microsecond per boundary); batched_*: 50 back-to-back launches over rotating buffers",
     }
     print(json.dumps(line))
     if distributed:
