@@ -77,6 +77,42 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of one mbarrier phase.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Variants taking 32-bit shared-memory addresses (cheaper to keep live than generic pointers).
+__device__ __forceinline__ void mbar_arrive_a(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test_wait_a(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void umma_commit_a(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 struct WaitEnv {
   uint32_t* status;          // global status words
   volatile uint32_t* abort;  // CTA-wide abort flag in shared memory
@@ -84,11 +120,11 @@ struct WaitEnv {
 
 // Bounded wait on one mbarrier phase.  Returns false when the CTA is aborting.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitEnv& env, uint32_t tag) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_test_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3Fu) == 0) {
+  while (!mbar_test_wait(bar, parity)) {
+    if ((++spins & 0x3FFu) == 0) {
       if (*env.abort) return false;
       if (global_timer_ns() - t0 > kWaitTimeoutNs) {
         *env.abort = 1;
@@ -96,6 +132,43 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
           env.status[1] = tag;
           env.status[2] = blockIdx.x;
           env.status[3] = parity;
+        }
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// ---- register re-balancing between warp groups ---------------------------------------------------
+// Executed by all four warps of a warp group (warps 4i..4i+3).  Roles that only issue copies or
+// MMAs give registers back so that the arithmetic warps can hold more data in flight.
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// Bounded wait, 32-bit-address form: `abort_addr` is the shared-memory address of the abort flag.
+__device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity, uint32_t* status, uint32_t abort_addr,
+                                            uint32_t tag) {
+  if (mbar_test_wait_a(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_test_wait_a(bar, parity)) {
+    if ((++spins & 0x3FFu) == 0) {
+      uint32_t aborted;
+      asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(aborted) : "r"(abort_addr) : "memory");
+      if (aborted) return false;
+      if (global_timer_ns() - t0 > kWaitTimeoutNs) {
+        asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_addr), "r"(1u) : "memory");
+        if (atomicCAS(status, 0u, static_cast<uint32_t>(kStatusWaitTimeout)) == 0u) {
+          status[1] = tag;
+          status[2] = blockIdx.x;
+          status[3] = parity;
         }
         return false;
       }

@@ -39,7 +39,7 @@ template <int KIND, int BLOCK_N>
 struct AccCfg {
   static constexpr bool kScaled = KIND == 2;
   static constexpr int kStages = BLOCK_N == 256 ? 4 : 6;
-  static constexpr int kElemsPerStage = kScaled ? 256 : 64;  // K elements covered by 128 bytes
+  static constexpr int kElemsPerStage = KIND == 2 ? 256 : (KIND == 1 ? 128 : 64);  // K elements covered by 128 bytes
   static constexpr int kTileA = kBlockM * 128;
   static constexpr int kTileB = BLOCK_N * 128;
   static constexpr int kSfa = kScaled ? 1024 : 0;                    // two 512-byte atoms (8 K32 blocks)
@@ -201,10 +201,18 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         sfa_t + (ks >> 1) * 4, sfb_t + (ks >> 1) * (BLOCK_N / 32));
             }
           } else {
-            constexpr uint32_t idesc = make_idesc(1, kFmtF16, kFmtF16, kBlockM, BLOCK_N);
+            if constexpr (KIND == 1) {
+              constexpr uint32_t idesc = make_idesc(2, kFmtS8, kFmtS8, kBlockM, BLOCK_N);
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              umma_f16(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
+              for (int ks = 0; ks < 4; ++ks) {
+                umma_i8(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
+              }
+            } else {
+              constexpr uint32_t idesc = make_idesc(1, kFmtF16, kFmtF16, kBlockM, BLOCK_N);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks) {
+                umma_f16(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
+              }
             }
           }
           umma_commit(&empty_bar[stage]);  // the stage may be refilled once these MMAs have read it
@@ -308,6 +316,7 @@ int launch(const GemmPlan& p, cudaStream_t stream) {
 int init_gemm_acc_attributes() {
   if (int rc = set_attr<0, 256>()) return rc;
   if (int rc = set_attr<0, 128>()) return rc;
+  if (int rc = set_attr<1, 256>()) return rc;
   if (int rc = set_attr<2, 256>()) return rc;
   if (int rc = set_attr<2, 128>()) return rc;
   return 0;
@@ -316,6 +325,7 @@ int init_gemm_acc_attributes() {
 int run_gemm_acc(const GemmPlan& p, cudaStream_t stream) {
   if (p.variant == 0) return p.block_n == 256 ? launch<0, 256>(p, stream) : launch<0, 128>(p, stream);
   if (p.variant == 2) return p.block_n == 256 ? launch<2, 256>(p, stream) : launch<2, 128>(p, stream);
+  if (p.variant == 3) return launch<1, 256>(p, stream);  // probe: plain INT8 GEMM, INT32 accumulator bits written as-is
   return fail("run_gemm_acc: plan is not an O0/O2 plan");
 }
 

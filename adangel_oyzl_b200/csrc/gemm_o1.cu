@@ -5,15 +5,20 @@
 //     P   = sum_{k in g} A_int8[m,k] * W_int8[n,k]                      (INT32, exact)
 //     acc = acc + float(P) * ((A_scale[m] * 2**(W_scale[n,g]-127)) * 0.5)  (FP32, round-to-nearest each step)
 // One tcgen05.mma kind::i8 instruction has K = 32, i.e. it computes exactly one group's partial
-// for a 128x128 tile.  The partial is written to one of four 128-column tensor-memory slots and
-// drained by the epilogue warps, which keep the FP32 accumulators in registers for the whole K
+// for a 128x128 tile.  Partials are produced two at a time (two MMAs, one commit) into one of two
+// 256-column halves of tensor memory, because an MMA into a fresh accumulator followed by its own
+// commit costs about a thousand cycles of latency that only back-to-back MMAs amortise.  The
+// epilogue warps drain the partials and keep the FP32 accumulators in registers for the whole K
 // loop:  u = RN(float(P) * A_scale[m]);  acc = fma(u, 2**(W_scale-128), acc).  The factor
 // 2**(W_scale-128) is a power of two, so u * 2**(W_scale-128) is exact and the fused form rounds
 // exactly where the reference's multiply-then-add does (barring FP32 underflow of the scale).
 //
 // Roles (640 threads): warp 0 TMA producer, warp 1 MMA issuer + tensor-memory owner, warp 2 turns
 // the tile's UE8M0 weight scales into FP32 factors in a shared-memory ring, warps 4-19 epilogue
-// (4 per tensor-memory lane quarter, 32 columns each).
+// (4 per tensor-memory lane quarter, 32 columns each).  The first warp group hands registers to the
+// epilogue warp groups so that each epilogue warp can keep the next partial's tensor-memory load in
+// flight while it scales and accumulates the current one (a tensor-memory load takes several
+// hundred cycles to return).
 #include "codecs.cuh"
 #include "common.cuh"
 #include "launch.h"
@@ -26,7 +31,7 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
 constexpr int kStages = 6;      // 32 KB each: A 128x128 B + W 128x128 B (4 groups)
 constexpr int kScStages = 8;    // 2 KB each: 4 groups x 128 FP32 factors
-constexpr int kSlots = 4;       // tensor-memory partial slots of 128 columns
+constexpr int kPairs = 2;       // tensor-memory halves, each holding the partials of two K32 groups
 constexpr int kEpiWarps = 16;
 constexpr int kFirstEpiWarp = 4;
 constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
@@ -60,6 +65,9 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) 
   return t;
 }
 
+// kDump = true adds the debug store of every INT32 partial (a separate instantiation so that the
+// production kernel carries none of its register pressure).
+template <bool kDump>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const float* __restrict__ a_scale, const uint8_t* __restrict__ w_scale, float* __restrict__ y,
@@ -71,15 +79,18 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full_bar = empty_bar + kStages;
-  uint64_t* tmem_empty_bar = tmem_full_bar + kSlots;
-  uint64_t* sc_full_bar = tmem_empty_bar + kSlots;
+  uint64_t* tmem_empty_bar = tmem_full_bar + kPairs;
+  uint64_t* sc_full_bar = tmem_empty_bar + kPairs;
   uint64_t* sc_empty_bar = sc_full_bar + kScStages;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sc_empty_bar + kScStages);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const WaitEnv env{status, abort_flag};
+  const uint32_t abort_a = smem_u32(const_cast<uint32_t*>(abort_flag));
+  const uint32_t tmem_full_a = smem_u32(tmem_full_bar), tmem_empty_a = smem_u32(tmem_empty_bar);
+  const uint32_t sc_full_a = smem_u32(sc_full_bar), sc_empty_a = smem_u32(sc_empty_bar);
+  const uint32_t full_a = smem_u32(full_bar), empty_a = smem_u32(empty_bar);
 
   const int num_m = (M + kBlockM - 1) / kBlockM;
   const int num_n = (N + kBlockN - 1) / kBlockN;
@@ -92,7 +103,7 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    for (int s = 0; s < kSlots; ++s) {
+    for (int s = 0; s < kPairs; ++s) {
       mbar_init(&tmem_full_bar[s], 1);
       mbar_init(&tmem_empty_bar[s], kEpiWarps);
     }
@@ -116,6 +127,8 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
+  if (warp < kFirstEpiWarp) {
+  reg_dealloc<32>();  // 128 threads x 64 registers returned = 512 threads x 16 registers gained below
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------------------
     if (lane == 0) {
@@ -125,7 +138,7 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         const TileCoord tc = tile_coord(tile, num_m, num_n);
         for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage);
+          ok = mbar_wait_a(empty_a + stage * 8, phase ^ 1u, status, abort_a, kTagEmpty | stage);
           if (!ok) break;
           uint8_t* st = smem + stage * kStageBytes;
           mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
@@ -141,31 +154,33 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -----------------------------------------------
     if (lane == 0) {
-      int stage = 0, slot = 0;
-      uint32_t phase = 0, slot_phase = 0;
+      int stage = 0, pair = 0;
+      uint32_t phase = 0, pair_phase = 0;
       bool ok = true;
       constexpr uint32_t idesc = make_idesc(2, kFmtS8, kFmtS8, kBlockM, kBlockN);
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         for (int kb = 0; ok && kb < num_kb; ++kb) {
-          ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | stage);
+          ok = mbar_wait_a(full_a + stage * 8, phase, status, abort_a, kTagFull | stage);
           if (!ok) break;
           tc_fence_after();
           const uint32_t st = smem_u32(smem + stage * kStageBytes);
           const uint64_t adesc = make_desc_sw128(st);
           const uint64_t bdesc = make_desc_sw128(st + kTile);
-          const int ng = min(4, groups - kb * 4);
-          for (int g = 0; g < ng; ++g) {
-            ok = mbar_wait(&tmem_empty_bar[slot], slot_phase ^ 1u, env, kTagTmemEmpty | slot);
+          const int ng = min(4, groups - kb * 4);  // K is a multiple of 64, so ng is 2 or 4
+          for (int g = 0; g < ng; g += 2) {
+            ok = mbar_wait_a(tmem_empty_a + pair * 8, pair_phase ^ 1u, status, abort_a, kTagTmemEmpty | pair);
             if (!ok) break;
             tc_fence_after();
-            umma_i8(tmem_base + static_cast<uint32_t>(slot * kBlockN), adesc + g * 2, bdesc + g * 2, idesc, 0u);
-            umma_commit(&tmem_full_bar[slot]);
-            if (++slot == kSlots) {
-              slot = 0;
-              slot_phase ^= 1u;
+            const uint32_t d = tmem_base + static_cast<uint32_t>(pair * 2 * kBlockN);
+            umma_i8(d, adesc + g * 2, bdesc + g * 2, idesc, 0u);
+            umma_i8(d + kBlockN, adesc + (g + 1) * 2, bdesc + (g + 1) * 2, idesc, 0u);
+            umma_commit_a(tmem_full_a + pair * 8);
+            if (++pair == kPairs) {
+              pair = 0;
+              pair_phase ^= 1u;
             }
           }
-          if (ok) umma_commit(&empty_bar[stage]);
+          if (ok) umma_commit_a(empty_a + stage * 8);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -182,10 +197,10 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       const TileCoord tc = tile_coord(tile, num_m, num_n);
       for (int kb = 0; kb < num_kb; ++kb) {
-        ok = mbar_wait(&sc_empty_bar[scs], sc_phase ^ 1u, env, kTagScEmpty | scs);
+        ok = mbar_wait_a(sc_empty_a + scs * 8, sc_phase ^ 1u, status, abort_a, kTagScEmpty | scs);
         if (!ok) break;
         float* dst = sc_ring + scs * (kScBytes / 4);
-#pragma unroll
+#pragma unroll 1
         for (int i = 0; i < 4; ++i) {
           const int n_local = lane + 32 * i;
           const int n = tc.n_blk * kBlockN + n_local;
@@ -211,24 +226,39 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             dst[g * kBlockN + n_local] = ((valid >> g) & 1u) ? ue8m0_half_to_float((codes >> (8 * g)) & 0xFFu) : 0.0f;
           }
         }
-        mbar_arrive(&sc_full_bar[scs]);
+        mbar_arrive_a(sc_full_a + scs * 8);
         if (++scs == kScStages) {
           scs = 0;
           sc_phase ^= 1u;
         }
       }
     }
-  } else if (warp >= kFirstEpiWarp) {
+  }
+  } else {
+    reg_alloc<112>();
     // ------------------------------- epilogue ---------------------------------------------------
-    // Each warp owns 32 columns of one lane quarter.  A partial is fetched in two 16-column halves
-    // into two register buffers so that the tensor-memory load of the next half is in flight while
-    // the current half is scaled and accumulated.
+    // Each warp owns 32 columns of one lane quarter.  The two partials of a pair go to two register
+    // buffers: while one partial is scaled and accumulated, the load of the next is in flight.
     const int q = warp & 3;                     // tensor-memory lane quarter
     const int cs = (warp - kFirstEpiWarp) >> 2;  // 32-column slice of the 128-column partial
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(cs * 32);
-    int slot = 0, scs = 0;
-    uint32_t slot_phase = 0, sc_phase = 0;
+    const uint32_t sc_base = smem_u32(sc_ring) + static_cast<uint32_t>(cs * 32 * 4);
+    int pair = 0, scs = 0;
+    uint32_t pair_phase = 0, sc_phase = 0;
     bool ok = true;
+
+    auto accumulate = [&](const uint32_t (&p)[32], float2 (&acc)[16], const float2 a2, const uint32_t sc) {
+#pragma unroll
+      for (int j4 = 0; j4 < 8; ++j4) {
+        float4 s;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(s.x), "=f"(s.y), "=f"(s.z), "=f"(s.w) : "r"(sc + j4 * 16));
+        const float2 f0 = make_float2(__int2float_rn(static_cast<int>(p[4 * j4])), __int2float_rn(static_cast<int>(p[4 * j4 + 1])));
+        const float2 f1 = make_float2(__int2float_rn(static_cast<int>(p[4 * j4 + 2])), __int2float_rn(static_cast<int>(p[4 * j4 + 3])));
+        acc[2 * j4] = __ffma2_rn(__fmul2_rn(f0, a2), make_float2(s.x, s.y), acc[2 * j4]);
+        acc[2 * j4 + 1] = __ffma2_rn(__fmul2_rn(f1, a2), make_float2(s.z, s.w), acc[2 * j4 + 1]);
+      }
+    };
+
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       const TileCoord tc = tile_coord(tile, num_m, num_n);
       const int row = tc.m_blk * kBlockM + q * 32 + lane;
@@ -238,71 +268,56 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       float2 acc[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) acc[j] = make_float2(0.0f, 0.0f);
-      uint32_t lo[16], hi[16];
-      // prologue: both halves of the tile's first partial
-      ok = mbar_wait(&tmem_full_bar[slot], slot_phase, env, kTagTmemFull | slot);
+      uint32_t pa[32], pb[32];
+      // prologue: the first partial of the tile's first pair
+      ok = mbar_wait_a(tmem_full_a + pair * 8, pair_phase, status, abort_a, kTagTmemFull | pair);
       if (!ok) break;
       tc_fence_after();
-      tmem_ld_32x16(t_lane + slot * kBlockN, lo);
-      tmem_ld_32x16(t_lane + slot * kBlockN + 16, hi);
-      tmem_wait_ld_for(lo);
-      for (int g = 0; ok && g < groups; ++g) {
+      tmem_ld_32x32(t_lane + pair * 2 * kBlockN, pa);
+      for (int g = 0; ok && g < groups; g += 2) {  // K is a multiple of 64: groups come in pairs
         if ((g & 3) == 0) {
-          ok = mbar_wait(&sc_full_bar[scs], sc_phase, env, kTagScFull | scs);
+          ok = mbar_wait_a(sc_full_a + scs * 8, sc_phase, status, abort_a, kTagScFull | scs);
           if (!ok) break;
         }
-        const float4* sc = reinterpret_cast<const float4*>(sc_ring + scs * (kScBytes / 4) + (g & 3) * kBlockN + cs * 32);
-        if (partial_dump != nullptr) {  // warp-uniform: the wait below is a warp-wide instruction
-          tmem_wait_ld_for(hi);
+        const uint32_t sc = sc_base + static_cast<uint32_t>(scs * kScBytes + ((g & 3) * kBlockN) * 4);
+        // ---- first partial of the pair: wait for it, start loading the second, compute
+        tmem_wait_ld_for(pa);
+        tmem_ld_32x32(t_lane + (pair * 2 + 1) * kBlockN, pb);
+        if constexpr (kDump) {
+          if (row < M) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            if (row >= M) break;
-            if (col0 + j < N) partial_dump[(static_cast<long>(row) * N + col0 + j) * groups + g] = static_cast<int>(lo[j]);
-            if (col0 + 16 + j < N)
-              partial_dump[(static_cast<long>(row) * N + col0 + 16 + j) * groups + g] = static_cast<int>(hi[j]);
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < N) partial_dump[(static_cast<long>(row) * N + col0 + j) * groups + g] = static_cast<int>(pa[j]);
           }
         }
-        // ---- first half: columns 0..15 of this warp's slice
-#pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          const float4 s = sc[j4];
-          const float2 f0 = make_float2(__int2float_rn(static_cast<int>(lo[4 * j4])), __int2float_rn(static_cast<int>(lo[4 * j4 + 1])));
-          const float2 f1 = make_float2(__int2float_rn(static_cast<int>(lo[4 * j4 + 2])), __int2float_rn(static_cast<int>(lo[4 * j4 + 3])));
-          acc[2 * j4] = __ffma2_rn(__fmul2_rn(f0, a2), make_float2(s.x, s.y), acc[2 * j4]);
-          acc[2 * j4 + 1] = __ffma2_rn(__fmul2_rn(f1, a2), make_float2(s.z, s.w), acc[2 * j4 + 1]);
-        }
-        // the second half has arrived: the slot is fully read and can take a new partial
-        tmem_wait_ld_for(hi);
+        accumulate(pa, acc, a2, sc);
+        // ---- second partial: wait for it, hand the pair back, start loading the next pair's first
+        tmem_wait_ld_for(pb);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty_bar[slot]);
-        if (++slot == kSlots) {
-          slot = 0;
-          slot_phase ^= 1u;
+        if (lane == 0) mbar_arrive_a(tmem_empty_a + pair * 8);
+        if (++pair == kPairs) {
+          pair = 0;
+          pair_phase ^= 1u;
         }
-        const bool more = g + 1 < groups;
+        const bool more = g + 2 < groups;
         if (more) {
-          ok = mbar_wait(&tmem_full_bar[slot], slot_phase, env, kTagTmemFull | slot);
+          ok = mbar_wait_a(tmem_full_a + pair * 8, pair_phase, status, abort_a, kTagTmemFull | pair);
           if (!ok) break;
           tc_fence_after();
-          tmem_ld_32x16(t_lane + slot * kBlockN, lo);  // in flight during the second half's arithmetic
+          tmem_ld_32x32(t_lane + pair * 2 * kBlockN, pa);
         }
-        // ---- second half: columns 16..31
+        if constexpr (kDump) {
+          if (row < M) {
 #pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          const float4 s = sc[4 + j4];
-          const float2 f0 = make_float2(__int2float_rn(static_cast<int>(hi[4 * j4])), __int2float_rn(static_cast<int>(hi[4 * j4 + 1])));
-          const float2 f1 = make_float2(__int2float_rn(static_cast<int>(hi[4 * j4 + 2])), __int2float_rn(static_cast<int>(hi[4 * j4 + 3])));
-          acc[8 + 2 * j4] = __ffma2_rn(__fmul2_rn(f0, a2), make_float2(s.x, s.y), acc[8 + 2 * j4]);
-          acc[8 + 2 * j4 + 1] = __ffma2_rn(__fmul2_rn(f1, a2), make_float2(s.z, s.w), acc[8 + 2 * j4 + 1]);
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < N) partial_dump[(static_cast<long>(row) * N + col0 + j) * groups + g + 1] = static_cast<int>(pb[j]);
+          }
         }
-        if (more) {
-          tmem_wait_ld_for(lo);
-          tmem_ld_32x16(t_lane + slot * kBlockN + 16, hi);  // in flight during the next first half
-        }
-        if ((g & 3) == 3 || !more) {
+        accumulate(pb, acc, a2, sc + kBlockN * 4);
+        if ((g & 3) == 2 || !more) {
           __syncwarp();
-          if (lane == 0) mbar_arrive(&sc_empty_bar[scs]);
+          if (lane == 0) mbar_arrive_a(sc_empty_a + scs * 8);
           if (++scs == kScStages) {
             scs = 0;
             sc_phase ^= 1u;
@@ -336,16 +351,26 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 }  // namespace
 
 int init_gemm_o1_attributes() {
+  if (int rc = check_cuda(
+          cudaFuncSetAttribute(gemm_o1_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+          "cudaFuncSetAttribute(gemm_o1_kernel)"))
+    return rc;
   return check_cuda(
-      cudaFuncSetAttribute(gemm_o1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
-      "cudaFuncSetAttribute(gemm_o1_kernel)");
+      cudaFuncSetAttribute(gemm_o1_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+      "cudaFuncSetAttribute(gemm_o1_kernel<dump>)");
 }
 
 int run_gemm_o1(const GemmPlan& p, cudaStream_t stream) {
   if (p.variant != 1) return fail("run_gemm_o1: plan is not an O1 plan");
-  gemm_o1_kernel<<<p.grid, kThreads, kSmemBytes, stream>>>(
-      p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y,
-      p.partial_dump, p.M, p.N, p.K, p.ldy, p.status);
+  if (p.partial_dump != nullptr) {
+    gemm_o1_kernel<true><<<p.grid, kThreads, kSmemBytes, stream>>>(
+        p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y,
+        p.partial_dump, p.M, p.N, p.K, p.ldy, p.status);
+  } else {
+    gemm_o1_kernel<false><<<p.grid, kThreads, kSmemBytes, stream>>>(
+        p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y, nullptr,
+        p.M, p.N, p.K, p.ldy, p.status);
+  }
   return check_cuda(cudaGetLastError(), "gemm_o1_kernel launch");
 }
 
