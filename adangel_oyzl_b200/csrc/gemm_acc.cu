@@ -10,6 +10,9 @@
 //               scale-factor atoms, into a multi-stage shared-memory ring guarded by mbarriers
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (and, for O2, the shared ->
 //               tensor-memory scale-factor copies) and commits completion to the mbarriers
+//   warp 10     (O2) one lane copies each stage's scale-factor atoms from shared to tensor memory
+//               (tcgen05.cp) and commits to a per-stage mbarrier, so that the MMA lane, whose
+//               instruction issue is the scarce resource, issues nothing but MMAs
 //   warps 2-9   epilogue: two warps per 32-lane quarter of tensor memory, each draining half of the
 //               accumulator's columns into registers in one go (so the accumulator is released
 //               after a few hundred cycles), then writing 32x16 blocks through swizzled
@@ -24,7 +27,8 @@ namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kEpiWarps = 8;
-constexpr int kAccThreads = (2 + kEpiWarps) * 32;
+constexpr int kSfWarp = 2 + kEpiWarps;  // copies scale factors into tensor memory (O2 only)
+constexpr int kAccThreads = (2 + kEpiWarps + 2) * 32;
 constexpr int kStagingPerWarp = 2048;  // one 32-row x 16-column FP32 block
 constexpr int kGroupM = 8;  // tile rasterisation: sweep 8 row-blocks before moving to the next column-block
 
@@ -33,6 +37,7 @@ enum : uint32_t {  // wait tags reported on timeout
   kTagFull = 0x200,
   kTagTmemEmpty = 0x300,
   kTagTmemFull = 0x400,
+  kTagSfFull = 0x500,
 };
 
 template <int KIND, int BLOCK_N>
@@ -87,7 +92,8 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
   uint64_t* empty_bar = bars + Cfg::kStages;
   uint64_t* tmem_full_bar = bars + 2 * Cfg::kStages;
   uint64_t* tmem_empty_bar = tmem_full_bar + Cfg::kAccStages;
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + Cfg::kAccStages);
+  uint64_t* sf_full_bar = tmem_empty_bar + Cfg::kAccStages;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sf_full_bar + Cfg::kStages);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -104,6 +110,7 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     for (int s = 0; s < Cfg::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
+      mbar_init(&sf_full_bar[s], 1);
     }
     for (int a = 0; a < Cfg::kAccStages; ++a) {
       mbar_init(&tmem_full_bar[a], 1);
@@ -181,18 +188,11 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
           const uint64_t adesc = make_desc_sw128(st);
           const uint64_t bdesc = make_desc_sw128(st + Cfg::kTileA);
           if constexpr (Cfg::kScaled) {
-            const uint32_t sfa_s = st + Cfg::kTileA + Cfg::kTileB;
-            const uint32_t sfb_s = sfa_s + Cfg::kSfa;
+            ok = mbar_wait(&sf_full_bar[stage], phase, env, kTagSfFull | stage);
+            if (!ok) break;
+            tc_fence_after();
             const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
             const uint32_t sfb_t = sfa_t + 8;
-#pragma unroll
-            for (int ka = 0; ka < 2; ++ka) {
-              tmem_cp_32x128b_warpx4(sfa_t + ka * 4, make_desc_sf(sfa_s + ka * 512));
-#pragma unroll
-              for (int rb = 0; rb < BLOCK_N / 128; ++rb) {
-                tmem_cp_32x128b_warpx4(sfb_t + ka * (BLOCK_N / 32) + rb * 4, make_desc_sf(sfb_s + rb * 1024 + ka * 512));
-              }
-            }
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
               const uint32_t sf_id = (ks & 1) * 2;
@@ -224,7 +224,43 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         if (ok) umma_commit(&tmem_full_bar[acc]);
       }
     }
-  } else {
+  } else if (warp == kSfWarp) {
+    // ------------------------------- scale-factor copier (O2) -----------------------------------
+    if constexpr (Cfg::kScaled) {
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            // the stage's data has landed; its tensor-memory scale columns were last read by MMAs
+            // that completed before the stage was handed back to the producer
+            ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | 0x80 | stage);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
+            const uint32_t sfa_s = st + Cfg::kTileA + Cfg::kTileB;
+            const uint32_t sfb_s = sfa_s + Cfg::kSfa;
+            const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
+            const uint32_t sfb_t = sfa_t + 8;
+#pragma unroll
+            for (int ka = 0; ka < 2; ++ka) {
+              tmem_cp_32x128b_warpx4(sfa_t + ka * 4, make_desc_sf(sfa_s + ka * 512));
+#pragma unroll
+              for (int rb = 0; rb < BLOCK_N / 128; ++rb) {
+                tmem_cp_32x128b_warpx4(sfb_t + ka * (BLOCK_N / 32) + rb * 4, make_desc_sf(sfb_s + rb * 1024 + ka * 512));
+              }
+            }
+            umma_commit(&sf_full_bar[stage]);
+            if (++stage == Cfg::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp >= 2 && warp < 2 + kEpiWarps) {
     // ------------------------------- epilogue ---------------------------------------------------
     const int q = warp & 3;         // the 32-lane quarter of tensor memory this warp can read
     const int h = (warp - 2) >> 2;  // which half of the accumulator's columns this warp drains
