@@ -144,17 +144,6 @@ int adg_gemm_o1(const void* a_int8, const void* a_scale, const void* w_int8, con
   return run_plan(plan, as_stream(stream));
 }
 
-// probe (not part of the ABI header): plain INT8 GEMM through the accumulating kernel
-int adg_probe_gemm_i8(const void* a_int8, const void* w_int8, float* y, int M, int N, int K, void* stream) {
-  GemmPlan plan;
-  if (int rc = plan_o0(&plan, a_int8, w_int8, y, M, N, K / 2, N)) return rc;  // borrow the output map
-  plan.variant = 3;
-  plan.K = K;
-  if (int rc = encode_tensor_map_2d(&plan.tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_int8, M, K, K, 128, 128)) return rc;
-  if (int rc = encode_tensor_map_2d(&plan.tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_int8, N, K, K, 256, 128)) return rc;
-  return run_plan(plan, as_stream(stream));
-}
-
 int adg_gemm_o2(const void* a_mxfp4, const void* a_sf_tiled, const void* w_mxfp4, const void* w_sf_tiled, float* y,
                 int M, int N, int K, int ldy, void* stream) {
   GemmPlan plan;

@@ -352,7 +352,6 @@ int launch(const GemmPlan& p, cudaStream_t stream) {
 int init_gemm_acc_attributes() {
   if (int rc = set_attr<0, 256>()) return rc;
   if (int rc = set_attr<0, 128>()) return rc;
-  if (int rc = set_attr<1, 256>()) return rc;
   if (int rc = set_attr<2, 256>()) return rc;
   if (int rc = set_attr<2, 128>()) return rc;
   return 0;
@@ -361,7 +360,6 @@ int init_gemm_acc_attributes() {
 int run_gemm_acc(const GemmPlan& p, cudaStream_t stream) {
   if (p.variant == 0) return p.block_n == 256 ? launch<0, 256>(p, stream) : launch<0, 128>(p, stream);
   if (p.variant == 2) return p.block_n == 256 ? launch<2, 256>(p, stream) : launch<2, 128>(p, stream);
-  if (p.variant == 3) return launch<1, 256>(p, stream);  // probe: plain INT8 GEMM, INT32 accumulator bits written as-is
   return fail("run_gemm_acc: plan is not an O0/O2 plan");
 }
 
