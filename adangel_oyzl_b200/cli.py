@@ -1,4 +1,4 @@
-"""Command-line entry point: ``python -m adangel_oyzl_b200 {doctor,verify-layout,show-config}``.
+"""Command-line entry point: ``python -m adangel_oyzl_b200 {doctor,verify-layout,show-config,run,analyze}``.
 
 Mirrors the reference CLI (``python/adangel/cli.py:12-18,46-53,56-91``) for the commands that belong
 to the native hot path.
@@ -38,6 +38,19 @@ def _show_config(args) -> None:
     print(yaml.safe_dump(config, sort_keys=False))
 
 
+def _run(args) -> None:
+    from .benchmark.runner import run_experiment
+
+    print(run_experiment(args.config, args.output, sample_limit=args.samples, warmup_override=args.warmup,
+                         repeats_override=args.repeats))
+
+
+def _analyze(args) -> None:
+    from .analysis import generate_report
+
+    print(generate_report(args.run, args.output, allow_unstable=args.allow_unstable))
+
+
 def build_parser() -> argparse.ArgumentParser:
     parser = argparse.ArgumentParser(prog="adangel_oyzl_b200")
     commands = parser.add_subparsers(dest="command", required=True)
@@ -53,6 +66,20 @@ def build_parser() -> argparse.ArgumentParser:
     show = commands.add_parser("show-config", help="parse and print a YAML config")
     show.add_argument("--config", required=True)
     show.set_defaults(func=_show_config)
+    run = commands.add_parser("run", help="run the interleaved O0/O1/O2 experiment on synthetic samples")
+    run.add_argument("--config", required=True)
+    run.add_argument("--output", required=True)
+    run.add_argument("--samples", type=int)
+    run.add_argument("--warmup", type=int)
+    run.add_argument("--repeats", type=int)
+    run.add_argument("--require-native", action="store_true", help="kept for explicit scripts; a run always requires native")
+    run.set_defaults(func=_run)
+
+    analyze = commands.add_parser("analyze", help="generate the four tables of a finished run")
+    analyze.add_argument("--run", required=True)
+    analyze.add_argument("--output", required=True)
+    analyze.add_argument("--allow-unstable", action="store_true", help="include records that failed the CV gate")
+    analyze.set_defaults(func=_analyze)
     return parser
 
 

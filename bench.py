@@ -39,6 +39,12 @@ VARIANTS = ("o0", "o1", "o2")
 FLOP_PER_VARIANT = 2.0 * M * N_PER_GPU * K
 L2_BYTES = 126 * 1024 * 1024
 NOMINAL_TFLOPS = {"o0": 2250.0, "o1": 4500.0, "o2": 9000.0}  # dense FP16 / INT8 / FP4
+# dram__bytes_read.sum + dram__bytes_write.sum per launch at 4096^3 from the ncu capture summarised in
+# profiles/bench_step_kernels_full_4096.md (the 126 MB L2 keeps most of the 64 MiB output on chip)
+NCU_DRAM_TRAFFIC_BYTES = {"o0_int8_to_fp16": 16.8e6, "o0_gemm_f16": 120.7e6, "o1_gemm_i8": 51.4e6,
+                          "o2_quantize": 16.8e6, "o2_gemm_mxf4": 33.0e6}
+# every INT32 K32 partial of O1 crosses the tensor-memory read port (128 B/clk/SM measured):
+TMEM_READ_BYTES_PER_CLK = 128.0
 
 
 def measured_peaks():
@@ -330,9 +336,15 @@ def run_native_arm(args) -> None:
     dominant = max(kernel_ms, key=kernel_ms.get)
     d = kernels_out[dominant]
     roofline = {"kernel": dominant, "bound": d["bound"], "achieved": d["achieved"], "peak": d["peak"], "unit": d["unit"],
-                "frac": d["frac"], "traffic": None,
+                "frac": d["frac"], "traffic": NCU_DRAM_TRAFFIC_BYTES.get(dominant),
                 "peak_source": f"{peaks['source']}: bf16 cuBLAS burst x{peak_mult[gemm_variant[dominant]]:g}" if d["bound"] == "tensor"
                 else f"{peaks['source']}: HBM copy"}
+
+    if dominant == "o1_gemm_i8" and clocks and clocks.get("sm_mhz"):
+        floor_s = (M * N_PER_GPU * (K // 32) * 4) / (148 * TMEM_READ_BYTES_PER_CLK * clocks["sm_mhz"] * 1e6)
+        roofline["secondary_bound"] = {
+            "what": "tensor-memory read port: every K32 INT32 partial is drained to registers (literal O1 semantics)",
+            "floor_ms": floor_s * 1e3, "frac_of_floor": floor_s * 1e3 / d["ms"]}
 
     # end to end through the host-buffer C ABI (N = 1 only): pinned A in, Y back, every variant, every step
     e2e = None
