@@ -1,0 +1,299 @@
+// O2 for decode-sized activations (M <= 64): a weight-streaming, split-K block-scaled MXFP4 GEMM.
+//
+// With so few activation rows the 128-row tile of the regular kernel would be almost empty and only
+// N/256 CTAs would stream W, so the operands are swapped: the tensor core computes
+// Y^T[n, m] = W[n, :] . A[m, :]^T with the 128 MMA rows taken from W and the MMA N extent equal to M
+// rounded up to 16.  The grid is (N/128 row blocks of W) x (K splits); K is split only when W has
+// few row blocks.  Every CTA accumulates its K slice in tensor memory; with one split it writes Y
+// directly, otherwise it writes an FP32 partial and the last CTA of a row block to finish adds the
+// partials in split order (a fixed order, so the result is reproducible) and writes Y.
+//
+// Scale factors: W's tiled scales are the MMA's A-side scales (128-row atoms as stored), A's tiled
+// scales are the B-side scales (row block 0 of A's tiled buffer).
+#include "common.cuh"
+#include "launch.h"
+
+namespace adg {
+
+namespace {
+
+constexpr int kRows = 128;      // W rows per CTA
+constexpr int kMaxM = 64;       // activation rows covered by one MMA
+constexpr int kStages = 4;
+constexpr int kTileW = kRows * 128;
+constexpr int kTileA = kMaxM * 128;
+constexpr int kSf = 1024;       // two 512-byte atoms (8 K32 blocks) for each side
+constexpr int kStageBytes = kTileW + kTileA + 2 * kSf;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
+constexpr int kThreads = 192;   // warp 0 producer, warp 1 MMA, warps 2-5 epilogue
+constexpr int kAccCols = 64;
+constexpr int kSfColBase = kAccCols;
+constexpr int kSfColsPerStage = 16;  // per K-atom: 4 (W side) + 4 (A side); two K-atoms per stage
+constexpr int kTmemCols = 128;
+constexpr int kMaxSplits = 8;    // K slices per row block of W
+
+enum : uint32_t { kTagEmpty = 0x2100, kTagFull = 0x2200, kTagAcc = 0x2300 };
+
+__global__ void __launch_bounds__(kThreads, 2)
+gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
+                      const uint8_t* __restrict__ sf_w, const uint8_t* __restrict__ sf_a, float* __restrict__ y,
+                      float* __restrict__ partials, int* __restrict__ counters, int M, int N, int K, int ldy,
+                      int kb_per_split, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* acc_bar = bars + 2 * kStages;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+  volatile uint32_t* abort_flag = tmem_base_slot + 1;
+  volatile int* is_last = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const WaitEnv env{status, abort_flag};
+  const int nb = blockIdx.x;      // 128-row block of W
+  const int split = blockIdx.y;   // K slice
+  const int splits = gridDim.y;
+  const int num_kb_total = (K + 255) / 256;
+  const int kb0 = split * kb_per_split;
+  const int kb1 = min(num_kb_total, kb0 + kb_per_split);
+  const int katoms = static_cast<int>(((K / 32 + 7) / 8) * 2);
+  const uint32_t m_pad = static_cast<uint32_t>((M + 15) / 16 * 16);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    *is_last = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_a);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage)) break;
+        uint8_t* st = smem + stage * kStageBytes;
+        mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+        tma_load_2d(st, &tm_w, &full_bar[stage], kb * 128, nb * kRows);
+        tma_load_2d(st + kTileW, &tm_a, &full_bar[stage], kb * 128, 0);
+        bulk_load(st + kTileW + kTileA, sf_w + (static_cast<long>(nb) * katoms + kb * 2) * 512, kSf, &full_bar[stage]);
+        bulk_load(st + kTileW + kTileA + kSf, sf_a + static_cast<long>(kb * 2) * 512, kSf, &full_bar[stage]);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | stage);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t st = smem_u32(smem + stage * kStageBytes);
+        const uint64_t wdesc = make_desc_sw128(st);
+        const uint64_t adesc = make_desc_sw128(st + kTileW);
+        const uint32_t sfw_t = tmem_base + kSfColBase + stage * kSfColsPerStage;  // MMA A-side scales (W)
+        const uint32_t sfa_t = sfw_t + 8;                                          // MMA B-side scales (A)
+#pragma unroll
+        for (int ka = 0; ka < 2; ++ka) {
+          tmem_cp_32x128b_warpx4(sfw_t + ka * 4, make_desc_sf(st + kTileW + kTileA + ka * 512));
+          tmem_cp_32x128b_warpx4(sfa_t + ka * 4, make_desc_sf(st + kTileW + kTileA + kSf + ka * 512));
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint32_t sf_id = (ks & 1) * 2;
+          const uint32_t idesc = make_idesc_mxf4(kRows, m_pad, sf_id, sf_id);
+          umma_mxf4(tmem_base, wdesc + ks * 2, adesc + ks * 2, idesc, (kb != kb0 || ks != 0) ? 1u : 0u,
+                    sfw_t + (ks >> 1) * 4, sfa_t + (ks >> 1) * 4);
+        }
+        umma_commit(&empty_bar[stage]);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (ok) umma_commit(acc_bar);
+    }
+  } else {
+    // epilogue: lane = one row n of W, registers = the M outputs of that row
+    const int q = warp & 3;
+    const int n = nb * kRows + q * 32 + lane;
+    bool ok = kb1 > kb0 ? mbar_wait(acc_bar, 0, env, kTagAcc) : true;
+    uint32_t r[2][32];
+    if (ok) {
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      if (kb1 > kb0) {
+        tmem_ld_32x32(t_addr, r[0]);
+        tmem_ld_32x32(t_addr + 32, r[1]);
+        tmem_wait_ld_for(r[0]);
+        tmem_wait_ld_for(r[1]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[0][j] = r[1][j] = 0u;
+      }
+      if (splits == 1) {
+        if (n < N) {
+#pragma unroll
+          for (int m = 0; m < kMaxM; ++m)
+            if (m < M) y[static_cast<long>(m) * ldy + n] = __uint_as_float(r[m >> 5][m & 31]);
+        }
+      } else {
+        if (n < N) {
+#pragma unroll
+          for (int m = 0; m < kMaxM; ++m)
+            if (m < M) partials[(static_cast<long>(split) * M + m) * N + n] = __uint_as_float(r[m >> 5][m & 31]);
+        }
+        // the last CTA of this row block to get here adds the partials in split order
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const int prev = atomicAdd(&counters[nb], 1);
+          const int last = prev == splits - 1 ? 1 : 0;
+          if (last) counters[nb] = 0;  // ready for the next launch
+          *is_last = last;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*is_last && n < N) {
+          __threadfence();
+          // four output rows at a time, all their partial loads in flight before the first add
+          for (int m0 = 0; m0 < M; m0 += 4) {
+            float v[4][kMaxSplits];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+              for (int s = 0; s < kMaxSplits; ++s) {
+                v[i][s] = (s < splits && m0 + i < M)
+                              ? __ldcg(partials + (static_cast<long>(s) * M + m0 + i) * N + n)
+                              : 0.0f;
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              if (m0 + i < M) {
+                float sum = 0.0f;
+#pragma unroll
+                for (int s = 0; s < kMaxSplits; ++s) sum += v[i][s];  // split order; absent splits add +0
+                y[static_cast<long>(m0 + i) * ldy + n] = sum;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// library-owned scratch for the split-K partials and the per-row-block arrival counters
+struct Workspace {
+  float* partials = nullptr;
+  size_t partial_bytes = 0;
+  int* counters = nullptr;
+  size_t counter_count = 0;
+};
+Workspace g_ws[64];
+
+int ensure_workspace(int device, size_t partial_bytes, size_t counter_count, Workspace** out) {
+  Workspace& ws = g_ws[device];
+  if (ws.partial_bytes < partial_bytes) {
+    if (ws.partials) cudaFree(ws.partials);
+    if (int rc = check_cuda(cudaMalloc(&ws.partials, partial_bytes), "cudaMalloc(split-K partials)")) return rc;
+    ws.partial_bytes = partial_bytes;
+  }
+  if (ws.counter_count < counter_count) {
+    if (ws.counters) cudaFree(ws.counters);
+    if (int rc = check_cuda(cudaMalloc(&ws.counters, counter_count * sizeof(int)), "cudaMalloc(counters)")) return rc;
+    if (int rc = check_cuda(cudaMemset(ws.counters, 0, counter_count * sizeof(int)), "cudaMemset(counters)")) return rc;
+    ws.counter_count = counter_count;
+  }
+  *out = &ws;
+  return 0;
+}
+
+}  // namespace
+
+int init_gemm_skinny_attributes() {
+  return check_cuda(
+      cudaFuncSetAttribute(gemm_o2_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+      "cudaFuncSetAttribute(gemm_o2_skinny_kernel)");
+}
+
+// Plan for Y[M,N] = A_mxfp4 . W_mxfp4^T with M <= 64.  The partials and counters are shared per
+// device, so launches of such plans must be ordered on one stream.
+int plan_o2_skinny(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const void* w_mxfp4, const void* sfb_tiled,
+                   float* y, int M, int N, int K, int ldy) {
+  DeviceCtx* ctx = nullptr;
+  if (int rc = device_ctx(&ctx)) return rc;
+  if (M <= 0 || M > kMaxM) return fail("plan_o2_skinny: M must be in [1, 64]");
+  *plan = GemmPlan{};
+  plan->variant = 2;
+  plan->skinny = 1;
+  plan->M = M, plan->N = N, plan->K = K, plan->ldy = ldy;
+  plan->sfa = sfa_tiled;
+  plan->sfb = sfb_tiled;
+  plan->y = y;
+  plan->status = ctx->status;
+  const uint64_t kbytes = static_cast<uint64_t>(K) / 2;
+  if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_mxfp4, N, kbytes, kbytes, kRows, 128))
+    return rc;
+  if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_mxfp4, M, kbytes, kbytes, kMaxM, 128))
+    return rc;
+  plan->tm_y = plan->tm_a;
+  const int num_nblk = (N + kRows - 1) / kRows;
+  const int num_kb = (K + 255) / 256;
+  // K is split only when W has too few row blocks to occupy a useful number of SMs: measured on
+  // B200, 32 CTAs already stream W as fast as 256 do, while the split-K hand-off (fence, arrival
+  // counter, re-reading the partials) adds several microseconds.  The partial traffic
+  // (splits * M * N * 4 bytes) is also kept below W's own bytes.
+  int splits = 32 / num_nblk;
+  const int traffic_cap = K / (16 * ((M + 15) / 16 * 16));
+  if (splits > traffic_cap) splits = traffic_cap;
+  if (splits > kMaxSplits) splits = kMaxSplits;
+  if (splits > num_kb) splits = num_kb;
+  if (splits < 1) splits = 1;
+  plan->kb_per_split = (num_kb + splits - 1) / splits;
+  plan->splits = (num_kb + plan->kb_per_split - 1) / plan->kb_per_split;
+  plan->grid = num_nblk;
+  Workspace* ws = nullptr;
+  if (int rc = ensure_workspace(ctx->device, static_cast<size_t>(plan->splits) * M * N * sizeof(float), num_nblk, &ws))
+    return rc;
+  plan->partials = ws->partials;
+  plan->counters = ws->counters;
+  return 0;
+}
+
+int run_gemm_o2_skinny(const GemmPlan& p, cudaStream_t stream) {
+  gemm_o2_skinny_kernel<<<dim3(p.grid, p.splits), kThreads, kSmemBytes, stream>>>(
+      p.tm_b, p.tm_a, static_cast<const uint8_t*>(p.sfb), static_cast<const uint8_t*>(p.sfa), p.y, p.partials,
+      p.counters, p.M, p.N, p.K, p.ldy, p.kb_per_split, p.status);
+  return check_cuda(cudaGetLastError(), "gemm_o2_skinny_kernel launch");
+}
+
+}  // namespace adg

@@ -68,6 +68,10 @@ struct GemmPlan {
   const void* sfb = nullptr;       // O2: tiled W scales
   float* y = nullptr;
   int32_t* partial_dump = nullptr;  // O1 debug: INT32 partials [M, N, K/32]
+  // decode-sized O2 (M <= 64): operand-swapped split-K kernel; tm_a = A map, tm_b = W map
+  int skinny = 0, splits = 1, kb_per_split = 0;
+  float* partials = nullptr;  // [splits, M, N] FP32, library-owned
+  int* counters = nullptr;    // one arrival counter per 128-row block of W, library-owned
   uint32_t* status = nullptr;
 };
 
@@ -83,5 +87,9 @@ int run_gemm_acc(const GemmPlan& plan, cudaStream_t stream);
 int run_gemm_o1(const GemmPlan& plan, cudaStream_t stream);
 int init_gemm_acc_attributes();
 int init_gemm_o1_attributes();
+int init_gemm_skinny_attributes();
+int plan_o2_skinny(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const void* w_mxfp4, const void* sfb_tiled,
+                   float* y, int M, int N, int K, int ldy);
+int run_gemm_o2_skinny(const GemmPlan& plan, cudaStream_t stream);
 
 }  // namespace adg

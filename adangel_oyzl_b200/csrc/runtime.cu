@@ -65,6 +65,7 @@ int device_ctx(DeviceCtx** out) {
     }
     if (int rc = init_gemm_acc_attributes()) return rc;
     if (int rc = init_gemm_o1_attributes()) return rc;
+    if (int rc = init_gemm_skinny_attributes()) return rc;
     g_ctx[dev] = ctx;
     g_ctx_ready[dev] = true;
   }
@@ -185,6 +186,7 @@ int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const vo
   if (int rc = check_shape(M, N, K, ldy)) return rc;
   if ((reinterpret_cast<uintptr_t>(sfa_tiled) & 15u) != 0 || (reinterpret_cast<uintptr_t>(sfb_tiled) & 15u) != 0)
     return fail("tiled scale buffers must be 16-byte aligned");
+  if (M <= 64) return plan_o2_skinny(plan, a_mxfp4, sfa_tiled, w_mxfp4, sfb_tiled, y, M, N, K, ldy);
   *plan = GemmPlan{};
   plan->variant = 2;
   plan->M = M, plan->N = N, plan->K = K, plan->ldy = ldy;
@@ -202,6 +204,7 @@ int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const vo
 
 int run_plan(const GemmPlan& plan, cudaStream_t stream) {
   if (plan.variant == 1) return run_gemm_o1(plan, stream);
+  if (plan.skinny) return run_gemm_o2_skinny(plan, stream);
   return run_gemm_acc(plan, stream);
 }
 

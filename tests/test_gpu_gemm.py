@@ -77,7 +77,8 @@ def test_canonical_grid(K, shape):
     _compare(K, *orc.canonical_inputs(*shape), dump=shape[0] <= 256)
 
 
-@pytest.mark.parametrize("shape", [(1, 128, 64), (16, 256, 192), (64, 384, 320), (129, 257 * 4, 448), (300, 40, 128)])
+@pytest.mark.parametrize("shape", [(1, 128, 64), (16, 256, 192), (64, 384, 320), (129, 257 * 4, 448), (300, 40, 128),
+                                   (5, 4096, 1024), (48, 136, 2048), (33, 128, 4096)])
 def test_ragged_shapes(K, shape):
     # K not a multiple of the kernels' K slab, M/N not multiples of the tile, single-row A
     m, n, k = shape
