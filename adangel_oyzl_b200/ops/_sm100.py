@@ -167,14 +167,24 @@ def kernel_metadata(variant: str, m: int, n: int, k: int) -> dict:
     }
     if variant == "o0":
         common.update(mma_family="tcgen05.mma.cta_group::1.kind::f16", kernel_symbol="gemm_acc_kernel<0>",
-                      stages=4 if block_n == 256 else 5, mma_shape=[128, block_n, 16])
+                      stages=4 if block_n == 256 else 6, accumulator_stages=2, threads=384,
+                      mma_shape=[128, block_n, 16])
     elif variant == "o1":
         common.update(mma_family="tcgen05.mma.cta_group::1.kind::i8", kernel_symbol="gemm_o1_kernel",
-                      stages=6, mma_shape=[128, 128, 32], partial_rescale="per-K32, FP32 registers",
+                      stages=6, scale_stages=8, threads=640, mma_shape=[128, 128, 32],
+                      partial_rescale="per-K32, FP32 registers",
                       accumulator="INT32 partial in tensor memory, FP32 accumulate in registers")
+    elif m <= 64:
+        # decode shapes: operands swapped, W rows are the MMA M dimension
+        m_pad = (m + 15) // 16 * 16
+        common.update(mma_family="tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32",
+                      kernel_symbol="gemm_o2_skinny_kernel", stages=4, threads=192, tile=[m_pad, 128],
+                      persistent=False, mma_shape=[128, m_pad, 64], scale_format="UE8M0", weight_copy=False,
+                      global_partial_buffer="only when K is split (N < 4096)")
     else:
         common.update(mma_family="tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32",
-                      kernel_symbol="gemm_acc_kernel<2>", stages=4 if block_n == 256 else 5,
+                      kernel_symbol="gemm_acc_kernel<2>", stages=4 if block_n == 256 else 6,
+                      accumulator_stages=1 if block_n == 256 else 2, threads=384,
                       mma_shape=[128, block_n, 64], scale_format="UE8M0", weight_copy=False)
     return common
 
