@@ -68,7 +68,8 @@ struct GemmPlan {
   const void* sfb = nullptr;       // O2: tiled W scales
   float* y = nullptr;
   int32_t* partial_dump = nullptr;  // O1 debug: INT32 partials [M, N, K/32]
-  // decode-sized O2 (M <= 64): operand-swapped split-K kernel; tm_a = A map, tm_b = W map
+  // decode-sized O1/O2 (M <= 64): operand-swapped kernels; tm_a = A map, tm_b = W map; `splits` is
+  // grid.y (K slices for O2, 16-row slices of A for O1)
   int skinny = 0, splits = 1, kb_per_split = 0;
   float* partials = nullptr;  // [splits, M, N] FP32, library-owned
   int* counters = nullptr;    // one arrival counter per 128-row block of W, library-owned
@@ -91,5 +92,9 @@ int init_gemm_skinny_attributes();
 int plan_o2_skinny(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const void* w_mxfp4, const void* sfb_tiled,
                    float* y, int M, int N, int K, int ldy);
 int run_gemm_o2_skinny(const GemmPlan& plan, cudaStream_t stream);
+int init_gemm_o1_skinny_attributes();
+int plan_o1_skinny(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale,
+                   float* y, int M, int N, int K, int ldy);
+int run_gemm_o1_skinny(const GemmPlan& plan, cudaStream_t stream);
 
 }  // namespace adg

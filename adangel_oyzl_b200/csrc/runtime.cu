@@ -66,6 +66,7 @@ int device_ctx(DeviceCtx** out) {
     if (int rc = init_gemm_acc_attributes()) return rc;
     if (int rc = init_gemm_o1_attributes()) return rc;
     if (int rc = init_gemm_skinny_attributes()) return rc;
+    if (int rc = init_gemm_o1_skinny_attributes()) return rc;
     g_ctx[dev] = ctx;
     g_ctx_ready[dev] = true;
   }
@@ -166,6 +167,7 @@ int plan_o1(GemmPlan* plan, const void* a_int8, const void* a_scale, const void*
   DeviceCtx* ctx = nullptr;
   if (int rc = device_ctx(&ctx)) return rc;
   if (int rc = check_shape(M, N, K, ldy)) return rc;
+  if (M <= 64 && partial_dump == nullptr) return plan_o1_skinny(plan, a_int8, a_scale, w_int8, w_scale, y, M, N, K, ldy);
   *plan = GemmPlan{};
   plan->variant = 1;
   plan->M = M, plan->N = N, plan->K = K, plan->ldy = ldy;
@@ -203,7 +205,7 @@ int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const vo
 }
 
 int run_plan(const GemmPlan& plan, cudaStream_t stream) {
-  if (plan.variant == 1) return run_gemm_o1(plan, stream);
+  if (plan.variant == 1) return plan.skinny ? run_gemm_o1_skinny(plan, stream) : run_gemm_o1(plan, stream);
   if (plan.skinny) return run_gemm_o2_skinny(plan, stream);
   return run_gemm_acc(plan, stream);
 }

@@ -85,6 +85,23 @@ def test_ragged_shapes(K, shape):
     _compare(K, *orc.canonical_inputs(m, n, k, seed=11))
 
 
+@pytest.mark.parametrize("shape", [(1, 128, 64), (16, 256, 192), (17, 200, 320), (64, 384, 320), (5, 4096, 1024),
+                                   (48, 136, 2048), (33, 128, 4096), (64, 1024, 4096)])
+def test_decode_shapes(K, shape):
+    # M <= 64 without the partial dump: the operand-swapped O1 and O2 kernels
+    m, n, k = shape
+    _compare(K, *orc.canonical_inputs(m, n, k, seed=13), dump=False)
+
+
+def test_decode_matches_prefill_rows(K):
+    # the decode kernels and the 128-row-tile kernels give the same bits for the same activation rows
+    a_int8, a_scale, w_mx, w_sc = orc.canonical_inputs(160, 512, 1024, seed=17)
+    full = _gpu_all(K, a_int8, a_scale, w_mx, w_sc)
+    part = _gpu_all(K, a_int8[:40], a_scale[:40], w_mx, w_sc)
+    np.testing.assert_array_equal(part[1], full[1][:40])
+    np.testing.assert_allclose(part[2], full[2][:40], rtol=RTOL, atol=ATOL)
+
+
 def test_output_column_block(K):
     # Y written as a column block of a wider matrix (the N-sharded layout): ldy > N
     import torch
