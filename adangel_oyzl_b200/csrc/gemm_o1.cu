@@ -27,17 +27,32 @@ namespace adg {
 
 namespace {
 
+#ifdef ADG_TRACE
+#define TR(slot_, idx_)                                                                                      \
+  do {                                                                                                       \
+    if (blockIdx.x == 0 && (idx_) < 256) trace[(slot_) * 256 + (idx_)] = static_cast<uint32_t>(clock64());     \
+  } while (0)
+#else
+#define TR(slot_, idx_) do {} while (0)
+#endif
+
+#ifndef ADG_O1_BN
+#define ADG_O1_BN 128
+#endif
 constexpr int kBlockM = 128;
-constexpr int kBlockN = 128;
-constexpr int kStages = 6;      // 32 KB each: A 128x128 B + W 128x128 B (4 groups)
-constexpr int kScStages = 8;    // 2 KB each: 4 groups x 128 FP32 factors
+constexpr int kBlockN = ADG_O1_BN;
+constexpr int kCtasPerSm = 128 / kBlockN;
+constexpr int kStages = kBlockN == 128 ? 6 : 4;  // A 128x128 B + W kBlockN x 128 B (4 groups) each
+constexpr int kScStages = 8;    // 4 groups x kBlockN FP32 factors each
 constexpr int kPairs = 2;       // tensor-memory halves, each holding the partials of two K32 groups
-constexpr int kEpiWarps = 16;
+constexpr int kEpiWarps = 4 * (kBlockN / 32);
 constexpr int kFirstEpiWarp = 4;
 constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
 constexpr int kTile = kBlockM * 128;
-constexpr int kStageBytes = 2 * kTile;
+constexpr int kStageBytes = kTile + kBlockN * 128;
 constexpr int kScBytes = 4 * kBlockN * 4;
+constexpr int kTmemCols = kPairs * 2 * kBlockN;
+constexpr int kEpiRegs = kBlockN == 128 ? 112 : 104;
 constexpr int kSmemBytes = kStages * kStageBytes + kScStages * kScBytes + 1024 + 1024;
 constexpr int kGroupM = 8;
 
@@ -68,7 +83,7 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) 
 // kDump = true adds the debug store of every INT32 partial (a separate instantiation so that the
 // production kernel carries none of its register pressure).
 template <bool kDump>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const float* __restrict__ a_scale, const uint8_t* __restrict__ w_scale, float* __restrict__ y,
                int32_t* __restrict__ partial_dump, int M, int N, int K, int ldy, uint32_t* status) {
@@ -97,6 +112,10 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   const int num_tiles = num_m * num_n;
   const int groups = K / 32;
   const int num_kb = (groups + 3) / 4;
+#ifdef ADG_TRACE
+  uint32_t* trace = reinterpret_cast<uint32_t*>(partial_dump);
+  int tr_i = 0;
+#endif
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -119,7 +138,7 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     tma_prefetch_desc(&tm_b);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_base_slot, 512);
+    tmem_alloc(tmem_base_slot, kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -160,21 +179,29 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       constexpr uint32_t idesc = make_idesc(2, kFmtS8, kFmtS8, kBlockM, kBlockN);
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         for (int kb = 0; ok && kb < num_kb; ++kb) {
+          TR(3, tr_i >> 1);
           ok = mbar_wait_a(full_a + stage * 8, phase, status, abort_a, kTagFull | stage);
           if (!ok) break;
+          TR(4, tr_i >> 1);
           tc_fence_after();
           const uint32_t st = smem_u32(smem + stage * kStageBytes);
           const uint64_t adesc = make_desc_sw128(st);
           const uint64_t bdesc = make_desc_sw128(st + kTile);
           const int ng = min(4, groups - kb * 4);  // K is a multiple of 64, so ng is 2 or 4
           for (int g = 0; g < ng; g += 2) {
+            TR(0, tr_i);
             ok = mbar_wait_a(tmem_empty_a + pair * 8, pair_phase ^ 1u, status, abort_a, kTagTmemEmpty | pair);
             if (!ok) break;
+            TR(1, tr_i);
             tc_fence_after();
             const uint32_t d = tmem_base + static_cast<uint32_t>(pair * 2 * kBlockN);
             umma_i8(d, adesc + g * 2, bdesc + g * 2, idesc, 0u);
             umma_i8(d + kBlockN, adesc + (g + 1) * 2, bdesc + (g + 1) * 2, idesc, 0u);
             umma_commit_a(tmem_full_a + pair * 8);
+            TR(2, tr_i);
+#ifdef ADG_TRACE
+            ++tr_i;
+#endif
             if (++pair == kPairs) {
               pair = 0;
               pair_phase ^= 1u;
@@ -190,43 +217,65 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
   } else if (warp == 2) {
     // ------------------------------- weight-scale factors ---------------------------------------
+    // Lane l converts rows l, l+32, ... of the tile's W rows.  The codes of the next K slab are
+    // requested before the current slab is converted, so that the global-load latency (these
+    // strided 4-byte reads mostly miss the small L1) never sits between two ring slots.
     int scs = 0;
     uint32_t sc_phase = 0;
     bool ok = true;
     const bool vec = (groups & 3) == 0;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      const TileCoord tc = tile_coord(tile, num_m, num_n);
+    constexpr int kRowsPerLane = kBlockN / 32;
+    auto load_codes = [&](int n_blk, int kb, uint32_t (&codes)[kRowsPerLane]) {
+#pragma unroll
+      for (int i = 0; i < kRowsPerLane; ++i) {
+        const int n = n_blk * kBlockN + lane + 32 * i;
+        codes[i] = 0;
+        if (n < N) {
+          const uint8_t* src = w_scale + static_cast<long>(n) * groups + kb * 4;
+          if (vec) {
+            codes[i] = __ldg(reinterpret_cast<const uint32_t*>(src));
+          } else {
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              if (kb * 4 + g < groups) codes[i] |= static_cast<uint32_t>(__ldg(src + g)) << (8 * g);
+          }
+        }
+      }
+    };
+    uint32_t next_codes[kRowsPerLane];
+    int tile = blockIdx.x;
+    if (tile < num_tiles) load_codes(tile_coord(tile, num_m, num_n).n_blk, 0, next_codes);
+    for (; ok && tile < num_tiles; tile += gridDim.x) {
+      const int n_blk = tile_coord(tile, num_m, num_n).n_blk;
       for (int kb = 0; kb < num_kb; ++kb) {
+        uint32_t codes[kRowsPerLane];
+#pragma unroll
+        for (int i = 0; i < kRowsPerLane; ++i) codes[i] = next_codes[i];
+        if (kb + 1 < num_kb) {
+          load_codes(n_blk, kb + 1, next_codes);
+        } else if (tile + static_cast<int>(gridDim.x) < num_tiles) {
+          load_codes(tile_coord(tile + gridDim.x, num_m, num_n).n_blk, 0, next_codes);
+        }
+        if (lane == 0) TR(15, tr_i);
         ok = mbar_wait_a(sc_empty_a + scs * 8, sc_phase ^ 1u, status, abort_a, kTagScEmpty | scs);
         if (!ok) break;
+        if (lane == 0) TR(16, tr_i);
         float* dst = sc_ring + scs * (kScBytes / 4);
-#pragma unroll 1
-        for (int i = 0; i < 4; ++i) {
-          const int n_local = lane + 32 * i;
-          const int n = tc.n_blk * kBlockN + n_local;
-          uint32_t codes = 0;
-          uint32_t valid = 0;
-          if (n < N) {
-            const uint8_t* src = w_scale + static_cast<long>(n) * groups + kb * 4;
-            if (vec) {
-              codes = __ldg(reinterpret_cast<const uint32_t*>(src));
-              valid = 0xF;
-            } else {
 #pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                if (kb * 4 + g < groups) {
-                  codes |= static_cast<uint32_t>(__ldg(src + g)) << (8 * g);
-                  valid |= 1u << g;
-                }
-              }
-            }
-          }
+        for (int i = 0; i < kRowsPerLane; ++i) {
+          const int n_local = lane + 32 * i;
+          const bool row_ok = n_blk * kBlockN + n_local < N;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            dst[g * kBlockN + n_local] = ((valid >> g) & 1u) ? ue8m0_half_to_float((codes >> (8 * g)) & 0xFFu) : 0.0f;
+            const bool valid = row_ok && kb * 4 + g < groups;
+            dst[g * kBlockN + n_local] = valid ? ue8m0_half_to_float((codes[i] >> (8 * g)) & 0xFFu) : 0.0f;
           }
         }
         mbar_arrive_a(sc_full_a + scs * 8);
+        if (lane == 0) TR(17, tr_i);
+#ifdef ADG_TRACE
+        ++tr_i;
+#endif
         if (++scs == kScStages) {
           scs = 0;
           sc_phase ^= 1u;
@@ -235,7 +284,7 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
   }
   } else {
-    reg_alloc<112>();
+    reg_alloc<kEpiRegs>();
     // ------------------------------- epilogue ---------------------------------------------------
     // Each warp owns 32 columns of one lane quarter.  The two partials of a pair go to two register
     // buffers: while one partial is scaled and accumulated, the load of the next is in flight.
@@ -281,7 +330,14 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         }
         const uint32_t sc = sc_base + static_cast<uint32_t>(scs * kScBytes + ((g & 3) * kBlockN) * 4);
         // ---- first partial of the pair: wait for it, start loading the second, compute
+#ifdef ADG_TRACE
+        const int tslot = warp == kFirstEpiWarp ? 5 : 10;
+        const bool tr_on = lane == 0 && (warp == kFirstEpiWarp || warp == kFirstEpiWarp + kEpiWarps - 1);
+#endif
         tmem_wait_ld_for(pa);
+#ifdef ADG_TRACE
+        if (tr_on) TR(tslot, tr_i);
+#endif
         tmem_ld_32x32(t_lane + (pair * 2 + 1) * kBlockN, pb);
         if constexpr (kDump) {
           if (row < M) {
@@ -291,11 +347,17 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           }
         }
         accumulate(pa, acc, a2, sc);
+#ifdef ADG_TRACE
+        if (tr_on) TR(tslot + 1, tr_i);
+#endif
         // ---- second partial: wait for it, hand the pair back, start loading the next pair's first
         tmem_wait_ld_for(pb);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_a(tmem_empty_a + pair * 8);
+#ifdef ADG_TRACE
+        if (tr_on) TR(tslot + 2, tr_i);
+#endif
+        // the next pair's first load goes out before this pair is handed back, so that the warp
+        // has no load in flight only for the length of one barrier probe
+        const int done_pair = pair;
         if (++pair == kPairs) {
           pair = 0;
           pair_phase ^= 1u;
@@ -305,8 +367,14 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           ok = mbar_wait_a(tmem_full_a + pair * 8, pair_phase, status, abort_a, kTagTmemFull | pair);
           if (!ok) break;
           tc_fence_after();
+#ifdef ADG_TRACE
+          if (tr_on) TR(tslot + 3, tr_i);
+#endif
           tmem_ld_32x32(t_lane + pair * 2 * kBlockN, pa);
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_a(tmem_empty_a + done_pair * 8);
         if constexpr (kDump) {
           if (row < M) {
 #pragma unroll
@@ -315,6 +383,10 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           }
         }
         accumulate(pb, acc, a2, sc + kBlockN * 4);
+#ifdef ADG_TRACE
+        if (tr_on) TR(tslot + 4, tr_i);
+        ++tr_i;
+#endif
         if ((g & 3) == 2 || !more) {
           __syncwarp();
           if (lane == 0) mbar_arrive_a(sc_empty_a + scs * 8);
@@ -345,10 +417,13 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 1) tmem_dealloc(tmem_base, 512);
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 }  // namespace
+
+int o1_block_n() { return kBlockN; }
+int o1_ctas_per_sm() { return kCtasPerSm; }
 
 int init_gemm_o1_attributes() {
   if (int rc = check_cuda(
@@ -362,13 +437,22 @@ int init_gemm_o1_attributes() {
 
 int run_gemm_o1(const GemmPlan& p, cudaStream_t stream) {
   if (p.variant != 1) return fail("run_gemm_o1: plan is not an O1 plan");
+#ifdef ADG_TRACE
+  if (false) {
+#else
   if (p.partial_dump != nullptr) {
+#endif
     gemm_o1_kernel<true><<<p.grid, kThreads, kSmemBytes, stream>>>(
         p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y,
         p.partial_dump, p.M, p.N, p.K, p.ldy, p.status);
   } else {
     gemm_o1_kernel<false><<<p.grid, kThreads, kSmemBytes, stream>>>(
-        p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y, nullptr,
+        p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y,
+#ifdef ADG_TRACE
+        p.partial_dump,
+#else
+        nullptr,
+#endif
         p.M, p.N, p.K, p.ldy, p.status);
   }
   return check_cuda(cudaGetLastError(), "gemm_o1_kernel launch");

@@ -88,6 +88,8 @@ int run_gemm_acc(const GemmPlan& plan, cudaStream_t stream);
 int run_gemm_o1(const GemmPlan& plan, cudaStream_t stream);
 int init_gemm_acc_attributes();
 int init_gemm_o1_attributes();
+int o1_block_n();      // W rows per O1 tile
+int o1_ctas_per_sm();  // resident O1 CTAs per SM
 int init_gemm_skinny_attributes();
 int plan_o2_skinny(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const void* w_mxfp4, const void* sfb_tiled,
                    float* y, int M, int N, int K, int ldy);

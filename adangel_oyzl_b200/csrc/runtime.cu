@@ -176,9 +176,14 @@ int plan_o1(GemmPlan* plan, const void* a_int8, const void* a_scale, const void*
   plan->partial_dump = partial_dump;
   plan->y = y;
   if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_int8, M, K, K, 128, 128)) return rc;
-  if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_int8, N, K, K, 128, 128)) return rc;
+  if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_int8, N, K, K, o1_block_n(), 128))
+    return rc;
   plan->tm_y = plan->tm_a;
-  return finish_plan(plan, 128);
+  if (int rc = finish_plan(plan, o1_block_n())) return rc;
+  const long tiles = static_cast<long>((M + 127) / 128) * ((N + o1_block_n() - 1) / o1_block_n());
+  const long resident = static_cast<long>(ctx->sm_count) * o1_ctas_per_sm();
+  plan->grid = static_cast<int>(tiles < resident ? tiles : resident);
+  return 0;
 }
 
 int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const void* w_mxfp4, const void* sfb_tiled,
