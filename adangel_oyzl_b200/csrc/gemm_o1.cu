@@ -296,15 +296,23 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     uint32_t pair_phase = 0, sc_phase = 0;
     bool ok = true;
 
-    auto accumulate = [&](const uint32_t (&p)[32], float2 (&acc)[16], const float2 a2, const uint32_t sc) {
+    // Three passes over the partial (in place), each a run of independent instructions, so that
+    // the chain convert -> multiply -> fma of one element never stalls the warp.
+    auto accumulate = [&](uint32_t (&p)[32], float2 (&acc)[16], const float2 a2, const uint32_t sc) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) p[j] = __float_as_uint(__int2float_rn(static_cast<int>(p[j])));
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float2 u = __fmul2_rn(make_float2(__uint_as_float(p[2 * j]), __uint_as_float(p[2 * j + 1])), a2);
+        p[2 * j] = __float_as_uint(u.x);
+        p[2 * j + 1] = __float_as_uint(u.y);
+      }
 #pragma unroll
       for (int j4 = 0; j4 < 8; ++j4) {
         float4 s;
         asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(s.x), "=f"(s.y), "=f"(s.z), "=f"(s.w) : "r"(sc + j4 * 16));
-        const float2 f0 = make_float2(__int2float_rn(static_cast<int>(p[4 * j4])), __int2float_rn(static_cast<int>(p[4 * j4 + 1])));
-        const float2 f1 = make_float2(__int2float_rn(static_cast<int>(p[4 * j4 + 2])), __int2float_rn(static_cast<int>(p[4 * j4 + 3])));
-        acc[2 * j4] = __ffma2_rn(__fmul2_rn(f0, a2), make_float2(s.x, s.y), acc[2 * j4]);
-        acc[2 * j4 + 1] = __ffma2_rn(__fmul2_rn(f1, a2), make_float2(s.z, s.w), acc[2 * j4 + 1]);
+        acc[2 * j4] = __ffma2_rn(make_float2(__uint_as_float(p[4 * j4]), __uint_as_float(p[4 * j4 + 1])), make_float2(s.x, s.y), acc[2 * j4]);
+        acc[2 * j4 + 1] = __ffma2_rn(make_float2(__uint_as_float(p[4 * j4 + 2]), __uint_as_float(p[4 * j4 + 3])), make_float2(s.z, s.w), acc[2 * j4 + 1]);
       }
     };
 
@@ -372,8 +380,7 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #endif
           tmem_ld_32x32(t_lane + pair * 2 * kBlockN, pa);
         }
-        tc_fence_before();
-        __syncwarp();
+        tc_fence_before();  // tcgen05.wait::ld is warp-collective: every lane's loads have landed
         if (lane == 0) mbar_arrive_a(tmem_empty_a + done_pair * 8);
         if constexpr (kDump) {
           if (row < M) {
