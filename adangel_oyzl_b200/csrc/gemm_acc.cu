@@ -268,6 +268,7 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     uint8_t* buf = staging + (warp - 2) * kStagingPerWarp;
     const uint32_t buf_row = smem_u32(buf) + lane * 64;
     const uint32_t swz = static_cast<uint32_t>((lane >> 1) & 3);
+    const uint64_t store_policy = l2_policy_evict_first();
     int local_tile = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
@@ -306,7 +307,9 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
           __syncwarp();
           if (lane == 0) {
             const int col = col0 + c * 16;
-            if (row0 < M && col < N) tma_store_2d(&tm_y, buf, col, row0);
+            // Y is written once and never re-read here: marked evict-first so that it does not
+            // push the operand tiles, which every CTA re-reads, out of the L2
+            if (row0 < M && col < N) tma_store_2d_hint(&tm_y, buf, col, row0, store_policy);
             bulk_commit_group();
           }
         }
