@@ -12,9 +12,10 @@
 // 64 tensor-memory columns, and four such batches can be in flight.  The grid is
 // (N/128) x ceil(M/16); each CTA walks all of K in order, so the accumulation order per element is
 // the reference's and the result does not depend on the grid.  An epilogue thread owns one row n of
-// W: its 16 accumulators are the 16 activation rows, its weight scale is per thread and the
-// activation scales are per register.  While one batch is scaled and accumulated, the
-// tensor-memory load of the next is in flight.
+// W and 8 of the CTA's 16 activation rows: its weight scale is per thread, the activation scales
+// are per register.  While one batch is scaled and accumulated, the tensor-memory load of the next
+// is in flight.  A thread needs 100+ cycles to issue one MMA whatever its size, so two warps issue
+// (even and odd batches; every batch has its own tensor-memory slot, so they need no ordering).
 #include "codecs.cuh"
 #include "common.cuh"
 #include "launch.h"
@@ -32,7 +33,10 @@ constexpr int kStageBytes = kTileW + kTileA;
 constexpr int kSlots = 4;                 // batches of partials in tensor memory
 constexpr int kSlotCols = 4 * kCols;      // four K32 groups x 16 columns
 constexpr int kTmemCols = kSlots * kSlotCols;
-constexpr int kThreads = 192;             // warp 0 producer, warp 1 MMA, warps 2-5 epilogue
+constexpr int kEpiWarps = 8;
+constexpr int kFirstEpiWarp = 4;
+constexpr int kColsPerWarp = kCols / (kEpiWarps / 4);  // 8
+constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;  // warp 0 producer, warps 1-2 MMA, warps 4-11 epilogue
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
 
 enum : uint32_t { kTagEmpty = 0x3100, kTagFull = 0x3200, kTagSlotEmpty = 0x3300, kTagSlotFull = 0x3400 };
@@ -65,7 +69,7 @@ gemm_o1_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     }
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(&slot_full_bar[s], 1);
-      mbar_init(&slot_empty_bar[s], 4);
+      mbar_init(&slot_empty_bar[s], kEpiWarps);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -99,12 +103,14 @@ gemm_o1_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 2) {
     if (lane == 0) {
-      int stage = 0, slot = 0;
-      uint32_t phase = 0, slot_phase = 0;
       constexpr uint32_t idesc = make_idesc(2, kFmtS8, kFmtS8, kRows, kCols);
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = warp - 1; kb < num_kb; kb += 2) {
+        const int stage = kb % kStages;
+        const uint32_t phase = static_cast<uint32_t>(kb / kStages) & 1u;
+        const int slot = kb % kSlots;
+        const uint32_t slot_phase = static_cast<uint32_t>(kb / kSlots) & 1u;
         if (!mbar_wait(&full_bar[stage], phase, env, kTagFull | stage)) break;
         if (!mbar_wait(&slot_empty_bar[slot], slot_phase ^ 1u, env, kTagSlotEmpty | slot)) break;
         tc_fence_after();
@@ -116,29 +122,23 @@ gemm_o1_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         for (int g = 0; g < ng; ++g) umma_i8(d + g * kCols, wdesc + g * 2, adesc + g * 2, idesc, 0u);
         umma_commit(&slot_full_bar[slot]);
         umma_commit(&empty_bar[stage]);
-        if (++stage == kStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
-        if (++slot == kSlots) {
-          slot = 0;
-          slot_phase ^= 1u;
-        }
       }
     }
-  } else {
+  } else if (warp >= kFirstEpiWarp) {
     // ------------------------------- epilogue ---------------------------------------------------
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
     const int n = nb * kRows + q * 32 + lane;
     const bool n_ok = n < N;
-    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const int ch = (warp - kFirstEpiWarp) >> 2;  // which 8 of the CTA's 16 activation rows
+    const int mc = m0 + ch * kColsPerWarp;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(ch * kColsPerWarp);
     const uint8_t* sc_row = w_scale + static_cast<long>(n_ok ? n : 0) * groups;
     const bool vec = (groups & 3) == 0;
 
-    float asc[kCols], acc[kCols];
+    float asc[kColsPerWarp], acc[kColsPerWarp];
 #pragma unroll
-    for (int j = 0; j < kCols; ++j) {
-      asc[j] = (m0 + j < M) ? __ldg(a_scale + m0 + j) : 0.0f;
+    for (int j = 0; j < kColsPerWarp; ++j) {
+      asc[j] = (mc + j < M) ? __ldg(a_scale + mc + j) : 0.0f;
       acc[j] = 0.0f;
     }
 
@@ -153,32 +153,39 @@ gemm_o1_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         if (kb * 4 + g < groups) c |= static_cast<uint32_t>(__ldg(sc_row + kb * 4 + g)) << (8 * g);
       return c;
     };
-    auto load_batch = [&](int slot, uint32_t (&p)[4][kCols]) {
+    auto load_batch = [&](int slot, uint32_t (&p)[4][kColsPerWarp]) {
 #pragma unroll
-      for (int g = 0; g < 4; ++g) tmem_ld_32x16(t_lane + static_cast<uint32_t>(slot * kSlotCols + g * kCols), p[g]);
+      for (int g = 0; g < 4; ++g) tmem_ld_32x8(t_lane + static_cast<uint32_t>(slot * kSlotCols + g * kCols), p[g]);
     };
-    auto wait_batch = [&](uint32_t (&p)[4][kCols]) {
+    auto wait_batch = [&](uint32_t (&p)[4][kColsPerWarp]) {
 #pragma unroll
       for (int g = 0; g < 4; ++g) tmem_wait_ld_for(p[g]);
     };
-    auto accumulate = [&](const uint32_t (&p)[4][kCols], uint32_t codes, int ng) {
+    // convert, multiply and accumulate as separate in-place passes: runs of independent instructions
+    auto accumulate = [&](uint32_t (&p)[4][kColsPerWarp], uint32_t codes, int ng) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int j = 0; j < kColsPerWarp; ++j) p[g][j] = __float_as_uint(__int2float_rn(static_cast<int>(p[g][j])));
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int j = 0; j < kColsPerWarp; ++j) p[g][j] = __float_as_uint(__fmul_rn(__uint_as_float(p[g][j]), asc[j]));
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         if (g < ng) {
           const float s = ue8m0_half_to_float((codes >> (8 * g)) & 0xFFu);
 #pragma unroll
-          for (int j = 0; j < kCols; ++j)
-            acc[j] = __fmaf_rn(__fmul_rn(__int2float_rn(static_cast<int>(p[g][j])), asc[j]), s, acc[j]);
+          for (int j = 0; j < kColsPerWarp; ++j) acc[j] = __fmaf_rn(__uint_as_float(p[g][j]), s, acc[j]);
         }
       }
     };
     auto release = [&](int slot) {
-      tc_fence_before();
-      __syncwarp();
+      tc_fence_before();  // tcgen05.wait::ld is warp-collective: every lane's loads have landed
       if (lane == 0) mbar_arrive(&slot_empty_bar[slot]);
     };
 
-    uint32_t pa[4][kCols], pb[4][kCols];
+    uint32_t pa[4][kColsPerWarp], pb[4][kColsPerWarp];
     int slot = 0;
     uint32_t slot_phase = 0;
     auto next_slot = [&]() {
@@ -223,8 +230,8 @@ gemm_o1_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     }
     if (ok && n_ok) {
 #pragma unroll
-      for (int j = 0; j < kCols; ++j)
-        if (m0 + j < M) y[static_cast<long>(m0 + j) * ldy + n] = acc[j];
+      for (int j = 0; j < kColsPerWarp; ++j)
+        if (mc + j < M) y[static_cast<long>(mc + j) * ldy + n] = acc[j];
     }
   }
 
