@@ -169,6 +169,12 @@ def kernel_metadata(variant: str, m: int, n: int, k: int) -> dict:
         common.update(mma_family="tcgen05.mma.cta_group::1.kind::f16", kernel_symbol="gemm_acc_kernel<0>",
                       stages=4 if block_n == 256 else 6, accumulator_stages=2, threads=384,
                       mma_shape=[128, block_n, 16])
+    elif variant == "o1" and m <= 64:
+        # decode shapes: operands swapped, one CTA per 128 W rows x 16 A rows, K walked in order
+        common.update(mma_family="tcgen05.mma.cta_group::1.kind::i8", kernel_symbol="gemm_o1_skinny_kernel",
+                      stages=8, threads=384, tile=[16, 128], persistent=False, mma_shape=[128, 16, 32],
+                      partial_rescale="per-K32, FP32 registers",
+                      accumulator="INT32 partial in tensor memory, FP32 accumulate in registers")
     elif variant == "o1":
         common.update(mma_family="tcgen05.mma.cta_group::1.kind::i8", kernel_symbol="gemm_o1_kernel",
                       stages=6, scale_stages=8, threads=640, mma_shape=[128, 128, 32],
