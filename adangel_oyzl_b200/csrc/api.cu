@@ -359,7 +359,7 @@ int adg_session_create(adg_session** out, int variant, int max_M, int N, int K, 
   return 0;
 }
 
-int adg_session_run(adg_session* s, const void* a_int8_host, const void* a_scale_host, int M, float* y_host) {
+int adg_session_submit(adg_session* s, const void* a_int8_host, const void* a_scale_host, int M, float* y_host) {
   if (s == nullptr) return fail("session must not be NULL");
   if (M <= 0 || M > s->max_M) return fail("M exceeds the session's max_M");
   const int N = s->N, K = s->K;
@@ -381,9 +381,17 @@ int adg_session_run(adg_session* s, const void* a_int8_host, const void* a_scale
     if (int rc = plan_o2(&plan, s->a_conv.p, s->a_sf_tiled.p, s->w_raw.p, s->w_conv.p, y, M, N, K, N)) return rc;
   }
   if (int rc = run_plan(plan, st)) return rc;
-  if (int rc = check_cuda(cudaMemcpyAsync(y_host, y, sizeof(float) * M * static_cast<size_t>(N), cudaMemcpyDeviceToHost, st), "D2H Y"))
-    return rc;
-  return check_device_status(st);
+  return check_cuda(cudaMemcpyAsync(y_host, y, sizeof(float) * M * static_cast<size_t>(N), cudaMemcpyDeviceToHost, st), "D2H Y");
+}
+
+int adg_session_wait(adg_session* s) {
+  if (s == nullptr) return fail("session must not be NULL");
+  return check_device_status(s->stream);
+}
+
+int adg_session_run(adg_session* s, const void* a_int8_host, const void* a_scale_host, int M, float* y_host) {
+  if (int rc = adg_session_submit(s, a_int8_host, a_scale_host, M, y_host)) return rc;
+  return adg_session_wait(s);
 }
 
 void adg_session_destroy(adg_session* s) {

@@ -189,6 +189,16 @@ class HostSession:
         _sm100._check(_lib().adg_session_run(self._handle, _host_ptr(a_int8), _host_ptr(a_scale), m, _host_ptr(y_out)))
         return y_out
 
+    def submit(self, a_int8, a_scale, y_out):
+        """Enqueue one pass and return at once; the host buffers must be pinned and stay untouched
+        until :meth:`wait`.  Passes of different sessions overlap (each session has its own stream)."""
+        m = a_int8.shape[0]
+        _sm100._check(_lib().adg_session_submit(self._handle, _host_ptr(a_int8), _host_ptr(a_scale), m, _host_ptr(y_out)))
+        return y_out
+
+    def wait(self):
+        _sm100._check(_lib().adg_session_wait(self._handle))
+
     def close(self):
         if self._handle:
             _lib().adg_session_destroy(self._handle)

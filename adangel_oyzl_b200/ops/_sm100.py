@@ -57,6 +57,8 @@ _SIGNATURES = {
     "adg_verify_layout": (c_int, [POINTER(c_int), POINTER(c_float)]),
     "adg_session_create": (c_int, [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "adg_session_run": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "adg_session_submit": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "adg_session_wait": (c_int, [c_void_p]),
     "adg_session_destroy": (None, [c_void_p]),
 }
 

@@ -353,24 +353,32 @@ def run_native_arm(args) -> None:
         s_host = torch.empty((M,), dtype=torch.float32).pin_memory()
         a_host.copy_(a_int8.cpu())
         s_host.copy_(a_scale.cpu())
-        y_host = torch.empty((M, N_PER_GPU), dtype=torch.float32).pin_memory()
+        y_host = {v: torch.empty((M, N_PER_GPU), dtype=torch.float32).pin_memory() for v in VARIANTS}
         w_mx_host, w_sc_host = w_mxfp4.cpu().contiguous(), w_scale.cpu().contiguous()
         sessions = {v: kernels.HostSession(v, M, w_mx_host, w_sc_host) for v in VARIANTS}
         e2e_steps = max(3, min(args.steps, 10))
-        for v in VARIANTS:
-            sessions[v].run(a_host, s_host, y_host)
+
+        def e2e_step():
+            # the three variants' passes are submitted back to back (each on its session's stream), so
+            # one variant's copies overlap another's kernels; the step ends when every Y is in host memory
+            for v in VARIANTS:
+                sessions[v].submit(a_host, s_host, y_host[v])
+            for v in VARIANTS:
+                sessions[v].wait()
+
+        e2e_step()
         torch.cuda.synchronize(dev)
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            for v in VARIANTS:
-                sessions[v].run(a_host, s_host, y_host)
+            e2e_step()
         e2e_sec = (time.perf_counter() - t0) / e2e_steps
         for s in sessions.values():
             s.close()
         e2e = {"value": len(VARIANTS) * FLOP_PER_VARIANT / e2e_sec / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": len(VARIANTS) * (M * K + 4 * M), "d2h_bytes_per_step": len(VARIANTS) * 4 * M * N_PER_GPU,
                "ms_per_step": e2e_sec * 1e3, "steps": e2e_steps,
-               "path": "adg_session_run (C ABI, pinned host buffers): H2D A + conversion + GEMM + D2H Y per variant"}
+               "path": "adg_session_submit/wait (C ABI, pinned host buffers): H2D A + conversion + GEMM + D2H Y per variant, "
+                       "the three variants' passes in flight together"}
 
     cpu = None
     if not distributed and not args.no_cpu_baseline:

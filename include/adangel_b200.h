@@ -188,6 +188,14 @@ int adg_session_create(adg_session** out, int variant, int max_M, int N, int K, 
  * result is in y_host. */
 int adg_session_run(adg_session* session, const void* a_int8_host, const void* a_scale_host, int M, float* y_host);
 
+/* The two halves of adg_session_run: submit enqueues the pass on the session's own stream and
+ * returns at once (pinned host buffers; both must stay untouched until the wait), wait blocks until
+ * the result is in y_host and reports device-side errors.  Several sessions submitted before their
+ * waits overlap one session's copies with another's kernels.  One pass in flight per session.
+ * No reference counterpart (the reference's operators are synchronous device-tensor calls). */
+int adg_session_submit(adg_session* session, const void* a_int8_host, const void* a_scale_host, int M, float* y_host);
+int adg_session_wait(adg_session* session);
+
 void adg_session_destroy(adg_session* session);
 
 #ifdef __cplusplus

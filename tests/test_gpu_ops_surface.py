@@ -142,3 +142,25 @@ def test_host_session_matches_device_path(golden_dir):
         session.run(a_int8, a_scale, y)
         session.close()
         np.testing.assert_allclose(y, ref[key], rtol=1e-3, atol=1e-3)
+
+
+def test_host_sessions_overlapped_submit_wait(golden_dir):
+    # the three variants' passes in flight together (submit all, then wait all), pinned buffers
+    import torch
+    from adangel_oyzl_b200.kernels import HostSession
+
+    ref, args = golden_inputs(golden_dir, "fp16_seed2026_132x132x256")
+    a_int8, a_scale, w_mx, w_sc = (torch.from_numpy(np.ascontiguousarray(a)) for a in args)
+    a_pin, s_pin = a_int8.pin_memory(), a_scale.pin_memory()
+    sessions = {v: HostSession(v, 256, w_mx, w_sc) for v in ("o0", "o1", "o2")}
+    outs = {v: torch.empty((a_int8.shape[0], w_mx.shape[0]), dtype=torch.float32).pin_memory() for v in sessions}
+    for _ in range(2):
+        for v, s in sessions.items():
+            s.submit(a_pin, s_pin, outs[v])
+        for s in sessions.values():
+            s.wait()
+    for s in sessions.values():
+        s.close()
+    np.testing.assert_allclose(outs["o0"].numpy(), ref["o0_output"], rtol=1e-3, atol=1e-3)
+    np.testing.assert_array_equal(outs["o1"].numpy(), ref["o1_output"])
+    np.testing.assert_allclose(outs["o2"].numpy(), ref["o2_output"], rtol=1e-3, atol=1e-3)
