@@ -131,6 +131,27 @@ int adg_o2_tile_scales(const void* sf_natural, void* sf_tiled, int64_t rows, int
   return launch_o2_tile_scales(sf_natural, sf_tiled, rows, K, as_stream(stream)) ? fail("o2_tile_scales launch failed") : 0;
 }
 
+int adg_quantize_int8_per_row(const void* x, int x_dtype, void* q_int8, void* scale, int64_t rows, int64_t K,
+                              void* stream) {
+  if (rows <= 0 || K <= 0) return fail("rows and K must be positive");
+  if (K % 4 != 0) return fail("K must be divisible by 4");
+  if (x_dtype != 0 && x_dtype != 1) return fail("x_dtype must be 0 (FP32) or 1 (FP16)");
+  if (rows > 0x7fffffffL) return fail("too many rows");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = device_ctx(&ctx)) return rc;
+  return launch_quantize_int8_rows(x, x_dtype, q_int8, scale, rows, K, as_stream(stream)) ? fail("quantize_int8_per_row launch failed") : 0;
+}
+
+int adg_quantize_mxfp4(const void* x, int x_dtype, void* packed, void* scale_codes, int64_t rows, int64_t K,
+                       void* stream) {
+  if (rows <= 0 || K <= 0) return fail("rows and K must be positive");
+  if (K % 32 != 0) return fail("K must be divisible by 32");
+  if (x_dtype != 0 && x_dtype != 1) return fail("x_dtype must be 0 (FP32) or 1 (FP16)");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = device_ctx(&ctx)) return rc;
+  return launch_quantize_mxfp4(x, x_dtype, packed, scale_codes, rows, K, as_stream(stream)) ? fail("quantize_mxfp4 launch failed") : 0;
+}
+
 int adg_gemm_o0(const void* a_fp16, const void* w_fp16, float* y, int M, int N, int K, int ldy, void* stream) {
   GemmPlan plan;
   if (int rc = plan_o0(&plan, a_fp16, w_fp16, y, M, N, K, ldy)) return rc;

@@ -44,6 +44,9 @@ int launch_mxfp4_to_int8(const void* packed, void* out, long rows, long k, cudaS
 int launch_o2_quantize(const void* a_int8, const void* row_scale, void* codes, void* sf_natural, void* sf_tiled,
                        long rows, long k, cudaStream_t stream);
 int launch_o2_tile_scales(const void* natural, void* tiled, long rows, long k, cudaStream_t stream);
+// sample preparation; dtype 0 = FP32, 1 = FP16
+int launch_quantize_int8_rows(const void* x, int dtype, void* q, void* scale, long rows, long k, cudaStream_t stream);
+int launch_quantize_mxfp4(const void* x, int dtype, void* codes, void* scale_codes, long rows, long k, cudaStream_t stream);
 
 // ---- tensor maps ---------------------------------------------------------------------------------
 // 2-D row-major tensor [rows, cols] of `elem_bytes`-wide elements with a row pitch of `pitch_bytes`;

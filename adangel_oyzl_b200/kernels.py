@@ -96,6 +96,52 @@ def o2_tile_scales(scales):
     return tiled
 
 
+def _float_dtype_code(x):
+    import torch
+
+    _require(x.is_cuda and x.dim() == 2 and x.is_contiguous(), "expected a contiguous rank-2 CUDA tensor")
+    _require(x.dtype in (torch.float32, torch.float16), "expected a float32 or float16 tensor")
+    return 0 if x.dtype == torch.float32 else 1
+
+
+def quantize_int8_per_row(x, check_finite: bool = True):
+    """Per-row symmetric INT8 of a float32/float16 CUDA matrix: ``(q int8 [M,K], scale f32 [M])``.
+
+    Same contract as the reference's ``quantize_int8_per_row`` (quantization/int8.py:6-17),
+    including its rejection of NaN/Inf (a host-side check there too)."""
+    import torch
+
+    code = _float_dtype_code(x)
+    rows, k = x.shape
+    if check_finite and not bool(torch.isfinite(x).all()):
+        raise ValueError("activation contains NaN/Inf")
+    q = torch.empty((rows, k), dtype=torch.int8, device=x.device)
+    scale = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _sm100._check(_lib().adg_quantize_int8_per_row(x.data_ptr(), code, q.data_ptr(), scale.data_ptr(), rows, k, _stream(q)))
+    return q, scale
+
+
+def quantize_mxfp4(x, check_finite: bool = True):
+    """MXFP4 of a float32/float16 CUDA matrix: ``(packed u8 [N,K/2], scale codes u8 [N,K/32])``.
+
+    Same contract as the reference's ``quantize_mxfp4`` (quantization/mxfp4.py:147-180) with the
+    exact block exponent of its scalar helper and CUDA kernel."""
+    import torch
+
+    code = _float_dtype_code(x)
+    rows, k = x.shape
+    if k % 32:
+        raise ValueError("x must be rank-2 and K must be divisible by 32")
+    if check_finite and not bool(torch.isfinite(x).all()):
+        raise ValueError("MXFP4 input contains NaN/Inf")
+    packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((rows, k // 32), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _sm100._check(_lib().adg_quantize_mxfp4(x.data_ptr(), code, packed.data_ptr(), scales.data_ptr(), rows, k, _stream(packed)))
+    return packed, scales
+
+
 def _output(out, m, n, device):
     import torch
 

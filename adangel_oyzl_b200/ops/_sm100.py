@@ -49,6 +49,8 @@ _SIGNATURES = {
     "adg_o2_tiled_scale_bytes": (c_int64, [c_int64, c_int64]),
     "adg_o2_quantize_activation": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "adg_o2_tile_scales": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "adg_quantize_int8_per_row": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "adg_quantize_mxfp4": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "adg_gemm_o0": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "adg_gemm_o1": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "adg_gemm_o2": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),

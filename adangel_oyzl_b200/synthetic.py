@@ -65,6 +65,13 @@ def canonical_floats(m: int, n: int, k: int, seed: int = CANONICAL_SEED):
 def canonical_inputs(m: int, n: int, k: int, seed: int = CANONICAL_SEED, device="cpu", sample_id=None) -> PreparedInputs:
     a, w = canonical_floats(m, n, k, seed)
     a, w = a.to(device), w.to(device)
-    a_int8, a_scale = quantize_int8_per_row(a)
-    w_mxfp4, w_scale = quantize_mxfp4(w)
+    if a.is_cuda:
+        # the CUDA quantizers (bit-identical to the torch functions above, without their temporaries)
+        from . import kernels
+
+        a_int8, a_scale = kernels.quantize_int8_per_row(a, check_finite=False)
+        w_mxfp4, w_scale = kernels.quantize_mxfp4(w, check_finite=False)
+    else:
+        a_int8, a_scale = quantize_int8_per_row(a)
+        w_mxfp4, w_scale = quantize_mxfp4(w)
     return PreparedInputs(sample_id or f"synthetic_{m}x{n}x{k}_seed{seed}", a_int8, a_scale, w_mxfp4, w_scale)

@@ -85,6 +85,25 @@ int adg_o2_quantize_activation(const void* a_int8, const void* a_scale, void* a_
  * Replaces adangel_o2_repack_scale for SFB (o2_cutlass.cu:261-274, :298-316). */
 int adg_o2_tile_scales(const void* sf_natural, void* sf_tiled, int64_t rows, int64_t K, void* stream);
 
+/* ---- sample preparation (device pointers): the step in front of the hot path ----------------- */
+/* x_dtype: 0 = FP32, 1 = FP16 (widened to FP32 first, as the reference does).  Inputs must be
+ * finite; the reference rejects NaN/Inf with a host-side check before quantizing and callers of
+ * these entry points do the same. */
+
+/* Symmetric per-row INT8 quantization: scale[r] = amax_r / 127 (1 for an all-zero row),
+ * q = clamp(round_half_even(x / scale), -127, 127).  Replaces quantize_int8_per_row
+ * (python/adangel/quantization/int8.py:6-17) as used by prepare_trace
+ * (python/adangel/trace/prepare.py:113). */
+int adg_quantize_int8_per_row(const void* x, int x_dtype, void* q_int8, void* scale, int64_t rows, int64_t K,
+                              void* stream);
+
+/* MXFP4 quantization of the last dimension: per (row, K32 block) the UE8M0 scale code
+ * floor(log2(amax)) - 2 + 127 (127 for an all-zero block, exponent taken exactly) and packed E2M1
+ * round-to-nearest-even codes [rows,K/2] (even K in the low nibble).  Replaces quantize_mxfp4
+ * (python/adangel/quantization/mxfp4.py:147-180) as used by prepare_trace (prepare.py:114). */
+int adg_quantize_mxfp4(const void* x, int x_dtype, void* packed, void* scale_codes, int64_t rows, int64_t K,
+                       void* stream);
+
 /* ---- GEMM kernels (device pointers) ---------------------------------------------------------- */
 /* ldy is the row pitch of Y in elements (>= N); Y may be a column block of a wider matrix. */
 
