@@ -29,6 +29,9 @@ def _throughput_tflops(m: int, n: int, k: int, ms: float) -> float:
     return (2.0 * m * n * k) / ms / 1.0e9 if ms > 0 else 0.0
 
 
+DECODE_MAX_M = 64  # activations up to this many rows take the weight-streaming decode kernels
+
+
 def _conversion_bytes(variant: str, stage: str, m: int, n: int, k: int) -> int:
     """Bytes each conversion stage moves, with the reference's accounting (runner.py:22-37)."""
     natural_sfa = m * (k // 32)
@@ -40,6 +43,10 @@ def _conversion_bytes(variant: str, stage: str, m: int, n: int, k: int) -> int:
         ("o2", "activation_conversion"): m * k + 4 * m + m * k // 2 + 3 * natural_sfa,
         ("o2", "weight_conversion"): 2 * natural_sfb,
     }
+    if stage == "gemm" and m <= DECODE_MAX_M:
+        # decode shapes are weight-streaming: the GEMM itself is reported in GB/s (W once, A, scales, Y)
+        sizes[("o1", "gemm")] = n * k + natural_sfb + m * k + 4 * m + 4 * m * n
+        sizes[("o2", "gemm")] = n * k // 2 + natural_sfb + m * k // 2 + natural_sfa + 4 * m * n
     return sizes.get((variant, stage), 0)
 
 
@@ -103,11 +110,29 @@ def _roofline(variant: str, summaries: dict, m: int, n: int, k: int) -> dict:
     return out
 
 
-def run_experiment(config_path, output_dir, *, sample_limit=None, warmup_override=None, repeats_override=None,
-                   device="cuda") -> Path:
-    import torch
+def _iter_samples(config, n_samples, device, prepared_dir, formal):
+    """The experiment's samples: loaded from a prepared directory (manifest order, hashes checked)
+    or generated from the seeded synthetic distribution, ``n_samples`` per configured shape."""
+    if prepared_dir is not None:
+        from ..trace.storage import load_manifest, load_prepared
 
+        prepared_dir = Path(prepared_dir)
+        manifest = load_manifest(prepared_dir, formal=formal)
+        for record in manifest["samples"][:n_samples]:
+            yield load_prepared(prepared_dir / record["file"], device=device, expected_sha256=record["sha256"])
+        return
     from ..synthetic import canonical_inputs
+
+    seed = int(config["experiment"]["seed"])
+    for m, n, k in _shapes(config):
+        for sample_index in range(n_samples):
+            yield canonical_inputs(m, n, k, seed=seed + sample_index, device=device,
+                                   sample_id=f"synthetic_{m}x{n}x{k}_s{sample_index:02d}")
+
+
+def run_experiment(config_path, output_dir, *, sample_limit=None, warmup_override=None, repeats_override=None,
+                   device="cuda", prepared_dir=None) -> Path:
+    import torch
 
     require_native()
     config_path, output_dir = Path(config_path), Path(output_dir)
@@ -138,58 +163,54 @@ def run_experiment(config_path, output_dir, *, sample_limit=None, warmup_overrid
     modes = list(config["modes"])
     variants = list(config["variants"])
     formal = bool(config["experiment"].get("formal", False))
-    seed = int(config["experiment"]["seed"])
     with (output_dir / "results.jsonl").open("w", encoding="utf-8") as stream:
-        for shape in _shapes(config):
-            m, n, k = shape
-            for sample_index in range(n_samples):
-                inputs = canonical_inputs(m, n, k, seed=seed + sample_index, device=device,
-                                          sample_id=f"synthetic_{m}x{n}x{k}_s{sample_index:02d}")
-                records = []
-                # variants are interleaved inside each mode to reduce temperature/boost drift
-                for mode in modes:
-                    for variant in variants:
-                        payload = benchmark_variant(inputs, variant, mode, warmup, repeats, backend="native",
-                                                    conversion_inner_repeats=conversion_inner_repeats,
-                                                    formal=formal and shape == (4096, 4096, 4096))
-                        _validate_benchmark_payload(payload, repeats, mode, conversion_inner_repeats)
-                        summaries, stable = _summarize_timings(payload["timings_ms"], max_cv)
-                        for stage, stats in summaries.items():
-                            byte_count = _conversion_bytes(variant, stage, m, n, k)
-                            stats["bytes_moved"] = byte_count
-                            stats["bytes_moved_fused"] = _fused_conversion_bytes(variant, stage, m, n, k)
-                            stats["throughput_gbps"] = (byte_count / float(stats["median_ms"]) / 1.0e6
-                                                        if byte_count and float(stats["median_ms"]) > 0 else 0.0)
-                        gemm_median = summaries.get("gemm", {}).get("median_ms", 0.0)
-                        record = {
-                            "schema_version": 2,
-                            "sample_id": inputs.sample_id,
-                            "variant": variant,
-                            "mode": mode,
-                            "shape": [m, n, k],
-                            "timings_ms": payload["timings_ms"],
-                            "summary": summaries,
-                            "equivalent_tflops": _throughput_tflops(m, n, k, float(gemm_median)),
-                            "mse_vs_o0": None,
-                            "kernel": payload.get("kernel"),
-                            "timing_method": payload.get("timing_method"),
-                            "stable_cv": stable,
-                            "valid": stable,
-                            "roofline": _roofline(variant, summaries, m, n, k),
-                        }
-                        records.append((record, payload["output"] if mode == "compute_only" else None))
-                        del payload
-                outputs = {r["variant"]: out for r, out in records if r["mode"] == "compute_only"}
-                mse = {}
-                if "o0" in outputs:
-                    reference = outputs["o0"]
-                    if not torch.isfinite(reference).all():
-                        raise RuntimeError(f"{inputs.sample_id}: O0 output contains NaN/Inf")
-                    mse = {name: mse_fp64(out, reference) for name, out in outputs.items()}
-                for record, _ in records:
-                    record["mse_vs_o0"] = mse.get(record["variant"])
-                    stream.write(json.dumps(record, ensure_ascii=False) + "\n")
-                    stream.flush()
-                del inputs, records, outputs
-                torch.cuda.empty_cache()
+        for inputs in _iter_samples(config, n_samples, device, prepared_dir, formal):
+            shape = m, n, k = inputs.shape
+            records = []
+            # variants are interleaved inside each mode to reduce temperature/boost drift
+            for mode in modes:
+                for variant in variants:
+                    payload = benchmark_variant(inputs, variant, mode, warmup, repeats, backend="native",
+                                                conversion_inner_repeats=conversion_inner_repeats,
+                                                formal=formal and shape == (4096, 4096, 4096))
+                    _validate_benchmark_payload(payload, repeats, mode, conversion_inner_repeats)
+                    summaries, stable = _summarize_timings(payload["timings_ms"], max_cv)
+                    for stage, stats in summaries.items():
+                        byte_count = _conversion_bytes(variant, stage, m, n, k)
+                        stats["bytes_moved"] = byte_count
+                        stats["bytes_moved_fused"] = _fused_conversion_bytes(variant, stage, m, n, k)
+                        stats["throughput_gbps"] = (byte_count / float(stats["median_ms"]) / 1.0e6
+                                                    if byte_count and float(stats["median_ms"]) > 0 else 0.0)
+                    gemm_median = summaries.get("gemm", {}).get("median_ms", 0.0)
+                    record = {
+                        "schema_version": 2,
+                        "sample_id": inputs.sample_id,
+                        "variant": variant,
+                        "mode": mode,
+                        "shape": [m, n, k],
+                        "timings_ms": payload["timings_ms"],
+                        "summary": summaries,
+                        "equivalent_tflops": _throughput_tflops(m, n, k, float(gemm_median)),
+                        "mse_vs_o0": None,
+                        "kernel": payload.get("kernel"),
+                        "timing_method": payload.get("timing_method"),
+                        "stable_cv": stable,
+                        "valid": stable,
+                        "roofline": _roofline(variant, summaries, m, n, k),
+                    }
+                    records.append((record, payload["output"] if mode == "compute_only" else None))
+                    del payload
+            outputs = {r["variant"]: out for r, out in records if r["mode"] == "compute_only"}
+            mse = {}
+            if "o0" in outputs:
+                reference = outputs["o0"]
+                if not torch.isfinite(reference).all():
+                    raise RuntimeError(f"{inputs.sample_id}: O0 output contains NaN/Inf")
+                mse = {name: mse_fp64(out, reference) for name, out in outputs.items()}
+            for record, _ in records:
+                record["mse_vs_o0"] = mse.get(record["variant"])
+                stream.write(json.dumps(record, ensure_ascii=False) + "\n")
+                stream.flush()
+            del inputs, records, outputs
+            torch.cuda.empty_cache()
     return output_dir

@@ -42,7 +42,24 @@ def _run(args) -> None:
     from .benchmark.runner import run_experiment
 
     print(run_experiment(args.config, args.output, sample_limit=args.samples, warmup_override=args.warmup,
-                         repeats_override=args.repeats))
+                         repeats_override=args.repeats, prepared_dir=args.prepared))
+
+
+def _prepare(args) -> None:
+    from .trace.prepare import prepare_synthetic, prepare_trace
+
+    if args.input:
+        if not (args.config and args.trace_config):
+            raise SystemExit("--input needs --config (experiment YAML) and --trace-config (trace selection YAML)")
+        records = prepare_trace(args.input, args.output, args.config, args.trace_config)
+    else:
+        import yaml
+
+        from .benchmark.runner import _shapes
+
+        config = yaml.safe_load(open(args.config, encoding="utf-8"))
+        records = prepare_synthetic(_shapes(config), args.output, seed=config["experiment"]["seed"])
+    print(f"prepared {len(records)} samples")
 
 
 def _analyze(args) -> None:
@@ -73,7 +90,15 @@ def build_parser() -> argparse.ArgumentParser:
     run.add_argument("--warmup", type=int)
     run.add_argument("--repeats", type=int)
     run.add_argument("--require-native", action="store_true", help="kept for explicit scripts; a run always requires native")
+    run.add_argument("--prepared", help="directory of prepared samples (manifest.json) to run instead of synthetic ones")
     run.set_defaults(func=_run)
+
+    prepare = commands.add_parser("prepare", help="quantize samples on the GPU into a prepared directory")
+    prepare.add_argument("--output", required=True)
+    prepare.add_argument("--config", required=True, help="experiment YAML (shapes and seed; formal YAML with --input)")
+    prepare.add_argument("--input", help="directory of a raw FP16 prefill trace (24 sample files + trace_manifest.json)")
+    prepare.add_argument("--trace-config", help="trace selection YAML (with --input)")
+    prepare.set_defaults(func=_prepare)
 
     analyze = commands.add_parser("analyze", help="generate the four tables of a finished run")
     analyze.add_argument("--run", required=True)
