@@ -113,3 +113,50 @@ def test_run_and_analyze_with_stubbed_native(tmp_path, monkeypatch):
     out = generate_report(run_dir, tmp_path / "report")
     for table in ("01_conversion_overhead.csv", "02_gemm_only.csv", "03_end_to_end.csv", "04_mse.csv"):
         assert (out / "tables" / table).stat().st_size > 0
+
+
+def test_run_from_prepared_directory_with_stubbed_native(tmp_path, monkeypatch):
+    # the runner takes its samples from a prepared directory (manifest order, hashes verified)
+    import torch
+    import yaml
+
+    from adangel_oyzl_b200 import synthetic
+    from adangel_oyzl_b200.trace import storage
+
+    prepared = tmp_path / "prepared"
+    records = []
+    for index, shape in enumerate([(64, 64, 64), (16, 96, 128)]):
+        sample = synthetic.canonical_inputs(*shape, seed=index, sample_id=f"s{index}")
+        record = storage.save_prepared(sample, prepared)
+        record.update(layer=index, projection="synthetic")
+        records.append(record)
+    storage.write_manifest(prepared, records, {"trace": {"source": "test"}}, formal=False)
+
+    seen = []
+
+    def fake_benchmark(inputs, variant, mode, warmup, repeats, backend="native", conversion_inner_repeats=100, formal=True):
+        seen.append((inputs.sample_id, inputs.shape))
+        payload = _payload(mode, repeats, conversion_inner_repeats, variant)
+        payload["output"] = torch.ones((inputs.shape[0], inputs.shape[1]))
+        return payload
+
+    monkeypatch.setattr(runner, "benchmark_variant", fake_benchmark)
+    monkeypatch.setattr(runner, "require_native", lambda: None)
+    monkeypatch.setattr(runner, "write_environment", lambda path: Path(path).write_text("{}"))
+    cfg = yaml.safe_load((ROOT / "adangel_oyzl_b200/configs/experiment/decode_skinny.yaml").read_text())
+    cfg["timing"].update(warmup=0, repeats=3)
+    cfg["data"]["samples"] = 2
+    cfg_path = tmp_path / "cfg.yaml"
+    cfg_path.write_text(yaml.safe_dump(cfg))
+    run_dir = runner.run_experiment(cfg_path, tmp_path / "run", device="cpu", prepared_dir=prepared)
+    rows = [json.loads(line) for line in (run_dir / "results.jsonl").read_text().splitlines()]
+    assert {(r["sample_id"], tuple(r["shape"])) for r in rows} == {("s0", (64, 64, 64)), ("s1", (16, 96, 128))}
+    assert set(seen) == {("s0", (64, 64, 64)), ("s1", (16, 96, 128))}
+    # decode-shaped GEMMs carry their weight-streaming byte count
+    decode = next(r for r in rows if r["sample_id"] == "s1" and r["variant"] == "o2" and r["mode"] == "compute_only")
+    assert decode["summary"]["gemm"]["bytes_moved"] == 96 * 128 // 2 + 96 * 4 + 16 * 128 // 2 + 16 * 4 + 4 * 16 * 96
+    # a corrupted sample file is refused
+    victim = prepared / "s0.pt"
+    victim.write_bytes(victim.read_bytes() + b"x")
+    with pytest.raises(ValueError, match="SHA-256 does not match"):
+        runner.run_experiment(cfg_path, tmp_path / "run2", device="cpu", prepared_dir=prepared)
