@@ -340,6 +340,7 @@ int adg_verify_layout(int* passed, float* max_abs_error) {
 struct adg_session {
   int variant = 0, max_M = 0, N = 0, K = 0;
   cudaStream_t stream = nullptr;
+  bool in_flight = false;  // a submitted pass has not been waited for yet
   DeviceBuffer w_raw, w_scale, w_conv, a_raw, a_scale, a_conv, a_sf_tiled, y;
 };
 
@@ -383,6 +384,7 @@ int adg_session_create(adg_session** out, int variant, int max_M, int N, int K, 
 int adg_session_submit(adg_session* s, const void* a_int8_host, const void* a_scale_host, int M, float* y_host) {
   if (s == nullptr) return fail("session must not be NULL");
   if (M <= 0 || M > s->max_M) return fail("M exceeds the session's max_M");
+  if (s->in_flight) return fail("the session already has a pass in flight: call adg_session_wait first");
   const int N = s->N, K = s->K;
   cudaStream_t st = s->stream;
   if (int rc = check_cuda(cudaMemcpyAsync(s->a_raw.p, a_int8_host, static_cast<size_t>(M) * K, cudaMemcpyHostToDevice, st), "H2D A"))
@@ -402,11 +404,15 @@ int adg_session_submit(adg_session* s, const void* a_int8_host, const void* a_sc
     if (int rc = plan_o2(&plan, s->a_conv.p, s->a_sf_tiled.p, s->w_raw.p, s->w_conv.p, y, M, N, K, N)) return rc;
   }
   if (int rc = run_plan(plan, st)) return rc;
-  return check_cuda(cudaMemcpyAsync(y_host, y, sizeof(float) * M * static_cast<size_t>(N), cudaMemcpyDeviceToHost, st), "D2H Y");
+  if (int rc = check_cuda(cudaMemcpyAsync(y_host, y, sizeof(float) * M * static_cast<size_t>(N), cudaMemcpyDeviceToHost, st), "D2H Y"))
+    return rc;
+  s->in_flight = true;
+  return 0;
 }
 
 int adg_session_wait(adg_session* s) {
   if (s == nullptr) return fail("session must not be NULL");
+  s->in_flight = false;
   return check_device_status(s->stream);
 }
 

@@ -159,6 +159,11 @@ def test_host_sessions_overlapped_submit_wait(golden_dir):
             s.submit(a_pin, s_pin, outs[v])
         for s in sessions.values():
             s.wait()
+    # a second submit before the wait is refused, and the session stays usable
+    sessions["o1"].submit(a_pin, s_pin, outs["o1"])
+    with pytest.raises(RuntimeError, match="already has a pass in flight"):
+        sessions["o1"].submit(a_pin, s_pin, outs["o1"])
+    sessions["o1"].wait()
     for s in sessions.values():
         s.close()
     np.testing.assert_allclose(outs["o0"].numpy(), ref["o0_output"], rtol=1e-3, atol=1e-3)
