@@ -147,6 +147,11 @@ def run_experiment(config_path, output_dir, *, sample_limit=None, warmup_overrid
         raise ValueError("warmup must be non-negative, repeats must be positive, and "
                          "conversion_inner_repeats must exceed one")
     n_samples = int(config["data"]["samples"])
+    if prepared_dir is not None:
+        # a prepared directory brings its own sample list
+        from ..trace.storage import load_manifest
+
+        n_samples = len(load_manifest(Path(prepared_dir), formal=bool(config["experiment"].get("formal", False)))["samples"])
     if sample_limit is not None:
         if not 1 <= sample_limit <= n_samples:
             raise ValueError(f"samples must be in [1,{n_samples}]")

@@ -39,10 +39,10 @@ VARIANTS = ("o0", "o1", "o2")
 FLOP_PER_VARIANT = 2.0 * M * N_PER_GPU * K
 L2_BYTES = 126 * 1024 * 1024
 NOMINAL_TFLOPS = {"o0": 2250.0, "o1": 4500.0, "o2": 9000.0}  # dense FP16 / INT8 / FP4
-# dram__bytes_read.sum + dram__bytes_write.sum per launch at 4096^3 from the ncu capture summarised in
-# profiles/bench_step_kernels_full_4096.md (the 126 MB L2 keeps most of the 64 MiB output on chip)
-NCU_DRAM_TRAFFIC_BYTES = {"o0_int8_to_fp16": 16.8e6, "o0_gemm_f16": 120.7e6, "o1_gemm_i8": 51.4e6,
-                          "o2_quantize": 16.8e6, "o2_gemm_mxf4": 33.0e6}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch at 4096^3 from an ncu capture of one
+# benchmark step (summary kept under profiles/; the 126 MB L2 keeps most of the 64 MiB output on chip)
+NCU_DRAM_TRAFFIC_BYTES = {"o0_int8_to_fp16": 16.8e6, "o0_gemm_f16": 109.1e6, "o1_gemm_i8": 52.1e6,
+                          "o2_quantize": 16.8e6, "o2_gemm_mxf4": 32.2e6}
 # every INT32 K32 partial of O1 crosses the tensor-memory read port (128 B/clk/SM measured):
 TMEM_READ_BYTES_PER_CLK = 128.0
 

@@ -145,7 +145,7 @@ def test_run_from_prepared_directory_with_stubbed_native(tmp_path, monkeypatch):
     monkeypatch.setattr(runner, "write_environment", lambda path: Path(path).write_text("{}"))
     cfg = yaml.safe_load((ROOT / "adangel_oyzl_b200/configs/experiment/decode_skinny.yaml").read_text())
     cfg["timing"].update(warmup=0, repeats=3)
-    cfg["data"]["samples"] = 2
+    cfg["data"]["samples"] = 1  # ignored: the prepared directory brings its own sample list
     cfg_path = tmp_path / "cfg.yaml"
     cfg_path.write_text(yaml.safe_dump(cfg))
     run_dir = runner.run_experiment(cfg_path, tmp_path / "run", device="cpu", prepared_dir=prepared)
