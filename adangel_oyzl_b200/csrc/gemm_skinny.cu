@@ -25,14 +25,14 @@ constexpr int kTileA = kMaxM * 128;
 constexpr int kSf = 1024;       // two 512-byte atoms (8 K32 blocks) for each side
 constexpr int kStageBytes = kTileW + kTileA + 2 * kSf;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
-constexpr int kThreads = 192;   // warp 0 producer, warp 1 MMA, warps 2-5 epilogue
+constexpr int kThreads = 224;   // warp 0 producer, warp 1 MMA, warps 2-5 epilogue, warp 6 scale-factor copier
 constexpr int kAccCols = 64;
 constexpr int kSfColBase = kAccCols;
 constexpr int kSfColsPerStage = 16;  // per K-atom: 4 (W side) + 4 (A side); two K-atoms per stage
 constexpr int kTmemCols = 128;
 constexpr int kMaxSplits = 8;    // K slices per row block of W
 
-enum : uint32_t { kTagEmpty = 0x2100, kTagFull = 0x2200, kTagAcc = 0x2300 };
+enum : uint32_t { kTagEmpty = 0x2100, kTagFull = 0x2200, kTagAcc = 0x2300, kTagSfFull = 0x2400 };
 
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
@@ -45,7 +45,8 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
   uint64_t* acc_bar = bars + 2 * kStages;
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+  uint64_t* sf_full_bar = acc_bar + 1;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sf_full_bar + kStages);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
   volatile int* is_last = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
 
@@ -65,6 +66,7 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
+      mbar_init(&sf_full_bar[s], 1);
     }
     mbar_init(acc_bar, 1);
     *abort_flag = 0;
@@ -108,7 +110,9 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       for (int kb = kb0; kb < kb1; ++kb) {
-        ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | stage);
+        // the scale-factor warp has copied this stage's scales into tensor memory (which also
+        // means the stage's operand tiles have landed)
+        ok = mbar_wait(&sf_full_bar[stage], phase, env, kTagSfFull | stage);
         if (!ok) break;
         tc_fence_after();
         const uint32_t st = smem_u32(smem + stage * kStageBytes);
@@ -116,11 +120,6 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         const uint64_t adesc = make_desc_sw128(st + kTileW);
         const uint32_t sfw_t = tmem_base + kSfColBase + stage * kSfColsPerStage;  // MMA A-side scales (W)
         const uint32_t sfa_t = sfw_t + 8;                                          // MMA B-side scales (A)
-#pragma unroll
-        for (int ka = 0; ka < 2; ++ka) {
-          tmem_cp_32x128b_warpx4(sfw_t + ka * 4, make_desc_sf(st + kTileW + kTileA + ka * 512));
-          tmem_cp_32x128b_warpx4(sfa_t + ka * 4, make_desc_sf(st + kTileW + kTileA + kSf + ka * 512));
-        }
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           const uint32_t sf_id = (ks & 1) * 2;
@@ -135,6 +134,32 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         }
       }
       if (ok) umma_commit(acc_bar);
+    }
+  } else if (warp == 6) {
+    // scale-factor copier: one thread per tcgen05 instruction costs the issuing thread about a
+    // hundred cycles, so the four copies per stage are kept off the MMA thread
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        // the stage's tensor-memory scale columns were last read by MMAs that completed before the
+        // stage was handed back to the producer
+        if (!mbar_wait(&full_bar[stage], phase, env, kTagFull | 0x80 | stage)) break;
+        tc_fence_after();
+        const uint32_t st = smem_u32(smem + stage * kStageBytes);
+        const uint32_t sfw_t = tmem_base + kSfColBase + stage * kSfColsPerStage;
+        const uint32_t sfa_t = sfw_t + 8;
+#pragma unroll
+        for (int ka = 0; ka < 2; ++ka) {
+          tmem_cp_32x128b_warpx4(sfw_t + ka * 4, make_desc_sf(st + kTileW + kTileA + ka * 512));
+          tmem_cp_32x128b_warpx4(sfa_t + ka * 4, make_desc_sf(st + kTileW + kTileA + kSf + ka * 512));
+        }
+        umma_commit(&sf_full_bar[stage]);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
     }
   } else {
     // epilogue: lane = one row n of W, registers = the M outputs of that row
