@@ -267,12 +267,12 @@ int plan_o1_skinny(GemmPlan* plan, const void* a_int8, const void* a_scale, cons
   if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_int8, M, K, K, kCols, 128)) return rc;
   plan->tm_y = plan->tm_a;
   plan->grid = (N + kRows - 1) / kRows;
-  plan->splits = (M + kCols - 1) / kCols;  // grid.y: 16-row slices of A
+  plan->grid_y = (M + kCols - 1) / kCols;  // 16-row slices of A
   return 0;
 }
 
 int run_gemm_o1_skinny(const GemmPlan& p, cudaStream_t stream) {
-  gemm_o1_skinny_kernel<<<dim3(p.grid, p.splits), kThreads, kSmemBytes, stream>>>(
+  gemm_o1_skinny_kernel<<<dim3(p.grid, p.grid_y), kThreads, kSmemBytes, stream>>>(
       p.tm_b, p.tm_a, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y, p.M, p.N, p.K,
       p.ldy, p.status);
   return check_cuda(cudaGetLastError(), "gemm_o1_skinny_kernel launch");

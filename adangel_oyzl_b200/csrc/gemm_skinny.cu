@@ -1,12 +1,13 @@
-// O2 for decode-sized activations (M <= 64): a weight-streaming, split-K block-scaled MXFP4 GEMM.
+// O2 for decode-sized activations (M <= 64): a weight-streaming block-scaled MXFP4 GEMM.
 //
 // With so few activation rows the 128-row tile of the regular kernel would be almost empty and only
 // N/256 CTAs would stream W, so the operands are swapped: the tensor core computes
 // Y^T[n, m] = W[n, :] . A[m, :]^T with the 128 MMA rows taken from W and the MMA N extent equal to M
-// rounded up to 16.  The grid is (N/128 row blocks of W) x (K splits); K is split only when W has
-// few row blocks.  Every CTA accumulates its K slice in tensor memory; with one split it writes Y
-// directly, otherwise it writes an FP32 partial and the last CTA of a row block to finish adds the
-// partials in split order (a fixed order, so the result is reproducible) and writes Y.
+// rounded up to 16.  One CTA per 128-row block of W walks all of K, accumulates in tensor memory
+// and writes its block of Y.  (Splitting K over several CTAs with a last-arriver reduction was
+// measured and removed: a launch of this kernel costs about 6.5 us before the first K slab is
+// consumed and 0.3 us per slab after that, and the hand-off of the partials cost more than the
+// slabs it saved.)
 //
 // Scale factors: W's tiled scales are the MMA's A-side scales (128-row atoms as stored), A's tiled
 // scales are the B-side scales (row block 0 of A's tiled buffer).
@@ -30,15 +31,13 @@ constexpr int kAccCols = 64;
 constexpr int kSfColBase = kAccCols;
 constexpr int kSfColsPerStage = 16;  // per K-atom: 4 (W side) + 4 (A side); two K-atoms per stage
 constexpr int kTmemCols = 128;
-constexpr int kMaxSplits = 8;    // K slices per row block of W
 
 enum : uint32_t { kTagEmpty = 0x2100, kTagFull = 0x2200, kTagAcc = 0x2300, kTagSfFull = 0x2400 };
 
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
                       const uint8_t* __restrict__ sf_w, const uint8_t* __restrict__ sf_a, float* __restrict__ y,
-                      float* __restrict__ partials, int* __restrict__ counters, int M, int N, int K, int ldy,
-                      int kb_per_split, uint32_t* status) {
+                      int M, int N, int K, int ldy, uint32_t* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -48,17 +47,13 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   uint64_t* sf_full_bar = acc_bar + 1;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sf_full_bar + kStages);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
-  volatile int* is_last = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const WaitEnv env{status, abort_flag};
   const int nb = blockIdx.x;      // 128-row block of W
-  const int split = blockIdx.y;   // K slice
-  const int splits = gridDim.y;
   const int num_kb_total = (K + 255) / 256;
-  const int kb0 = split * kb_per_split;
-  const int kb1 = min(num_kb_total, kb0 + kb_per_split);
+  const int kb0 = 0, kb1 = num_kb_total;
   const int katoms = static_cast<int>(((K / 32 + 7) / 8) * 2);
   const uint32_t m_pad = static_cast<uint32_t>((M + 15) / 16 * 16);
 
@@ -70,7 +65,6 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     }
     mbar_init(acc_bar, 1);
     *abort_flag = 0;
-    *is_last = 0;
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
@@ -179,53 +173,10 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[0][j] = r[1][j] = 0u;
       }
-      if (splits == 1) {
-        if (n < N) {
+      if (n < N) {
 #pragma unroll
-          for (int m = 0; m < kMaxM; ++m)
-            if (m < M) y[static_cast<long>(m) * ldy + n] = __uint_as_float(r[m >> 5][m & 31]);
-        }
-      } else {
-        if (n < N) {
-#pragma unroll
-          for (int m = 0; m < kMaxM; ++m)
-            if (m < M) partials[(static_cast<long>(split) * M + m) * N + n] = __uint_as_float(r[m >> 5][m & 31]);
-        }
-        // the last CTA of this row block to get here adds the partials in split order
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (warp == 2 && lane == 0) {
-          const int prev = atomicAdd(&counters[nb], 1);
-          const int last = prev == splits - 1 ? 1 : 0;
-          if (last) counters[nb] = 0;  // ready for the next launch
-          *is_last = last;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*is_last && n < N) {
-          __threadfence();
-          // four output rows at a time, all their partial loads in flight before the first add
-          for (int m0 = 0; m0 < M; m0 += 4) {
-            float v[4][kMaxSplits];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-#pragma unroll
-              for (int s = 0; s < kMaxSplits; ++s) {
-                v[i][s] = (s < splits && m0 + i < M)
-                              ? __ldcg(partials + (static_cast<long>(s) * M + m0 + i) * N + n)
-                              : 0.0f;
-              }
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              if (m0 + i < M) {
-                float sum = 0.0f;
-#pragma unroll
-                for (int s = 0; s < kMaxSplits; ++s) sum += v[i][s];  // split order; absent splits add +0
-                y[static_cast<long>(m0 + i) * ldy + n] = sum;
-              }
-            }
-          }
-        }
+        for (int m = 0; m < kMaxM; ++m)
+          if (m < M) y[static_cast<long>(m) * ldy + n] = __uint_as_float(r[m >> 5][m & 31]);
       }
     }
   }
@@ -236,32 +187,6 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
-// library-owned scratch for the split-K partials and the per-row-block arrival counters
-struct Workspace {
-  float* partials = nullptr;
-  size_t partial_bytes = 0;
-  int* counters = nullptr;
-  size_t counter_count = 0;
-};
-Workspace g_ws[64];
-
-int ensure_workspace(int device, size_t partial_bytes, size_t counter_count, Workspace** out) {
-  Workspace& ws = g_ws[device];
-  if (ws.partial_bytes < partial_bytes) {
-    if (ws.partials) cudaFree(ws.partials);
-    if (int rc = check_cuda(cudaMalloc(&ws.partials, partial_bytes), "cudaMalloc(split-K partials)")) return rc;
-    ws.partial_bytes = partial_bytes;
-  }
-  if (ws.counter_count < counter_count) {
-    if (ws.counters) cudaFree(ws.counters);
-    if (int rc = check_cuda(cudaMalloc(&ws.counters, counter_count * sizeof(int)), "cudaMalloc(counters)")) return rc;
-    if (int rc = check_cuda(cudaMemset(ws.counters, 0, counter_count * sizeof(int)), "cudaMemset(counters)")) return rc;
-    ws.counter_count = counter_count;
-  }
-  *out = &ws;
-  return 0;
-}
-
 }  // namespace
 
 int init_gemm_skinny_attributes() {
@@ -270,8 +195,7 @@ int init_gemm_skinny_attributes() {
       "cudaFuncSetAttribute(gemm_o2_skinny_kernel)");
 }
 
-// Plan for Y[M,N] = A_mxfp4 . W_mxfp4^T with M <= 64.  The partials and counters are shared per
-// device, so launches of such plans must be ordered on one stream.
+// Plan for Y[M,N] = A_mxfp4 . W_mxfp4^T with M <= 64.
 int plan_o2_skinny(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const void* w_mxfp4, const void* sfb_tiled,
                    float* y, int M, int N, int K, int ldy) {
   DeviceCtx* ctx = nullptr;
@@ -291,33 +215,14 @@ int plan_o2_skinny(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, c
   if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_mxfp4, M, kbytes, kbytes, kMaxM, 128))
     return rc;
   plan->tm_y = plan->tm_a;
-  const int num_nblk = (N + kRows - 1) / kRows;
-  const int num_kb = (K + 255) / 256;
-  // K is split only when W has too few row blocks to occupy a useful number of SMs: measured on
-  // B200, 32 CTAs already stream W as fast as 256 do, while the split-K hand-off (fence, arrival
-  // counter, re-reading the partials) adds several microseconds.  The partial traffic
-  // (splits * M * N * 4 bytes) is also kept below W's own bytes.
-  int splits = 32 / num_nblk;
-  const int traffic_cap = K / (16 * ((M + 15) / 16 * 16));
-  if (splits > traffic_cap) splits = traffic_cap;
-  if (splits > kMaxSplits) splits = kMaxSplits;
-  if (splits > num_kb) splits = num_kb;
-  if (splits < 1) splits = 1;
-  plan->kb_per_split = (num_kb + splits - 1) / splits;
-  plan->splits = (num_kb + plan->kb_per_split - 1) / plan->kb_per_split;
-  plan->grid = num_nblk;
-  Workspace* ws = nullptr;
-  if (int rc = ensure_workspace(ctx->device, static_cast<size_t>(plan->splits) * M * N * sizeof(float), num_nblk, &ws))
-    return rc;
-  plan->partials = ws->partials;
-  plan->counters = ws->counters;
+  plan->grid = (N + kRows - 1) / kRows;
   return 0;
 }
 
 int run_gemm_o2_skinny(const GemmPlan& p, cudaStream_t stream) {
-  gemm_o2_skinny_kernel<<<dim3(p.grid, p.splits), kThreads, kSmemBytes, stream>>>(
-      p.tm_b, p.tm_a, static_cast<const uint8_t*>(p.sfb), static_cast<const uint8_t*>(p.sfa), p.y, p.partials,
-      p.counters, p.M, p.N, p.K, p.ldy, p.kb_per_split, p.status);
+  gemm_o2_skinny_kernel<<<p.grid, kThreads, kSmemBytes, stream>>>(
+      p.tm_b, p.tm_a, static_cast<const uint8_t*>(p.sfb), static_cast<const uint8_t*>(p.sfa), p.y, p.M, p.N, p.K, p.ldy,
+      p.status);
   return check_cuda(cudaGetLastError(), "gemm_o2_skinny_kernel launch");
 }
 

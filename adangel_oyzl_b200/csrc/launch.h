@@ -71,11 +71,9 @@ struct GemmPlan {
   const void* sfb = nullptr;       // O2: tiled W scales
   float* y = nullptr;
   int32_t* partial_dump = nullptr;  // O1 debug: INT32 partials [M, N, K/32]
-  // decode-sized O1/O2 (M <= 64): operand-swapped kernels; tm_a = A map, tm_b = W map; `splits` is
-  // grid.y (K slices for O2, 16-row slices of A for O1)
-  int skinny = 0, splits = 1, kb_per_split = 0;
-  float* partials = nullptr;  // [splits, M, N] FP32, library-owned
-  int* counters = nullptr;    // one arrival counter per 128-row block of W, library-owned
+  // decode-sized O1/O2 (M <= 64): operand-swapped kernels; tm_a = A map, tm_b = W map; `grid_y`
+  // is the number of 16-row slices of A (O1 only)
+  int skinny = 0, grid_y = 1;
   uint32_t* status = nullptr;
 };
 

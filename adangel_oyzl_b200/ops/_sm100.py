@@ -189,8 +189,7 @@ def kernel_metadata(variant: str, m: int, n: int, k: int) -> dict:
         m_pad = (m + 15) // 16 * 16
         common.update(mma_family="tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32",
                       kernel_symbol="gemm_o2_skinny_kernel", stages=4, threads=192, tile=[m_pad, 128],
-                      persistent=False, mma_shape=[128, m_pad, 64], scale_format="UE8M0", weight_copy=False,
-                      global_partial_buffer="only when K is split (N < 4096)")
+                      persistent=False, mma_shape=[128, m_pad, 64], scale_format="UE8M0", weight_copy=False)
     else:
         common.update(mma_family="tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32",
                       kernel_symbol="gemm_acc_kernel<2>", stages=4 if block_n == 256 else 6,
