@@ -277,6 +277,16 @@ __device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
       : "r"(taddr)
       : "memory");
 }
+// 16 lanes x 32 consecutive columns in the 16x256b shape: of every 8-column block k (k = 0..3) thread
+// t receives columns 8k + 2*(t mod 4) and +1 of lane (base lane + t/4) in r[4k], r[4k+1] and of lane
+// (base lane + t/4 + 8) in r[4k+2], r[4k+3].  The base lane is a multiple of 16.  (Measured at about
+// half the bandwidth of the 32x32b shape; used by the micro-benchmarks only.)
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr)
+               : "memory");
+}
 // tcgen05.wait::ld that also names the destination registers of an earlier load, so that no use
 // of those registers can be scheduled ahead of the wait.
 __device__ __forceinline__ void tmem_wait_ld_for(uint32_t (&r)[8]) {

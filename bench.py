@@ -43,8 +43,9 @@ NOMINAL_TFLOPS = {"o0": 2250.0, "o1": 4500.0, "o2": 9000.0}  # dense FP16 / INT8
 # benchmark step (summary kept under profiles/; the 126 MB L2 keeps most of the 64 MiB output on chip)
 NCU_DRAM_TRAFFIC_BYTES = {"o0_int8_to_fp16": 16.8e6, "o0_gemm_f16": 109.1e6, "o1_gemm_i8": 52.1e6,
                           "o2_quantize": 16.8e6, "o2_gemm_mxf4": 32.2e6}
-# every INT32 K32 partial of O1 crosses the tensor-memory read port (128 B/clk/SM measured):
-TMEM_READ_BYTES_PER_CLK = 128.0
+# every INT32 K32 partial of O1 is converted, multiplied and accumulated in FP32 by the epilogue warps:
+# 3 issue cycles per partial per warp (measured in isolation with four warps per scheduler), 4 schedulers per SM
+O1_ISSUE_CYCLES_PER_PARTIAL = 3.0
 
 
 def measured_peaks():
@@ -341,9 +342,11 @@ def run_native_arm(args) -> None:
                 else f"{peaks['source']}: HBM copy"}
 
     if dominant == "o1_gemm_i8" and clocks and clocks.get("sm_mhz"):
-        floor_s = (M * N_PER_GPU * (K // 32) * 4) / (148 * TMEM_READ_BYTES_PER_CLK * clocks["sm_mhz"] * 1e6)
+        partials = M * N_PER_GPU * (K // 32)
+        floor_s = partials * O1_ISSUE_CYCLES_PER_PARTIAL / 32 / (148 * 4 * clocks["sm_mhz"] * 1e6)
         roofline["secondary_bound"] = {
-            "what": "tensor-memory read port: every K32 INT32 partial is drained to registers (literal O1 semantics)",
+            "what": "FP32/INT issue slots of the epilogue: every K32 INT32 partial is converted, scaled and accumulated "
+                    "separately (literal O1 semantics), 3 issue cycles per partial per warp",
             "floor_ms": floor_s * 1e3, "frac_of_floor": floor_s * 1e3 / d["ms"]}
 
     # end to end through the host-buffer C ABI (N = 1 only): pinned A in, Y back, every variant, every step
