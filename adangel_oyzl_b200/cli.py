@@ -45,6 +45,16 @@ def _run(args) -> None:
                          repeats_override=args.repeats, prepared_dir=args.prepared))
 
 
+def _audit(args) -> None:
+    from .audit import audit
+
+    result = audit(args.output)
+    print("\n".join(result["lines"]))
+    print(f"status={result['status']}")
+    if result["status"] != "PASS":
+        raise SystemExit(1)
+
+
 def _prepare(args) -> None:
     from .trace.prepare import prepare_synthetic, prepare_trace
 
@@ -92,6 +102,10 @@ def build_parser() -> argparse.ArgumentParser:
     run.add_argument("--require-native", action="store_true", help="kept for explicit scripts; a run always requires native")
     run.add_argument("--prepared", help="directory of prepared samples (manifest.json) to run instead of synthetic ones")
     run.set_defaults(func=_run)
+
+    audit = commands.add_parser("audit", help="check that every production kernel contains its TMA / tensor-core instruction family")
+    audit.add_argument("--output", help="directory for summary.txt")
+    audit.set_defaults(func=_audit)
 
     prepare = commands.add_parser("prepare", help="quantize samples on the GPU into a prepared directory")
     prepare.add_argument("--output", required=True)

@@ -155,3 +155,18 @@ def test_shard_ranges_cover_exactly():
     assert shard_range(28672, 8, 3) == (3 * 3584, 4 * 3584)
     with pytest.raises(ValueError):
         shard_range(10, 2, 2)
+
+
+def test_instruction_audit_passes(tmp_path):
+    # the counterpart of the reference's scripts/audit_instructions.sh: every production kernel's PTX
+    # (compiled from this project's sources) holds its TMA / tensor-core instruction family
+    import shutil
+
+    if shutil.which("nvcc") is None and not Path("/usr/local/cuda/bin/nvcc").exists():
+        pytest.skip("nvcc not available")
+    from adangel_oyzl_b200.audit import audit
+
+    result = audit(tmp_path)
+    assert result["status"] == "PASS", result["lines"]
+    assert (tmp_path / "summary.txt").read_text().startswith("status=PASS")
+    assert result["kernels"] >= 12
