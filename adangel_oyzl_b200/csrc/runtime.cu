@@ -9,6 +9,8 @@
 #include "common.cuh"
 #include "launch.h"
 
+#include <cstdlib>
+
 namespace adg {
 
 namespace {
@@ -66,6 +68,7 @@ int device_ctx(DeviceCtx** out) {
     if (int rc = init_gemm_acc_attributes()) return rc;
     if (int rc = init_gemm_o1_attributes()) return rc;
     if (int rc = init_gemm_skinny_attributes()) return rc;
+    if (int rc = init_gemm_pair_attributes()) return rc;
     if (int rc = init_gemm_o1_skinny_attributes()) return rc;
     g_ctx[dev] = ctx;
     g_ctx_ready[dev] = true;
@@ -155,6 +158,21 @@ int plan_o0(GemmPlan* plan, const void* a_fp16, const void* w_fp16, float* y, in
   if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a_fp16, M, K,
                                     static_cast<uint64_t>(K) * 2, 128, 64))
     return rc;
+  // opt-in: CTA pairs (cta_group::2) for shapes with at least one full pair tile
+  static const bool pair_enabled = [] { const char* e = getenv("ADG_O0_TWO_CTA"); return e != nullptr && e[0] == '1'; }();
+  if (pair_enabled && M >= o0_pair_tile_m() && N >= o0_pair_tile_n()) {
+    if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, w_fp16, N, K,
+                                      static_cast<uint64_t>(K) * 2, o0_pair_tile_n() / 2, 64))
+      return rc;
+    if (int rc = plan_output(plan, y)) return rc;
+    plan->pair = 1;
+    plan->block_n = o0_pair_tile_n();
+    const long tiles = static_cast<long>((M + o0_pair_tile_m() - 1) / o0_pair_tile_m()) * ((N + o0_pair_tile_n() - 1) / o0_pair_tile_n());
+    const long clusters = ctx->sm_count / 2;
+    plan->grid = static_cast<int>(2 * (tiles < clusters ? tiles : clusters));
+    plan->status = ctx->status;
+    return 0;
+  }
   if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, w_fp16, N, K,
                                     static_cast<uint64_t>(K) * 2, block_n, 64))
     return rc;
@@ -212,6 +230,7 @@ int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const vo
 int run_plan(const GemmPlan& plan, cudaStream_t stream) {
   if (plan.variant == 1) return plan.skinny ? run_gemm_o1_skinny(plan, stream) : run_gemm_o1(plan, stream);
   if (plan.skinny) return run_gemm_o2_skinny(plan, stream);
+  if (plan.pair) return run_gemm_o0_pair(plan, stream);
   return run_gemm_acc(plan, stream);
 }
 
