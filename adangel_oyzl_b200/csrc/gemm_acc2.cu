@@ -1,11 +1,15 @@
-// O0 GEMM on CTA pairs: tcgen05.mma.cta_group::2 over a 256 x 256 output tile.
+// O0 (kind::f16) and O2 (kind::mxf4.block_scale) GEMMs on CTA pairs: tcgen05.mma.cta_group::2 over a
+// 256 x 256 output tile.
 //
 // Two CTAs of a cluster (ranks 0 and 1, on neighbouring SMs) share one tile: each owns 128 rows of A
 // and of Y and the 128 x 256 FP32 accumulator for them in its own tensor memory, and each loads only
 // HALF of the W tile (128 of its 256 rows) into its shared memory; the pair's tensor cores read both
 // halves.  Per 128-byte K slab a CTA therefore brings in 32 KB instead of 48 KB, which buys six
 // pipeline stages instead of four and two thirds of the L2 traffic.  One thread of the even CTA (the
-// leader) issues every MMA for the pair.
+// leader) issues every MMA for the pair.  For O2 every CTA also loads the scale factors of its own 128
+// rows of A and of all 256 rows of the W tile (through 2-D tensor maps over the tiled scale arrays, so
+// that these loads, too, can signal the leader's barrier), and one more thread of the leader issues the
+// shared -> tensor-memory copies, which run in both CTAs, each from its own shared memory.
 //
 // Protocol (all mbarriers live in each CTA's shared memory at the same offsets):
 //   full[s]        the LEADER's barrier collects the bytes of all four TMA loads of a stage: the
@@ -14,9 +18,11 @@
 //   tmem_full[a]   every CTA's epilogue waits on its own; the leader commits to both
 //   tmem_empty[a]  the LEADER's barrier counts the epilogue warps of both CTAs (the follower's warps
 //                  arrive remotely)
-// Opt-in (environment variable read by the planner); the single-CTA kernel stays the default.
+//   sf_full[s]     (O2) the leader's copier thread commits the stage's scale-factor copies to it
 // All waits are bounded (see common.cuh); the two cluster-wide barriers at start and end are reached
 // by every thread after its bounded loops.
+#include <cstdio>
+
 #include "common.cuh"
 #include "launch.h"
 
@@ -27,20 +33,33 @@ namespace {
 constexpr int kBlockM = 128;     // rows per CTA
 constexpr int kBlockN = 256;     // columns of the pair's tile
 constexpr int kHalfN = kBlockN / 2;
-constexpr int kStages = 6;
 constexpr int kTileA = kBlockM * 128;
 constexpr int kTileB = kHalfN * 128;
-constexpr int kStageBytes = kTileA + kTileB;
-constexpr int kAccStages = 2;
 constexpr int kEpiWarps = 8;
+constexpr int kSfWarp = 2 + kEpiWarps;
 constexpr int kThreads = (2 + kEpiWarps + 2) * 32;
 constexpr int kStagingPerWarp = 2048;
 constexpr int kStagingBytes = kEpiWarps * kStagingPerWarp;
-constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 1024;
 constexpr int kGroupM = 4;  // tile rasterisation: sweep 4 row-pairs before moving to the next column block
-static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
 
-enum : uint32_t { kTagEmpty = 0x4100, kTagFull = 0x4200, kTagTmemEmpty = 0x4300, kTagTmemFull = 0x4400 };
+template <int KIND>
+struct PairCfg {
+  static constexpr bool kScaled = KIND == 2;
+  static constexpr int kStages = kScaled ? 5 : 6;
+  static constexpr int kElemsPerStage = kScaled ? 256 : 64;  // K elements covered by 128 bytes
+  static constexpr int kSfa = kScaled ? 1024 : 0;            // own 128 rows: two 512-byte atoms (8 K32 blocks)
+  static constexpr int kSfb = kScaled ? 2048 : 0;            // all 256 rows of the W tile
+  static constexpr int kStageBytes = kTileA + kTileB + kSfa + kSfb;
+  static constexpr int kAccStages = kScaled ? 1 : 2;
+  static constexpr int kSfColsPerStage = kScaled ? 8 + 2 * (kBlockN / 32) : 0;
+  static constexpr int kSfColBase = kAccStages * kBlockN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 1024;
+  static_assert(kStageBytes % 1024 == 0, "stages keep the 1024-byte alignment of the swizzled tiles");
+  static_assert(kSfColBase + kStages * kSfColsPerStage <= 512, "tensor memory over-subscribed");
+  static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
+};
+
+enum : uint32_t { kTagEmpty = 0x4100, kTagFull = 0x4200, kTagTmemEmpty = 0x4300, kTagTmemFull = 0x4400, kTagSfFull = 0x4500 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -86,10 +105,44 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, u
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_mxf4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate, uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// In both CTAs: 32 rows x 16 bytes of the CTA's own shared memory into 4 columns of its own tensor
+// memory, replicated into the four 32-lane quarters.
+__device__ __forceinline__ void tmem_cp_pair_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
 // arrive on `cluster_addr` (any CTA of the cluster) when the pair's MMAs issued so far have completed
 __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
 }
+
+// Optional stall accounting (compile with -DADG_PAIR_PROF): cycles each role of cluster 0 spends in
+// its waits, printed when the role ends.
+#ifdef ADG_PAIR_PROF
+#define PROF_DECL(...) long long __VA_ARGS__
+#define PROF_WAIT(ctr, call)       \
+  do {                             \
+    const long long t_ = clock64(); \
+    ok = (call);                   \
+    ctr += clock64() - t_;         \
+  } while (0)
+#define PROF_PRINT(...) \
+  if (cluster_id == 0) printf(__VA_ARGS__)
+#else
+#define PROF_DECL(...)
+#define PROF_WAIT(ctr, call) ok = (call)
+#define PROF_PRINT(...)
+#endif
 
 struct TileCoord {
   int m_pair, n_blk;
@@ -106,19 +159,23 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_mp, int num_n)
   return t;
 }
 
+template <int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_o0_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                    const __grid_constant__ CUtensorMap tm_y, float* __restrict__ y, int M, int N, int K, int ldy,
-                    int use_tma_store, uint32_t* status) {
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_sfa,
+                 const __grid_constant__ CUtensorMap tm_sfb, float* __restrict__ y, int M, int N, int K, int ldy,
+                 int use_tma_store, uint32_t* status) {
+  using Cfg = PairCfg<KIND>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* staging = smem + kStages * kStageBytes;
+  uint8_t* staging = smem + Cfg::kStages * Cfg::kStageBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kStagingBytes);
   uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + kStages;
-  uint64_t* tmem_full_bar = bars + 2 * kStages;
-  uint64_t* tmem_empty_bar = tmem_full_bar + kAccStages;
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + kAccStages);
+  uint64_t* empty_bar = bars + Cfg::kStages;
+  uint64_t* sf_full_bar = bars + 2 * Cfg::kStages;  // (O2) the stage's scale factors are in tensor memory
+  uint64_t* tmem_full_bar = bars + 3 * Cfg::kStages;
+  uint64_t* tmem_empty_bar = tmem_full_bar + Cfg::kAccStages;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + Cfg::kAccStages);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -132,14 +189,15 @@ gemm_o0_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int num_mp = (M + 2 * kBlockM - 1) / (2 * kBlockM);
   const int num_n = (N + kBlockN - 1) / kBlockN;
   const int num_tiles = num_mp * num_n;
-  const int num_kb = (K + 63) / 64;
+  const int num_kb = (K + Cfg::kElemsPerStage - 1) / Cfg::kElemsPerStage;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
+      mbar_init(&sf_full_bar[s], 1);
     }
-    for (int a = 0; a < kAccStages; ++a) {
+    for (int a = 0; a < Cfg::kAccStages; ++a) {
       mbar_init(&tmem_full_bar[a], 1);
       mbar_init(&tmem_empty_bar[a], 2 * kEpiWarps);
     }
@@ -150,6 +208,10 @@ gemm_o0_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b);
     tma_prefetch_desc(&tm_y);
+    if constexpr (Cfg::kScaled) {
+      tma_prefetch_desc(&tm_sfa);
+      tma_prefetch_desc(&tm_sfb);
+    }
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_base_slot, 512);
@@ -168,23 +230,34 @@ gemm_o0_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       uint32_t phase = 0;
       bool ok = true;
       const uint32_t full_leader = map_to_cta(smem_u32(full_bar), 0);
+      PROF_DECL(w_empty = 0, t_start = clock64());
       for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
         const TileCoord tc = tile_coord(tile, num_mp, num_n);
-        const int row0 = (tc.m_pair * 2 + static_cast<int>(rank)) * kBlockM;
+        const int m_blk = tc.m_pair * 2 + static_cast<int>(rank);
+        const int row0 = m_blk * kBlockM;
         const int wrow0 = tc.n_blk * kBlockN + static_cast<int>(rank) * kHalfN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage);
+          PROF_WAIT(w_empty, mbar_wait(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage));
           if (!ok) break;
-          uint8_t* st = smem + stage * kStageBytes;
-          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);
-          tma_load_2d_pair(st, &tm_a, full_leader + stage * 8, kb * 64, row0);
-          tma_load_2d_pair(st + kTileA, &tm_b, full_leader + stage * 8, kb * 64, wrow0);
-          if (++stage == kStages) {
+          uint8_t* st = smem + stage * Cfg::kStageBytes;
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
+          const uint32_t bar = full_leader + stage * 8;
+          const int x = kb * (KIND == 0 ? 64 : 128);  // tensor-map elements: halves or bytes
+          tma_load_2d_pair(st, &tm_a, bar, x, row0);
+          tma_load_2d_pair(st + kTileA, &tm_b, bar, x, wrow0);
+          if constexpr (Cfg::kScaled) {
+            // the scale maps are [row block][32-bit words of the block's atoms]: 256 words = the two
+            // atoms of this 256-element K slab
+            tma_load_2d_pair(st + kTileA + kTileB, &tm_sfa, bar, kb * 256, m_blk);
+            tma_load_2d_pair(st + kTileA + kTileB + Cfg::kSfa, &tm_sfb, bar, kb * 256, tc.n_blk * 2);
+          }
+          if (++stage == Cfg::kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
       }
+      PROF_PRINT("producer rank %u: total %lld, waiting for a free stage %lld\n", rank, clock64() - t_start, w_empty);
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (leader CTA only) -----------------------------
@@ -193,29 +266,49 @@ gemm_o0_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       uint32_t phase = 0;
       int local_tile = 0;
       bool ok = true;
-      constexpr uint32_t idesc = make_idesc(1, kFmtF16, kFmtF16, 2 * kBlockM, kBlockN);
       const uint32_t empty_own = smem_u32(empty_bar), empty_peer = map_to_cta(empty_own, peer);
       const uint32_t tfull_own = smem_u32(tmem_full_bar), tfull_peer = map_to_cta(tfull_own, peer);
+      PROF_DECL(w_full = 0, w_sf = 0, w_acc = 0, t_start = clock64());
       for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++local_tile) {
-        const int acc = local_tile % kAccStages;
-        const uint32_t acc_phase = static_cast<uint32_t>(local_tile / kAccStages) & 1u;
-        ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, env, kTagTmemEmpty | acc);
+        const int acc = local_tile % Cfg::kAccStages;
+        const uint32_t acc_phase = static_cast<uint32_t>(local_tile / Cfg::kAccStages) & 1u;
+#ifndef ADG_PAIR_NOACCWAIT
+        PROF_WAIT(w_acc, mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, env, kTagTmemEmpty | acc));
         if (!ok) break;
+#endif
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBlockN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | stage);
+          PROF_WAIT(w_full, mbar_wait(&full_bar[stage], phase, env, kTagFull | stage));
           if (!ok) break;
           tc_fence_after();
-          const uint32_t st = smem_u32(smem + stage * kStageBytes);
+          const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
           const uint64_t adesc = make_desc_sw128(st);
           const uint64_t bdesc = make_desc_sw128(st + kTileA);
+          if constexpr (Cfg::kScaled) {
+#ifndef ADG_PAIR_NOSFWAIT
+            PROF_WAIT(w_sf, mbar_wait(&sf_full_bar[stage], phase, env, kTagSfFull | stage));
+            if (!ok) break;
+            tc_fence_after();
+#endif
+            const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
+            const uint32_t sfb_t = sfa_t + 8;
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) umma_f16_pair(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
+            for (int ks = 0; ks < 4; ++ks) {
+              const uint32_t sf_id = (ks & 1) * 2;
+              const uint32_t idesc = make_idesc_mxf4(2 * kBlockM, kBlockN, sf_id, sf_id);
+              umma_mxf4_pair(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u,
+                             sfa_t + (ks >> 1) * 4, sfb_t + (ks >> 1) * (kBlockN / 32));
+            }
+          } else {
+            constexpr uint32_t idesc = make_idesc(1, kFmtF16, kFmtF16, 2 * kBlockM, kBlockN);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) umma_f16_pair(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
           // both CTAs' copies of the stage may be refilled once these MMAs have read them
           umma_commit_pair(empty_own + stage * 8);
           umma_commit_pair(empty_peer + stage * 8);
-          if (++stage == kStages) {
+          if (++stage == Cfg::kStages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -223,6 +316,47 @@ gemm_o0_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (ok) {
           umma_commit_pair(tfull_own + acc * 8);
           umma_commit_pair(tfull_peer + acc * 8);
+        }
+      }
+      PROF_PRINT("MMA thread: total %lld, waiting for data %lld, for scale copies %lld, for a free accumulator %lld\n",
+                 clock64() - t_start, w_full, w_sf, w_acc);
+    }
+  } else if (warp == kSfWarp) {
+    // ------------------------------- scale-factor copier (O2, leader CTA only) ----------------
+    if constexpr (Cfg::kScaled) {
+      if (lane == 0 && rank == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const uint32_t sf_full_own = smem_u32(sf_full_bar);
+        for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            // both CTAs' scale factors of the stage have landed; the stage's tensor-memory scale
+            // columns were last read by MMAs that completed before the stage was handed back
+            ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | 0x80 | stage);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
+            const uint32_t sfa_s = st + kTileA + kTileB;
+            const uint32_t sfb_s = sfa_s + Cfg::kSfa;
+            const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
+            const uint32_t sfb_t = sfa_t + 8;
+#ifndef ADG_PAIR_NOSFCP
+#pragma unroll
+            for (int ka = 0; ka < 2; ++ka) {
+              tmem_cp_pair_32x128b_warpx4(sfa_t + ka * 4, make_desc_sf(sfa_s + ka * 512));
+#pragma unroll
+              for (int rb = 0; rb < kBlockN / 128; ++rb) {
+                tmem_cp_pair_32x128b_warpx4(sfb_t + ka * (kBlockN / 32) + rb * 4, make_desc_sf(sfb_s + rb * 1024 + ka * 512));
+              }
+            }
+#endif
+            umma_commit_pair(sf_full_own + stage * 8);
+            if (++stage == Cfg::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
         }
       }
     }
@@ -238,11 +372,12 @@ gemm_o0_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const uint32_t tempty_leader = map_to_cta(smem_u32(tmem_empty_bar), 0);
     int local_tile = 0;
     bool ok = true;
+    PROF_DECL(w_tfull = 0, t_start = clock64());
     for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++local_tile) {
       const TileCoord tc = tile_coord(tile, num_mp, num_n);
-      const int acc = local_tile % kAccStages;
-      const uint32_t acc_phase = static_cast<uint32_t>(local_tile / kAccStages) & 1u;
-      ok = mbar_wait(&tmem_full_bar[acc], acc_phase, env, kTagTmemFull | acc);
+      const int acc = local_tile % Cfg::kAccStages;
+      const uint32_t acc_phase = static_cast<uint32_t>(local_tile / Cfg::kAccStages) & 1u;
+      PROF_WAIT(w_tfull, mbar_wait(&tmem_full_bar[acc], acc_phase, env, kTagTmemFull | acc));
       if (!ok) break;
       tc_fence_after();
       const int row0 = (tc.m_pair * 2 + static_cast<int>(rank)) * kBlockM + q * 32;
@@ -288,6 +423,10 @@ gemm_o0_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
     }
     if (lane == 0) bulk_wait_group<0>();
+    if (lane == 0 && warp == 2) {
+      PROF_PRINT("epilogue warp 2 rank %u: total %lld, waiting for an accumulator %lld (%d tiles)\n", rank,
+                 clock64() - t_start, w_tfull, local_tile);
+    }
   }
 
   // neither CTA may leave (or release tensor memory) while the other can still read its shared
@@ -299,19 +438,12 @@ gemm_o0_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
 }
 
-}  // namespace
-
-int init_gemm_pair_attributes() {
-  return check_cuda(cudaFuncSetAttribute(gemm_o0_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
-                    "cudaFuncSetAttribute(gemm_o0_pair_kernel)");
-}
-
-// The plan's tm_b must have 128-row boxes (one CTA's half of the W tile); grid = 2 x clusters.
-int run_gemm_o0_pair(const GemmPlan& p, cudaStream_t stream) {
+template <int KIND>
+int launch_pair(const GemmPlan& p, cudaStream_t stream) {
   cudaLaunchConfig_t config{};
   config.gridDim = dim3(static_cast<unsigned>(p.grid));
   config.blockDim = dim3(kThreads);
-  config.dynamicSmemBytes = kSmemBytes;
+  config.dynamicSmemBytes = PairCfg<KIND>::kSmemBytes;
   config.stream = stream;
   cudaLaunchAttribute attr{};
   attr.id = cudaLaunchAttributeClusterDimension;
@@ -320,12 +452,32 @@ int run_gemm_o0_pair(const GemmPlan& p, cudaStream_t stream) {
   attr.val.clusterDim.z = 1;
   config.attrs = &attr;
   config.numAttrs = 1;
-  return check_cuda(cudaLaunchKernelEx(&config, gemm_o0_pair_kernel, p.tm_a, p.tm_b, p.tm_y, p.y, p.M, p.N, p.K, p.ldy,
-                                       p.use_tma_store, p.status),
-                    "gemm_o0_pair_kernel launch");
+  return check_cuda(cudaLaunchKernelEx(&config, gemm_pair_kernel<KIND>, p.tm_a, p.tm_b, p.tm_y, p.tm_sfa, p.tm_sfb, p.y,
+                                       p.M, p.N, p.K, p.ldy, p.use_tma_store, p.status),
+                    "gemm_pair_kernel launch");
 }
 
-int o0_pair_tile_m() { return 2 * kBlockM; }
-int o0_pair_tile_n() { return kBlockN; }
+}  // namespace
+
+int init_gemm_pair_attributes() {
+  if (int rc = check_cuda(cudaFuncSetAttribute(gemm_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               PairCfg<0>::kSmemBytes),
+                          "cudaFuncSetAttribute(gemm_pair_kernel<0>)"))
+    return rc;
+  return check_cuda(cudaFuncSetAttribute(gemm_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         PairCfg<2>::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm_pair_kernel<2>)");
+}
+
+// The plan's tm_b must have 128-row boxes (one CTA's half of the W tile); grid = 2 x clusters; an O2
+// plan also carries the tensor maps of the two tiled scale arrays.
+int run_gemm_pair(const GemmPlan& p, cudaStream_t stream) {
+  if (p.variant == 0) return launch_pair<0>(p, stream);
+  if (p.variant == 2) return launch_pair<2>(p, stream);
+  return fail("run_gemm_pair: plan is not an O0/O2 plan");
+}
+
+int pair_tile_m() { return 2 * kBlockM; }
+int pair_tile_n() { return kBlockN; }
 
 }  // namespace adg

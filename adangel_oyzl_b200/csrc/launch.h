@@ -65,6 +65,7 @@ struct GemmPlan {
   int grid = 0;
   int use_tma_store = 0;
   CUtensorMap tm_a, tm_b, tm_y;
+  CUtensorMap tm_sfa, tm_sfb;  // O2 on CTA pairs: [row block][32-bit words] views of the tiled scale arrays
   const void* a_scale = nullptr;   // O1: float [M]
   const void* w_scale = nullptr;   // O1: natural UE8M0 [N, K/32]
   const void* sfa = nullptr;       // O2: tiled A scales
@@ -74,7 +75,7 @@ struct GemmPlan {
   // decode-sized O1/O2 (M <= 64): operand-swapped kernels; tm_a = A map, tm_b = W map; `grid_y`
   // is the number of 16-row slices of A (O1 only)
   int skinny = 0, grid_y = 1;
-  int pair = 0;  // O0 on CTA pairs (cta_group::2): tm_b has 128-row boxes, grid = 2 x clusters
+  int pair = 0;  // O0/O2 on CTA pairs (cta_group::2): tm_b has 128-row boxes, grid = 2 x clusters
   uint32_t* status = nullptr;
 };
 
@@ -94,9 +95,9 @@ int o1_block_n();      // W rows per O1 tile
 int o1_ctas_per_sm();  // resident O1 CTAs per SM
 int init_gemm_skinny_attributes();
 int init_gemm_pair_attributes();
-int run_gemm_o0_pair(const GemmPlan& plan, cudaStream_t stream);
-int o0_pair_tile_m();
-int o0_pair_tile_n();
+int run_gemm_pair(const GemmPlan& plan, cudaStream_t stream);
+int pair_tile_m();
+int pair_tile_n();
 int plan_o2_skinny(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const void* w_mxfp4, const void* sfb_tiled,
                    float* y, int M, int N, int K, int ldy);
 int run_gemm_o2_skinny(const GemmPlan& plan, cudaStream_t stream);

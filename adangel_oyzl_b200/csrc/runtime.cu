@@ -113,6 +113,45 @@ int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_b
 
 namespace {
 
+// [rows][row_bytes] view of a byte array in 32-bit words, no swizzle: used for the tiled scale arrays,
+// whose 512-byte atoms are copied as they lie.  The box is `box_rows` x `box_bytes`.
+int encode_word_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                       uint32_t box_bytes) {
+  if (g_encode == nullptr) return fail("tensor-map encoder not initialised");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return fail("tensor base address must be 16-byte aligned");
+  if ((row_bytes & 15u) != 0 || box_bytes % 16u != 0 || box_bytes / 4u > 256u) return fail("unsupported word-map geometry");
+  const cuuint64_t dims[2] = {row_bytes / 4u, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {box_bytes / 4u, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult res = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box,
+                                elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(res)));
+  return 0;
+}
+
+// CTA pairs (cta_group::2) are used when the environment asks for them and the shape has at least
+// one full pair tile.
+bool pair_enabled(int M, int N) {
+  static const bool enabled = [] {
+    const char* e = getenv("ADG_TWO_CTA");
+    return e != nullptr && e[0] == '1';
+  }();
+  return enabled && M >= pair_tile_m() && N >= pair_tile_n();
+}
+
+int finish_pair_plan(GemmPlan* plan, int sm_count, uint32_t* status) {
+  plan->pair = 1;
+  plan->block_n = pair_tile_n();
+  const long tiles = static_cast<long>((plan->M + pair_tile_m() - 1) / pair_tile_m()) *
+                     ((plan->N + pair_tile_n() - 1) / pair_tile_n());
+  const long clusters = sm_count / 2;
+  plan->grid = static_cast<int>(2 * (tiles < clusters ? tiles : clusters));
+  plan->status = status;
+  return 0;
+}
+
 int check_shape(int M, int N, int K, int ldy) {
   if (M <= 0 || N <= 0 || K <= 0) return fail("M, N, and K must be positive");
   if (K % 64 != 0) return fail("K must be divisible by 64");
@@ -158,20 +197,12 @@ int plan_o0(GemmPlan* plan, const void* a_fp16, const void* w_fp16, float* y, in
   if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a_fp16, M, K,
                                     static_cast<uint64_t>(K) * 2, 128, 64))
     return rc;
-  // opt-in: CTA pairs (cta_group::2) for shapes with at least one full pair tile
-  static const bool pair_enabled = [] { const char* e = getenv("ADG_O0_TWO_CTA"); return e != nullptr && e[0] == '1'; }();
-  if (pair_enabled && M >= o0_pair_tile_m() && N >= o0_pair_tile_n()) {
+  if (pair_enabled(M, N)) {
     if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, w_fp16, N, K,
-                                      static_cast<uint64_t>(K) * 2, o0_pair_tile_n() / 2, 64))
+                                      static_cast<uint64_t>(K) * 2, pair_tile_n() / 2, 64))
       return rc;
     if (int rc = plan_output(plan, y)) return rc;
-    plan->pair = 1;
-    plan->block_n = o0_pair_tile_n();
-    const long tiles = static_cast<long>((M + o0_pair_tile_m() - 1) / o0_pair_tile_m()) * ((N + o0_pair_tile_n() - 1) / o0_pair_tile_n());
-    const long clusters = ctx->sm_count / 2;
-    plan->grid = static_cast<int>(2 * (tiles < clusters ? tiles : clusters));
-    plan->status = ctx->status;
-    return 0;
+    return finish_pair_plan(plan, ctx->sm_count, ctx->status);
   }
   if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, w_fp16, N, K,
                                     static_cast<uint64_t>(K) * 2, block_n, 64))
@@ -221,6 +252,17 @@ int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const vo
   const uint64_t kbytes = static_cast<uint64_t>(K) / 2;
   if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_mxfp4, M, kbytes, kbytes, 128, 128))
     return rc;
+  if (pair_enabled(M, N)) {
+    if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_mxfp4, N, kbytes, kbytes,
+                                      pair_tile_n() / 2, 128))
+      return rc;
+    // tiled scales: [row block of 128][atoms along K][512 bytes]; a 256-element K slab is two atoms
+    const uint64_t row_bytes = static_cast<uint64_t>(((K / 32 + 7) / 8) * 2) * 512u;
+    if (int rc = encode_word_map_2d(&plan->tm_sfa, sfa_tiled, (M + 127) / 128, row_bytes, 1, 1024)) return rc;
+    if (int rc = encode_word_map_2d(&plan->tm_sfb, sfb_tiled, (N + 127) / 128, row_bytes, 2, 1024)) return rc;
+    if (int rc = plan_output(plan, y)) return rc;
+    return finish_pair_plan(plan, ctx->sm_count, ctx->status);
+  }
   if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_mxfp4, N, kbytes, kbytes, block_n, 128))
     return rc;
   if (int rc = plan_output(plan, y)) return rc;
@@ -230,7 +272,7 @@ int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const vo
 int run_plan(const GemmPlan& plan, cudaStream_t stream) {
   if (plan.variant == 1) return plan.skinny ? run_gemm_o1_skinny(plan, stream) : run_gemm_o1(plan, stream);
   if (plan.skinny) return run_gemm_o2_skinny(plan, stream);
-  if (plan.pair) return run_gemm_o0_pair(plan, stream);
+  if (plan.pair) return run_gemm_pair(plan, stream);
   return run_gemm_acc(plan, stream);
 }
 
