@@ -30,6 +30,17 @@ REQUIRED = {
                               r"tcgen05\.mma\.cta_group::1\.kind::mxf4\.block_scale", r"tcgen05\.cp\.cta_group::1\.32x128b\.warpx4",
                               r"tcgen05\.ld\.sync\.aligned\.32x32b"],
                              "O2 GEMM: TMA loads, block-scaled MXFP4 MMA, scale-factor copies, tensor-memory loads"),
+    "gemm_o1_bf16_kernel": ([r"cp\.async\.bulk\.tensor\.2d\.shared::cluster\.global", r"tcgen05\.mma\.cta_group::1\.kind::f16",
+                             r"tcgen05\.ld\.sync\.aligned\.32x32b", r"setmaxnreg"],
+                            "O1 GEMM on BF16 operands: TMA loads, kind::f16 MMA, tensor-memory loads, register re-balancing"),
+    "gemm_pair_kernelILi0E": ([r"cp\.async\.bulk\.tensor\.2d\.cta_group::2\.shared::cluster\.global",
+                               r"tcgen05\.mma\.cta_group::2\.kind::f16", r"tcgen05\.commit\.cta_group::2",
+                               r"barrier\.cluster\.arrive", r"cp\.async\.bulk\.tensor\.2d\.global\.shared::cta"],
+                              "O0 GEMM on CTA pairs: pair TMA loads, cta_group::2 MMA and commits, cluster barrier, TMA stores"),
+    "gemm_pair_kernelILi2E": ([r"cp\.async\.bulk\.tensor\.2d\.cta_group::2\.shared::cluster\.global",
+                               r"tcgen05\.mma\.cta_group::2\.kind::mxf4\.block_scale",
+                               r"tcgen05\.cp\.cta_group::2\.32x128b\.warpx4", r"tcgen05\.commit\.cta_group::2"],
+                              "O2 GEMM on CTA pairs: pair TMA loads, cta_group::2 block-scaled MMA, scale-factor copies, commits"),
     "gemm_o2_skinny_kernel": ([r"cp\.async\.bulk\.tensor\.2d\.shared::cluster\.global",
                                r"tcgen05\.mma\.cta_group::1\.kind::mxf4\.block_scale"],
                               "O2 decode GEMM: TMA loads, block-scaled MXFP4 MMA"),

@@ -115,6 +115,24 @@ int adg_mxfp4_to_int8(const void* w_mxfp4, void* out_int8, int64_t rows, int64_t
   return launch_mxfp4_to_int8(w_mxfp4, out_int8, rows, K, as_stream(stream)) ? fail("mxfp4_to_int8 launch failed") : 0;
 }
 
+int adg_mxfp4_to_bf16_scaled(const void* w_mxfp4, const void* w_scale, void* out_bf16, void* range_flag, int64_t rows,
+                             int64_t K, void* stream) {
+  if (int rc = check_conv_dims(rows, K)) return rc;
+  if (range_flag == nullptr) return fail("range_flag must not be NULL");
+  return launch_mxfp4_to_bf16_scaled(w_mxfp4, w_scale, out_bf16, range_flag, rows, K, as_stream(stream))
+             ? fail("mxfp4_to_bf16_scaled launch failed")
+             : 0;
+}
+
+int adg_int8_to_bf16(const void* a_int8, const void* a_scale, void* out_bf16, void* range_flag, int64_t rows, int64_t K,
+                     void* stream) {
+  if (int rc = check_conv_dims(rows, K)) return rc;
+  if (range_flag == nullptr) return fail("range_flag must not be NULL");
+  return launch_int8_to_bf16(a_int8, a_scale, out_bf16, range_flag, rows, K, as_stream(stream))
+             ? fail("int8_to_bf16 launch failed")
+             : 0;
+}
+
 int64_t adg_o2_tiled_scale_bytes(int64_t rows, int64_t K) { return tiled_scale_bytes(rows, K); }
 
 int adg_o2_quantize_activation(const void* a_int8, const void* a_scale, void* a_mxfp4, void* sf_natural,
@@ -162,6 +180,13 @@ int adg_gemm_o1(const void* a_int8, const void* a_scale, const void* w_int8, con
                 int32_t* partial_dump, int M, int N, int K, int ldy, void* stream) {
   GemmPlan plan;
   if (int rc = plan_o1(&plan, a_int8, a_scale, w_int8, w_scale, y, partial_dump, M, N, K, ldy)) return rc;
+  return run_plan(plan, as_stream(stream));
+}
+
+int adg_gemm_o1_bf16(const void* a_bf16, const void* a_scale, const void* w_bf16, float* y, const void* range_flag, int M,
+                     int N, int K, int ldy, void* stream) {
+  GemmPlan plan;
+  if (int rc = plan_o1_bf16(&plan, a_bf16, a_scale, w_bf16, y, range_flag, M, N, K, ldy)) return rc;
   return run_plan(plan, as_stream(stream));
 }
 

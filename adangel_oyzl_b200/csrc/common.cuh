@@ -20,6 +20,7 @@ enum StatusCode : uint32_t {
   kStatusOk = 0,
   kStatusWaitTimeout = 1,
   kStatusBadLaunch = 2,
+  kStatusOperandRange = 3,  // O1 BF16-operand kernel launched on operands outside its exact range
 };
 constexpr int kStatusWords = 8;
 constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s

@@ -6,9 +6,13 @@
 //   mxfp4_to_fp16      O0 weight conversion    (reference csrc/sm120/conversion.cu:10-23)
 //   int8_to_fp16       O0 activation conversion (reference csrc/sm120/conversion.cu:25-37)
 //   mxfp4_to_int8      O1 weight conversion    (reference csrc/sm120/conversion.cu:39-50)
+//   mxfp4_to_bf16_scaled / int8_to_bf16   operands of the O1 kernel that takes the weight scale through the
+//                      tensor core (gemm_o1_bf16.cu); no reference counterpart
 //   o2_quantize        O2 activation re-quantization fused with the scale-factor re-layout
 //                      (reference csrc/sm120/o2_cutlass.cu:207-259 and :261-274)
 //   o2_tile_scales     O2 weight-scale re-layout (reference csrc/sm120/o2_cutlass.cu:261-274)
+#include <cuda_bf16.h>
+
 #include "codecs.cuh"
 #include "launch.h"
 
@@ -102,6 +106,72 @@ __global__ void __launch_bounds__(kThreads) int8_to_fp16_kernel(const uint2* __r
     o[3] = *reinterpret_cast<const uint32_t*>(&h3);
     out[i] = make_uint4(o[0], o[1], o[2], o[3]);
   }
+}
+
+// ---- O1 (BF16 operands) weight: packed E2M1 + UE8M0 -> BF16 of e2m1 * 2^(scale-127) ------------
+// Exact: the value has two significant bits.  One 32-bit word (8 elements) per thread per step.
+// A scale code outside [kO1MinScaleCode, kO1MaxScaleCode] sets bit 0 of *range_flag.
+__global__ void __launch_bounds__(kThreads) mxfp4_to_bf16_scaled_kernel(const uint32_t* __restrict__ packed,
+                                                                        const uint8_t* __restrict__ scales,
+                                                                        uint4* __restrict__ out, long words,
+                                                                        uint32_t* __restrict__ range_flag) {
+  const long base = (static_cast<long>(blockIdx.x) * kUnroll) * kThreads + threadIdx.x;
+  bool bad = false;
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const long i = base + static_cast<long>(u) * kThreads;
+    if (i >= words) continue;
+    const uint32_t w = __ldg(packed + i);
+    const uint32_t code = __ldg(scales + (i >> 2));
+    bad |= code < kO1MinScaleCode || code > kO1MaxScaleCode;
+    const float s = __uint_as_float((code == 0u ? 1u : code) << 23);  // 2^(code-127); unused when out of range
+    uint32_t o[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const float2 f = __half22float2(e2m1x2_to_half2((w >> (8 * b)) & 0xFFu));
+      const __nv_bfloat162 v = __floats2bfloat162_rn(f.x * s, f.y * s);
+      o[b] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(range_flag, 1u);
+}
+
+// ---- O1 (BF16 operands) activation: INT8 -> BF16 of the integer itself, exact ------------------
+// Eight elements per thread per step.  The first `rows` threads of the grid also check the row
+// scales: one outside [2^kO1MinAScaleExp, 2^kO1MaxAScaleExp] (or not finite) sets bit 1 of *range_flag.
+__global__ void __launch_bounds__(kThreads) int8_to_bf16_kernel(const uint2* __restrict__ in,
+                                                                const float* __restrict__ row_scale,
+                                                                uint4* __restrict__ out, long octs, long rows,
+                                                                uint32_t* __restrict__ range_flag) {
+  const long base = (static_cast<long>(blockIdx.x) * kUnroll) * kThreads + threadIdx.x;
+  uint2 v[kUnroll];
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const long i = base + static_cast<long>(u) * kThreads;
+    if (i < octs) v[u] = __ldg(in + i);
+  }
+  bool bad = false;
+  const long gid = static_cast<long>(blockIdx.x) * kThreads + threadIdx.x;
+  if (gid < rows) {
+    const float s = __ldg(row_scale + gid);
+    bad = !(s >= exp2f(static_cast<float>(kO1MinAScaleExp)) && s <= exp2f(static_cast<float>(kO1MaxAScaleExp)));
+  }
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const long i = base + static_cast<long>(u) * kThreads;
+    if (i >= octs) continue;
+    float lo[4], hi[4];
+    int8x4_to_float4(v[u].x, lo);
+    int8x4_to_float4(v[u].y, hi);
+    const __nv_bfloat162 b0 = __floats2bfloat162_rn(lo[0], lo[1]);
+    const __nv_bfloat162 b1 = __floats2bfloat162_rn(lo[2], lo[3]);
+    const __nv_bfloat162 b2 = __floats2bfloat162_rn(hi[0], hi[1]);
+    const __nv_bfloat162 b3 = __floats2bfloat162_rn(hi[2], hi[3]);
+    out[i] = make_uint4(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1),
+                        *reinterpret_cast<const uint32_t*>(&b2), *reinterpret_cast<const uint32_t*>(&b3));
+  }
+  if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(range_flag, 2u);
 }
 
 // ---- O1 weight: packed E2M1 -> INT8 (2*E2M1) ---------------------------------------------------
@@ -236,6 +306,27 @@ int launch_int8_to_fp16(const void* in, const void* row_scale, void* out, long r
   int8_to_fp16_kernel<<<grid_for(octs, kThreads * kUnroll), kThreads, 0, stream>>>(
       static_cast<const uint2*>(in), static_cast<const float*>(row_scale), static_cast<uint4*>(out), octs,
       static_cast<int>(k / 8));
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_mxfp4_to_bf16_scaled(const void* packed, const void* scales, void* out, void* range_flag, long rows, long k,
+                                cudaStream_t stream) {
+  const long words = rows * k / 8;
+  if (words == 0) return 0;
+  mxfp4_to_bf16_scaled_kernel<<<grid_for(words, kThreads * kUnroll), kThreads, 0, stream>>>(
+      static_cast<const uint32_t*>(packed), static_cast<const uint8_t*>(scales), static_cast<uint4*>(out), words,
+      static_cast<uint32_t*>(range_flag));
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_int8_to_bf16(const void* in, const void* row_scale, void* out, void* range_flag, long rows, long k,
+                        cudaStream_t stream) {
+  const long octs = rows * k / 8;
+  if (octs == 0) return 0;
+  // K >= 32, so the grid has at least `rows` threads for the row-scale check
+  int8_to_bf16_kernel<<<grid_for(octs, kThreads * kUnroll), kThreads, 0, stream>>>(
+      static_cast<const uint2*>(in), static_cast<const float*>(row_scale), static_cast<uint4*>(out), octs, rows,
+      static_cast<uint32_t*>(range_flag));
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -1,0 +1,299 @@
+// O1 with the weight scale folded into the tensor-core operand: the K32 partials leave the tensor
+// core already multiplied by 2**(W_scale-128), as FP32, and exact.
+//
+// The O1 recurrence (reference reference/o1.py:16-20, kernel csrc/sm120/o1_gemm.cu:167-333), for every
+// output element and every K32 group g in ascending order:
+//     P   = sum_{k in g} A_int8[m,k] * W_int8[n,k]                         (exact integer, |P| <= 48768)
+//     acc = acc + float(P) * ((A_scale[m] * 2**(W_scale[n,g]-127)) * 0.5)   (FP32, rounded each step)
+// Because the weight's factor is a power of two, RN(float(P) * A_scale * 2**x) = RN(float(P) * 2**x *
+// A_scale) as long as nothing under- or overflows, and float(P) * 2**x is exactly representable.  So
+// the operands are handed to the tensor core as BF16 -- A as the integers themselves (8 significant
+// bits), W as e2m1 * 2**(W_scale-127) (2 significant bits, BF16's 8-bit exponent) -- and one K32
+// group is two kind::f16 MMAs (K = 16 each) with FP32 accumulation: all products and all their partial
+// sums are integer multiples of 2**(W_scale-128) below 2**24 of them, hence exact.  The epilogue is
+// left with one multiply by A_scale[m] and one add per partial and element: no integer-to-float
+// conversion, no per-column factor, no scale ring in shared memory, no scale warp.  Measured at
+// 4096^3: 375 us against 414 us for the INT8-operand kernel, bit-identical; converting A to BF16
+// costs another 18 us per call, and W takes two bytes per element instead of one.
+//
+// Preconditions (checked on the device by the conversion kernels, which set bits in `range_flag`):
+// W scale codes in [48, 208] and A scales in [2**-46, 2**30], so that no intermediate leaves the
+// normal FP32/BF16 range.  When the flag is set this kernel records an error status and returns
+// without computing; the INT8 kernel (gemm_o1.cu) covers every input.
+//
+// Roles (640 threads): warp 0 TMA producer, warp 1 MMA issuer + tensor-memory owner, warps 4-19
+// epilogue (4 per tensor-memory lane quarter, 32 columns each); warps 2-3 only complete the first
+// warp group, which hands its registers to the epilogue.  One 128-byte K slab (64 BF16 = two K32
+// groups = one "pair" of partials) per pipeline stage.
+#include "common.cuh"
+#include "launch.h"
+
+namespace adg {
+
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 128;
+constexpr int kStages = 6;      // A 128 x 128 B + W 128 x 128 B each: two K32 groups
+constexpr int kPairs = 2;       // tensor-memory halves, each holding the partials of two K32 groups
+constexpr int kEpiWarps = 4 * (kBlockN / 32);
+constexpr int kFirstEpiWarp = 4;
+constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
+constexpr int kTile = kBlockM * 128;
+constexpr int kStageBytes = kTile + kBlockN * 128;
+constexpr int kTmemCols = kPairs * 2 * kBlockN;
+constexpr int kEpiRegs = 112;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
+constexpr int kGroupM = 8;
+constexpr uint32_t kFmtBF16 = 1;  // kind::f16 operand format: bfloat16
+static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
+
+enum : uint32_t {
+  kTagEmpty = 0x5100,
+  kTagFull = 0x5200,
+  kTagTmemEmpty = 0x5300,
+  kTagTmemFull = 0x5400,
+};
+
+struct TileCoord {
+  int m_blk, n_blk;
+};
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) {
+  const int per_group = kGroupM * num_n;
+  const int group = tile / per_group;
+  const int first_m = group * kGroupM;
+  const int gsize = min(num_m - first_m, kGroupM);
+  const int in_group = tile - group * per_group;
+  TileCoord t;
+  t.m_blk = first_m + in_group % gsize;
+  t.n_blk = in_group / gsize;
+  return t;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                    const float* __restrict__ a_scale, float* __restrict__ y, const uint32_t* __restrict__ range_flag,
+                    int M, int N, int K, int ldy, uint32_t* status) {
+  // operands outside the exact range: refuse loudly, before any barrier or tensor memory exists
+  if (range_flag != nullptr) {
+    const uint32_t flag = *range_flag;
+    if (flag != 0u) {
+      if (threadIdx.x == 0 && atomicCAS(status, 0u, static_cast<uint32_t>(kStatusOperandRange)) == 0u) {
+        status[1] = flag;
+        status[2] = blockIdx.x;
+        status[3] = 0;
+      }
+      return;
+    }
+  }
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full_bar = empty_bar + kStages;
+  uint64_t* tmem_empty_bar = tmem_full_bar + kPairs;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + kPairs);
+  volatile uint32_t* abort_flag = tmem_base_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t abort_a = smem_u32(const_cast<uint32_t*>(abort_flag));
+  const uint32_t tmem_full_a = smem_u32(tmem_full_bar), tmem_empty_a = smem_u32(tmem_empty_bar);
+  const uint32_t full_a = smem_u32(full_bar), empty_a = smem_u32(empty_bar);
+
+  const int num_m = (M + kBlockM - 1) / kBlockM;
+  const int num_n = (N + kBlockN - 1) / kBlockN;
+  const int num_tiles = num_m * num_n;
+  const int num_pairs = K / 64;  // K is a multiple of 64: K32 groups come in pairs, one pair per stage
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < kPairs; ++s) {
+      mbar_init(&tmem_full_bar[s], 1);
+      mbar_init(&tmem_empty_bar[s], kEpiWarps);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp < kFirstEpiWarp) {
+    reg_dealloc<32>();  // 128 threads x 64 registers returned = 512 threads x 16 registers gained below
+    if (warp == 0) {
+      // ------------------------------- TMA producer -------------------------------------------
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+          const TileCoord tc = tile_coord(tile, num_m, num_n);
+          for (int kb = 0; kb < num_pairs; ++kb) {
+            ok = mbar_wait_a(empty_a + stage * 8, phase ^ 1u, status, abort_a, kTagEmpty | stage);
+            if (!ok) break;
+            uint8_t* st = smem + stage * kStageBytes;
+            mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+            tma_load_2d(st, &tm_a, &full_bar[stage], kb * 64, tc.m_blk * kBlockM);
+            tma_load_2d(st + kTile, &tm_b, &full_bar[stage], kb * 64, tc.n_blk * kBlockN);
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // ------------------------------- MMA issuer -----------------------------------------------
+      if (lane == 0) {
+        int stage = 0, pair = 0;
+        uint32_t phase = 0, pair_phase = 0;
+        bool ok = true;
+        constexpr uint32_t idesc = make_idesc(1, kFmtBF16, kFmtBF16, kBlockM, kBlockN);
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+          for (int kb = 0; ok && kb < num_pairs; ++kb) {
+            ok = mbar_wait_a(full_a + stage * 8, phase, status, abort_a, kTagFull | stage);
+            if (!ok) break;
+            ok = mbar_wait_a(tmem_empty_a + pair * 8, pair_phase ^ 1u, status, abort_a, kTagTmemEmpty | pair);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t st = smem_u32(smem + stage * kStageBytes);
+            const uint64_t adesc = make_desc_sw128(st);
+            const uint64_t bdesc = make_desc_sw128(st + kTile);
+            const uint32_t d = tmem_base + static_cast<uint32_t>(pair * 2 * kBlockN);
+            // each K32 group: two K16 MMAs into a fresh accumulator
+            umma_f16(d, adesc, bdesc, idesc, 0u);
+            umma_f16(d, adesc + 2, bdesc + 2, idesc, 1u);
+            umma_f16(d + kBlockN, adesc + 4, bdesc + 4, idesc, 0u);
+            umma_f16(d + kBlockN, adesc + 6, bdesc + 6, idesc, 1u);
+            umma_commit_a(tmem_full_a + pair * 8);
+            umma_commit_a(empty_a + stage * 8);
+            if (++pair == kPairs) {
+              pair = 0;
+              pair_phase ^= 1u;
+            }
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    }
+  } else {
+    reg_alloc<kEpiRegs>();
+    // ------------------------------- epilogue ---------------------------------------------------
+    // Each warp owns 32 columns of one lane quarter.  The two partials of a pair go to two register
+    // buffers: while one partial is scaled and accumulated, the load of the next is in flight.
+    const int q = warp & 3;                     // tensor-memory lane quarter
+    const int cs = (warp - kFirstEpiWarp) >> 2;  // 32-column slice of the 128-column partial
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(cs * 32);
+    int pair = 0;
+    uint32_t pair_phase = 0;
+    bool ok = true;
+
+    // Two passes, each a run of independent instructions: u = RN(partial * A_scale), acc = RN(acc + u).
+    // Scalar on purpose: the packed forms (mul.rn.f32x2 followed by add.rn.f32x2, or by an fma with a
+    // multiplier of one) were measured to come out contracted into one fused multiply-add -- a
+    // single rounding where the recurrence has two, which changes 30 % of the results by an ulp.
+    auto accumulate = [&](uint32_t (&p)[32], float2 (&acc)[16], const float a) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) p[j] = __float_as_uint(__fmul_rn(__uint_as_float(p[j]), a));
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        acc[j].x = __fadd_rn(acc[j].x, __uint_as_float(p[2 * j]));
+        acc[j].y = __fadd_rn(acc[j].y, __uint_as_float(p[2 * j + 1]));
+      }
+    };
+
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      const TileCoord tc = tile_coord(tile, num_m, num_n);
+      const int row = tc.m_blk * kBlockM + q * 32 + lane;
+      const int col0 = tc.n_blk * kBlockN + cs * 32;
+      const float a_m = row < M ? __ldg(a_scale + row) : 0.0f;
+      float2 acc[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] = make_float2(0.0f, 0.0f);
+      uint32_t pa[32], pb[32];
+      // prologue: the first partial of the tile's first pair
+      ok = mbar_wait_a(tmem_full_a + pair * 8, pair_phase, status, abort_a, kTagTmemFull | pair);
+      if (!ok) break;
+      tc_fence_after();
+      tmem_ld_32x32(t_lane + pair * 2 * kBlockN, pa);
+      for (int kb = 0; ok && kb < num_pairs; ++kb) {
+        // ---- first partial of the pair: wait for it, start loading the second, compute
+        tmem_wait_ld_for(pa);
+        tmem_ld_32x32(t_lane + (pair * 2 + 1) * kBlockN, pb);
+        accumulate(pa, acc, a_m);
+        // ---- second partial: wait for it, start loading the next pair's first, hand the pair back
+        tmem_wait_ld_for(pb);
+        const int done_pair = pair;
+        if (++pair == kPairs) {
+          pair = 0;
+          pair_phase ^= 1u;
+        }
+        if (kb + 1 < num_pairs) {
+          ok = mbar_wait_a(tmem_full_a + pair * 8, pair_phase, status, abort_a, kTagTmemFull | pair);
+          if (!ok) break;
+          tc_fence_after();
+          tmem_ld_32x32(t_lane + pair * 2 * kBlockN, pa);
+        }
+        tc_fence_before();  // tcgen05.wait::ld is warp-collective: every lane's loads have landed
+        if (lane == 0) mbar_arrive_a(tmem_empty_a + done_pair * 8);
+        accumulate(pb, acc, a_m);
+      }
+      if (ok && row < M) {
+        float* dst = y + static_cast<long>(row) * ldy + col0;
+        if (col0 + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            reinterpret_cast<float4*>(dst)[j4] = make_float4(acc[2 * j4].x, acc[2 * j4].y, acc[2 * j4 + 1].x, acc[2 * j4 + 1].y);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (col0 + 2 * j < N) dst[2 * j] = acc[j].x;
+            if (col0 + 2 * j + 1 < N) dst[2 * j + 1] = acc[j].y;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+}  // namespace
+
+int init_gemm_o1_bf16_attributes() {
+  return check_cuda(
+      cudaFuncSetAttribute(gemm_o1_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+      "cudaFuncSetAttribute(gemm_o1_bf16_kernel)");
+}
+
+int o1_bf16_block_n() { return kBlockN; }
+
+int run_gemm_o1_bf16(const GemmPlan& p, cudaStream_t stream) {
+  if (p.variant != 1 || !p.o1_bf16) return fail("run_gemm_o1_bf16: plan is not an O1 BF16-operand plan");
+  gemm_o1_bf16_kernel<<<p.grid, kThreads, kSmemBytes, stream>>>(p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), p.y,
+                                                                p.range_flag, p.M, p.N, p.K, p.ldy, p.status);
+  return check_cuda(cudaGetLastError(), "gemm_o1_bf16_kernel launch");
+}
+
+}  // namespace adg

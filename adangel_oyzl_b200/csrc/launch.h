@@ -41,6 +41,15 @@ inline long tiled_scale_bytes(long rows, long k) { return tiled_scale_rows(rows)
 int launch_mxfp4_to_fp16(const void* packed, const void* scales, void* out, long rows, long k, cudaStream_t stream);
 int launch_int8_to_fp16(const void* in, const void* row_scale, void* out, long rows, long k, cudaStream_t stream);
 int launch_mxfp4_to_int8(const void* packed, void* out, long rows, long k, cudaStream_t stream);
+// Operands of the O1 kernel with BF16 operands; `range_flag` is one device word (bit 0: a weight
+// scale code outside [kO1MinScaleCode, kO1MaxScaleCode]; bit 1: an activation scale outside
+// [2^kO1MinAScaleExp, 2^kO1MaxAScaleExp] or not finite).
+constexpr unsigned kO1MinScaleCode = 48, kO1MaxScaleCode = 208;
+constexpr int kO1MinAScaleExp = -46, kO1MaxAScaleExp = 30;
+int launch_mxfp4_to_bf16_scaled(const void* packed, const void* scales, void* out, void* range_flag, long rows, long k,
+                                cudaStream_t stream);
+int launch_int8_to_bf16(const void* in, const void* row_scale, void* out, void* range_flag, long rows, long k,
+                        cudaStream_t stream);
 int launch_o2_quantize(const void* a_int8, const void* row_scale, void* codes, void* sf_natural, void* sf_tiled,
                        long rows, long k, cudaStream_t stream);
 int launch_o2_tile_scales(const void* natural, void* tiled, long rows, long k, cudaStream_t stream);
@@ -75,6 +84,8 @@ struct GemmPlan {
   // decode-sized O1/O2 (M <= 64): operand-swapped kernels; tm_a = A map, tm_b = W map; `grid_y`
   // is the number of 16-row slices of A (O1 only)
   int skinny = 0, grid_y = 1;
+  int o1_bf16 = 0;                       // O1 with BF16 operands (weight scale folded into W)
+  const uint32_t* range_flag = nullptr;  // O1 BF16: device word set by the operand conversions
   int pair = 0;  // O0/O2 on CTA pairs (cta_group::2): tm_b has 128-row boxes, grid = 2 x clusters
   uint32_t* status = nullptr;
 };
@@ -84,6 +95,8 @@ int plan_o1(GemmPlan* plan, const void* a_int8, const void* a_scale, const void*
             int32_t* partial_dump, int M, int N, int K, int ldy);
 int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const void* w_mxfp4, const void* sfb_tiled,
             float* y, int M, int N, int K, int ldy);
+int plan_o1_bf16(GemmPlan* plan, const void* a_bf16, const void* a_scale, const void* w_bf16, float* y,
+                 const void* range_flag, int M, int N, int K, int ldy);
 int run_plan(const GemmPlan& plan, cudaStream_t stream);
 
 // Kernel entry points behind run_plan (defined in gemm_acc.cu / gemm_o1.cu).
@@ -95,6 +108,9 @@ int o1_block_n();      // W rows per O1 tile
 int o1_ctas_per_sm();  // resident O1 CTAs per SM
 int init_gemm_skinny_attributes();
 int init_gemm_pair_attributes();
+int init_gemm_o1_bf16_attributes();
+int run_gemm_o1_bf16(const GemmPlan& plan, cudaStream_t stream);
+int o1_bf16_block_n();
 int run_gemm_pair(const GemmPlan& plan, cudaStream_t stream);
 int pair_tile_m();
 int pair_tile_n();

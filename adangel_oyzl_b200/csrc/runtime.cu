@@ -69,6 +69,7 @@ int device_ctx(DeviceCtx** out) {
     if (int rc = init_gemm_o1_attributes()) return rc;
     if (int rc = init_gemm_skinny_attributes()) return rc;
     if (int rc = init_gemm_pair_attributes()) return rc;
+    if (int rc = init_gemm_o1_bf16_attributes()) return rc;
     if (int rc = init_gemm_o1_skinny_attributes()) return rc;
     g_ctx[dev] = ctx;
     g_ctx_ready[dev] = true;
@@ -87,6 +88,13 @@ int check_device_status(cudaStream_t stream) {
   if (words[0] == kStatusOk) return 0;
   check_cuda(cudaMemset(ctx->status, 0, sizeof(words)), "cudaMemset(status)");
   char buf[256];
+  if (words[0] == kStatusOperandRange) {
+    snprintf(buf, sizeof(buf),
+             "O1 BF16-operand GEMM refused: operands outside its exact range (flag=0x%x: bit 0 weight scale codes, bit 1 "
+             "activation scales); use the INT8-operand O1 GEMM for these inputs",
+             words[1]);
+    return fail(buf);
+  }
   snprintf(buf, sizeof(buf), "kernel wait timeout: code=%u tag=0x%x block=%u detail=%u", words[0], words[1], words[2],
            words[3]);
   return fail(buf);
@@ -131,14 +139,15 @@ int encode_word_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
   return 0;
 }
 
-// CTA pairs (cta_group::2) are used when the environment asks for them and the shape has at least
-// one full pair tile.
+// O0/O2 run on CTA pairs (cta_group::2, 256 x 256 tiles: 3 - 7 % faster at large shapes, bit-identical)
+// when the shape has at least one full pair tile and pairing rows wastes little: an even number of
+// 128-row blocks, or so many that the padded half block is under 3 %.  ADG_TWO_CTA=0 in the
+// environment (read at every plan) keeps every shape on the single-CTA kernel.
 bool pair_enabled(int M, int N) {
-  static const bool enabled = [] {
-    const char* e = getenv("ADG_TWO_CTA");
-    return e != nullptr && e[0] == '1';
-  }();
-  return enabled && M >= pair_tile_m() && N >= pair_tile_n();
+  const char* e = getenv("ADG_TWO_CTA");
+  if (e != nullptr && e[0] == '0') return false;
+  const int row_blocks = (M + 127) / 128;
+  return M >= pair_tile_m() && N >= pair_tile_n() && (row_blocks % 2 == 0 || row_blocks >= 33);
 }
 
 int finish_pair_plan(GemmPlan* plan, int sm_count, uint32_t* status) {
@@ -235,6 +244,28 @@ int plan_o1(GemmPlan* plan, const void* a_int8, const void* a_scale, const void*
   return 0;
 }
 
+int plan_o1_bf16(GemmPlan* plan, const void* a_bf16, const void* a_scale, const void* w_bf16, float* y,
+                 const void* range_flag, int M, int N, int K, int ldy) {
+  DeviceCtx* ctx = nullptr;
+  if (int rc = device_ctx(&ctx)) return rc;
+  if (int rc = check_shape(M, N, K, ldy)) return rc;
+  *plan = GemmPlan{};
+  plan->variant = 1;
+  plan->o1_bf16 = 1;
+  plan->M = M, plan->N = N, plan->K = K, plan->ldy = ldy;
+  plan->a_scale = a_scale;
+  plan->range_flag = static_cast<const uint32_t*>(range_flag);
+  plan->y = y;
+  if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_bf16, M, K,
+                                    static_cast<uint64_t>(K) * 2, 128, 64))
+    return rc;
+  if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w_bf16, N, K,
+                                    static_cast<uint64_t>(K) * 2, o1_bf16_block_n(), 64))
+    return rc;
+  plan->tm_y = plan->tm_a;
+  return finish_plan(plan, o1_bf16_block_n());
+}
+
 int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const void* w_mxfp4, const void* sfb_tiled,
             float* y, int M, int N, int K, int ldy) {
   DeviceCtx* ctx = nullptr;
@@ -270,6 +301,7 @@ int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const vo
 }
 
 int run_plan(const GemmPlan& plan, cudaStream_t stream) {
+  if (plan.variant == 1 && plan.o1_bf16) return run_gemm_o1_bf16(plan, stream);
   if (plan.variant == 1) return plan.skinny ? run_gemm_o1_skinny(plan, stream) : run_gemm_o1(plan, stream);
   if (plan.skinny) return run_gemm_o2_skinny(plan, stream);
   if (plan.pair) return run_gemm_pair(plan, stream);

@@ -40,6 +40,12 @@ def mxfp4_to_fp16(w_mxfp4, w_scale):
     return out
 
 
+def torch_device(device):
+    import torch
+
+    return torch.cuda.device(device)
+
+
 def int8_to_fp16(a_int8, a_scale):
     import torch
 
@@ -60,6 +66,41 @@ def mxfp4_to_int8(w_mxfp4):
     out = torch.empty((n, kh * 2), dtype=torch.int8, device=w_mxfp4.device)
     with torch.cuda.device(w_mxfp4.device):
         _sm100._check(_lib().adg_mxfp4_to_int8(w_mxfp4.data_ptr(), out.data_ptr(), n, kh * 2, _stream(out)))
+    return out
+
+
+def new_range_flag(device):
+    """The zeroed device word that the BF16-operand O1 conversions and GEMM share."""
+    import torch
+
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def mxfp4_to_bf16_scaled(w_mxfp4, w_scale, range_flag):
+    """W as BF16 of e2m1 * 2^(scale-127) (exact): the weight operand of :func:`gemm_o1_bf16`."""
+    import torch
+
+    n, kh = w_mxfp4.shape
+    _require(w_mxfp4.is_cuda and w_mxfp4.dtype == torch.uint8 and w_mxfp4.is_contiguous(), "W_mxfp4 must be contiguous CUDA uint8")
+    _require(w_scale.dtype == torch.uint8 and tuple(w_scale.shape) == (n, kh * 2 // 32) and w_scale.is_contiguous(), "invalid W_scale")
+    out = torch.empty((n, kh * 2), dtype=torch.bfloat16, device=w_mxfp4.device)
+    with torch.cuda.device(w_mxfp4.device):
+        _sm100._check(_lib().adg_mxfp4_to_bf16_scaled(
+            w_mxfp4.data_ptr(), w_scale.data_ptr(), out.data_ptr(), range_flag.data_ptr(), n, kh * 2, _stream(out)))
+    return out
+
+
+def int8_to_bf16(a_int8, a_scale, range_flag):
+    """A's integers as BF16 (exact): the activation operand of :func:`gemm_o1_bf16`."""
+    import torch
+
+    m, k = a_int8.shape
+    _require(a_int8.is_cuda and a_int8.dtype == torch.int8 and a_int8.is_contiguous(), "A_int8 must be contiguous CUDA int8")
+    _require(a_scale.dtype == torch.float32 and tuple(a_scale.shape) == (m,), "invalid A_scale")
+    out = torch.empty((m, k), dtype=torch.bfloat16, device=a_int8.device)
+    with torch.cuda.device(a_int8.device):
+        _sm100._check(_lib().adg_int8_to_bf16(
+            a_int8.data_ptr(), a_scale.data_ptr(), out.data_ptr(), range_flag.data_ptr(), m, k, _stream(out)))
     return out
 
 
@@ -174,6 +215,19 @@ def gemm_o1(a_int8, a_scale, w_int8, w_scale, out=None, dump_partials=False):
             a_int8.data_ptr(), a_scale.data_ptr(), w_int8.data_ptr(), w_scale.data_ptr(), out.data_ptr(),
             partials.data_ptr() if partials is not None else None, m, n, k, ldy, _stream(out)))
     return (out, partials) if dump_partials else out
+
+
+def gemm_o1_bf16(a_bf16, a_scale, w_bf16, range_flag, out=None):
+    """O1 on BF16 operands (same bits as :func:`gemm_o1` while ``range_flag`` stays zero; otherwise the
+    kernel refuses and the next status check raises)."""
+    m, k = a_bf16.shape
+    n = w_bf16.shape[0]
+    out, ldy = _output(out, m, n, a_bf16.device)
+    with torch_device(a_bf16.device):
+        _sm100._check(_lib().adg_gemm_o1_bf16(
+            a_bf16.data_ptr(), a_scale.data_ptr(), w_bf16.data_ptr(), out.data_ptr(), range_flag.data_ptr(),
+            m, n, k, ldy, _stream(out)))
+    return out
 
 
 def gemm_o2(a_mxfp4, a_sf_tiled, w_mxfp4, w_sf_tiled, out=None):

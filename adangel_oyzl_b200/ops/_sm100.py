@@ -46,6 +46,8 @@ _SIGNATURES = {
     "adg_mxfp4_to_fp16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "adg_int8_to_fp16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "adg_mxfp4_to_int8": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "adg_mxfp4_to_bf16_scaled": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "adg_int8_to_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "adg_o2_tiled_scale_bytes": (c_int64, [c_int64, c_int64]),
     "adg_o2_quantize_activation": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "adg_o2_tile_scales": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
@@ -53,6 +55,7 @@ _SIGNATURES = {
     "adg_quantize_mxfp4": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "adg_gemm_o0": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "adg_gemm_o1": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "adg_gemm_o1_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "adg_gemm_o2": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "adg_o2_linear_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int]),
     "adg_benchmark": (c_int, [POINTER(BenchArgs)]),

@@ -68,6 +68,19 @@ int adg_int8_to_fp16(const void* a_int8, const void* a_scale, void* out_fp16, in
  * Replaces adangel_launch_mxfp4_to_int8 (kernel_api.h:33-36, conversion.cu:39-50). */
 int adg_mxfp4_to_int8(const void* w_mxfp4, void* out_int8, int64_t rows, int64_t K, void* stream);
 
+/* Operands of adg_gemm_o1_bf16 (no reference counterpart: the reference's O1 kernel takes INT8
+ * operands; see adg_gemm_o1_bf16 for why these exist).
+ *   out_bf16[rows,K] = bfloat16(e2m1(nibble) * 2^(scale-127)), exact (two significant bits);
+ *   out_bf16[rows,K] = bfloat16(a), exact (integers of magnitude <= 128).
+ * range_flag is one zero-initialised 32-bit device word shared by the two conversions and the GEMM:
+ * bit 0 is set when a weight scale code lies outside [48, 208], bit 1 when an activation scale lies
+ * outside [2^-46, 2^30] or is not finite -- the ranges inside which the BF16-operand kernel is
+ * bit-identical to the INT8-operand kernel. */
+int adg_mxfp4_to_bf16_scaled(const void* w_mxfp4, const void* w_scale, void* out_bf16, void* range_flag, int64_t rows,
+                             int64_t K, void* stream);
+int adg_int8_to_bf16(const void* a_int8, const void* a_scale, void* out_bf16, void* range_flag, int64_t rows, int64_t K,
+                     void* stream);
+
 /* Size in bytes of the tiled scale-factor buffer for a [rows, K/32] scale matrix (512-byte atoms
  * of 128 rows x 4 blocks, zero padded to 256 rows / 8 blocks). */
 int64_t adg_o2_tiled_scale_bytes(int64_t rows, int64_t K);
@@ -117,6 +130,17 @@ int adg_gemm_o0(const void* a_fp16, const void* w_fp16, float* y, int M, int N, 
  * Replaces adangel_o1_tma_warp_specialized (csrc/sm120/o1_gemm.cu:167-392). */
 int adg_gemm_o1(const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale, float* y,
                 int32_t* partial_dump, int M, int N, int K, int ldy, void* stream);
+
+/* O1 GEMM on BF16 operands: the same recurrence and the same bits as adg_gemm_o1, computed with the
+ * weight's power-of-two scale folded into the tensor-core operand (tcgen05 kind::f16, BF16 x BF16,
+ * FP32 accumulate): each K32 partial leaves the tensor core as float(P) * 2^(W_scale-128), exact, and
+ * the epilogue multiplies by A_scale[m] and adds -- no integer conversion and no per-column factor
+ * in the inner loop, which is what bounds adg_gemm_o1.  a_bf16 / w_bf16 come from adg_int8_to_bf16 /
+ * adg_mxfp4_to_bf16_scaled.  If *range_flag is non-zero the kernel does not compute: it records an
+ * error that the next status check reports, and the caller falls back to adg_gemm_o1, which covers
+ * every input.  M > 64 is the intended use (decode-sized M: adg_gemm_o1). */
+int adg_gemm_o1_bf16(const void* a_bf16, const void* a_scale, const void* w_bf16, float* y, const void* range_flag, int M,
+                     int N, int K, int ldy, void* stream);
 
 /* O2 GEMM: block-scaled MXFP4 x MXFP4 (tcgen05 kind::mxf4.block_scale), scales in tiled layout.
  * Replaces the CUTLASS block-scaled GEMM (csrc/sm120/o2_cutlass.cu:35-93, :394-472). */

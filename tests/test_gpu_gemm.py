@@ -153,3 +153,62 @@ def test_full_size_4096(K):
     mse2 = float(((y2.double() - y0.double()) ** 2).mean())
     assert mse1 == pytest.approx(orc.mse_fp64(o1, o0), rel=0.25)
     assert mse2 == pytest.approx(orc.mse_fp64(o2, o0), rel=0.25)
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 320), (1000, 777, 128), (4224, 512, 256)])
+def test_cta_pair_kernels_match_single_cta(K, shape, monkeypatch):
+    # O0/O2 on CTA pairs (cta_group::2, the default where a full 256 x 256 pair tile exists) give the
+    # same bits as the single-CTA kernels; (1000, 777, .) has ragged edges and an unaligned Y pitch,
+    # (4224, ...) an odd number of row blocks
+    m, n, k = shape
+    args = orc.canonical_inputs(m, n, k, seed=23)
+    monkeypatch.setenv("ADG_TWO_CTA", "0")
+    single = _gpu_all(K, *args)
+    monkeypatch.delenv("ADG_TWO_CTA")
+    paired = _gpu_all(K, *args)
+    np.testing.assert_array_equal(paired[0], single[0])
+    np.testing.assert_array_equal(paired[2], single[2])
+    np.testing.assert_allclose(paired[0], orc.run_o0(*args)["output"], rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (200, 384, 256), (1000, 777, 128), (512, 1024, 2048)])
+def test_o1_bf16_operands_bit_identical(K, shape):
+    # the O1 kernel that takes the weight scale through the tensor core (BF16 operands) gives the
+    # oracle's bits, like the INT8-operand kernel
+    m, n, k = shape
+    a_int8, a_scale, w_mx, w_sc = orc.canonical_inputs(m, n, k, seed=29)
+    da, ds, dw, dws = to_cuda(a_int8, a_scale, w_mx, w_sc)
+    flag = K.new_range_flag("cuda")
+    y = K.gemm_o1_bf16(K.int8_to_bf16(da, ds, flag), ds, K.mxfp4_to_bf16_scaled(dw, dws, flag), flag)
+    K.check_status()
+    assert int(flag.item()) == 0
+    np.testing.assert_array_equal(y.cpu().numpy(), orc.run_o1(a_int8, a_scale, w_mx, w_sc)["output"])
+
+
+def test_o1_bf16_operands_refuse_out_of_range(K):
+    # scale codes / activation scales outside the exact range set the flag; the GEMM then refuses
+    # loudly instead of returning different bits, and the INT8-operand kernel still serves the input
+    import torch
+
+    a_int8, a_scale, w_mx, w_sc = orc.canonical_inputs(128, 128, 128, seed=31)
+    w_sc = w_sc.copy()
+    w_sc[5, 1] = 250
+    da, ds, dw, dws = to_cuda(a_int8, a_scale, w_mx, w_sc)
+    flag = K.new_range_flag("cuda")
+    wb = K.mxfp4_to_bf16_scaled(dw, dws, flag)
+    ab = K.int8_to_bf16(da, ds, flag)
+    assert int(flag.item()) == 1
+    y = torch.full((128, 128), -3.0, device="cuda")
+    K.gemm_o1_bf16(ab, ds, wb, flag, out=y)
+    with pytest.raises(RuntimeError, match="outside its exact range"):
+        K.check_status()
+    assert bool((y == -3.0).all())
+    K.check_status()  # the error is reported once
+    flag2 = K.new_range_flag("cuda")
+    tiny = ds.clone()
+    tiny[7] = 1e-30
+    K.int8_to_bf16(da, tiny, flag2)
+    assert int(flag2.item()) == 2
+    y1 = K.gemm_o1(da, ds, K.mxfp4_to_int8(dw), dws)
+    K.check_status()
+    np.testing.assert_array_equal(y1.cpu().numpy(), orc.run_o1(a_int8, a_scale, w_mx, w_sc)["output"])
