@@ -68,6 +68,10 @@ struct DeviceBuffer {
     if (p) cudaFree(p);
   }
   int alloc(size_t bytes) { return check_cuda(cudaMalloc(&p, bytes ? bytes : 1), "cudaMalloc"); }
+  void release() {
+    if (p) cudaFree(p);
+    p = nullptr;
+  }
 };
 
 }  // namespace
@@ -367,7 +371,38 @@ struct adg_session {
   cudaStream_t stream = nullptr;
   bool in_flight = false;  // a submitted pass has not been waited for yet
   DeviceBuffer w_raw, w_scale, w_conv, a_raw, a_scale, a_conv, a_sf_tiled, y;
+  // O1: the pass runs on BF16 operands (weight scale folded into W, see gemm_o1_bf16.cu) while the
+  // operands stay inside that kernel's exact range, and on the INT8 operands otherwise.  The weight's
+  // range is known at creation; an activation's is reported by its conversion into `flags` (device,
+  // word 0 = weight, word 1 = this pass), copied to `pass_flag` (pinned) behind the GEMM.  The INT8
+  // form of W is made on first need (decode-sized M, or a fallback).
+  bool w_in_bf16_range = false;
+  DeviceBuffer w_bf16, w_int8, flags;
+  uint32_t* pass_flag = nullptr;
+  bool pass_on_bf16 = false;
+  int pass_M = 0;
+  float* pass_y_host = nullptr;
 };
+
+namespace {
+
+int session_w_int8(adg_session* s) {
+  if (s->w_int8.p != nullptr) return 0;
+  if (s->w_int8.alloc(static_cast<size_t>(s->N) * s->K)) return 1;
+  return launch_mxfp4_to_int8(s->w_raw.p, s->w_int8.p, s->N, s->K, s->stream) ? fail("mxfp4_to_int8 launch failed") : 0;
+}
+
+int session_o1_int8_pass(adg_session* s, int M, float* y_host) {
+  if (int rc = session_w_int8(s)) return rc;
+  GemmPlan plan;
+  float* y = static_cast<float*>(s->y.p);
+  if (int rc = plan_o1(&plan, s->a_raw.p, s->a_scale.p, s->w_int8.p, s->w_scale.p, y, nullptr, M, s->N, s->K, s->N)) return rc;
+  if (int rc = run_plan(plan, s->stream)) return rc;
+  return check_cuda(cudaMemcpyAsync(y_host, y, sizeof(float) * M * static_cast<size_t>(s->N), cudaMemcpyDeviceToHost, s->stream),
+                    "D2H Y");
+}
+
+}  // namespace
 
 int adg_session_create(adg_session** out, int variant, int max_M, int N, int K, const void* w_mxfp4_host,
                        const void* w_scale_host) {
@@ -384,12 +419,17 @@ int adg_session_create(adg_session** out, int variant, int max_M, int N, int K, 
        s->a_scale.alloc(sizeof(float) * max_M) || s->y.alloc(sizeof(float) * max_M * static_cast<size_t>(N));
   if (!rc) rc = check_cuda(cudaMemcpyAsync(s->w_raw.p, w_mxfp4_host, nk / 2, cudaMemcpyHostToDevice, s->stream), "H2D W");
   if (!rc) rc = check_cuda(cudaMemcpyAsync(s->w_scale.p, w_scale_host, nk / 32, cudaMemcpyHostToDevice, s->stream), "H2D W scale");
+  uint32_t w_flag = 1;
   if (!rc) {
     if (variant == 0) {
       rc = s->w_conv.alloc(nk * 2) || s->a_conv.alloc(mk * 2) ||
            launch_mxfp4_to_fp16(s->w_raw.p, s->w_scale.p, s->w_conv.p, N, K, s->stream);
     } else if (variant == 1) {
-      rc = s->w_conv.alloc(nk) || launch_mxfp4_to_int8(s->w_raw.p, s->w_conv.p, N, K, s->stream);
+      rc = s->w_bf16.alloc(nk * 2) || s->a_conv.alloc(mk * 2) || s->flags.alloc(2 * sizeof(uint32_t)) ||
+           check_cuda(cudaMallocHost(reinterpret_cast<void**>(&s->pass_flag), sizeof(uint32_t)), "cudaMallocHost") ||
+           check_cuda(cudaMemsetAsync(s->flags.p, 0, 2 * sizeof(uint32_t), s->stream), "cudaMemsetAsync") ||
+           launch_mxfp4_to_bf16_scaled(s->w_raw.p, s->w_scale.p, s->w_bf16.p, s->flags.p, N, K, s->stream) ||
+           check_cuda(cudaMemcpyAsync(&w_flag, s->flags.p, sizeof(uint32_t), cudaMemcpyDeviceToHost, s->stream), "D2H flag");
     } else {
       const size_t sfa = tiled_scale_bytes(max_M, K);
       rc = s->w_conv.alloc(tiled_scale_bytes(N, K)) || s->a_conv.alloc(mk / 2) || s->a_sf_tiled.alloc(sfa) ||
@@ -398,6 +438,14 @@ int adg_session_create(adg_session** out, int variant, int max_M, int N, int K, 
     }
   }
   if (!rc) rc = check_cuda(cudaStreamSynchronize(s->stream), "session synchronization");
+  if (!rc && variant == 1) {
+    s->w_in_bf16_range = w_flag == 0;
+    if (!s->w_in_bf16_range) {
+      // this weight always takes the INT8 operands: drop the BF16 copy
+      s->w_bf16.release();
+      rc = session_w_int8(s) || check_cuda(cudaStreamSynchronize(s->stream), "session synchronization");
+    }
+  }
   if (rc) {
     adg_session_destroy(s);
     return 1;
@@ -418,17 +466,35 @@ int adg_session_submit(adg_session* s, const void* a_int8_host, const void* a_sc
     return rc;
   GemmPlan plan;
   float* y = static_cast<float*>(s->y.p);
+  s->pass_on_bf16 = false;
   if (s->variant == 0) {
     if (launch_int8_to_fp16(s->a_raw.p, s->a_scale.p, s->a_conv.p, M, K, st)) return fail("int8_to_fp16 launch failed");
     if (int rc = plan_o0(&plan, s->a_conv.p, s->w_conv.p, y, M, N, K, N)) return rc;
   } else if (s->variant == 1) {
-    if (int rc = plan_o1(&plan, s->a_raw.p, s->a_scale.p, s->w_conv.p, s->w_scale.p, y, nullptr, M, N, K, N)) return rc;
+    if (s->w_in_bf16_range && M > 64) {
+      uint32_t* pass_word = static_cast<uint32_t*>(s->flags.p) + 1;
+      if (int rc = check_cuda(cudaMemsetAsync(pass_word, 0, sizeof(uint32_t), st), "cudaMemsetAsync")) return rc;
+      if (launch_int8_to_bf16(s->a_raw.p, s->a_scale.p, s->a_conv.p, pass_word, M, K, st)) return fail("int8_to_bf16 launch failed");
+      if (int rc = plan_o1_bf16(&plan, s->a_conv.p, s->a_scale.p, s->w_bf16.p, y, pass_word, M, N, K, N)) return rc;
+      plan.quiet_refusal = 1;
+      if (int rc = run_plan(plan, st)) return rc;
+      if (int rc = check_cuda(cudaMemcpyAsync(s->pass_flag, pass_word, sizeof(uint32_t), cudaMemcpyDeviceToHost, st), "D2H flag"))
+        return rc;
+      s->pass_on_bf16 = true;
+      s->pass_M = M;
+      s->pass_y_host = y_host;
+    } else {
+      if (int rc = session_o1_int8_pass(s, M, y_host)) return rc;
+      s->in_flight = true;
+      return 0;
+    }
   } else {
     if (launch_o2_quantize(s->a_raw.p, s->a_scale.p, s->a_conv.p, nullptr, s->a_sf_tiled.p, M, K, st))
       return fail("o2_quantize launch failed");
     if (int rc = plan_o2(&plan, s->a_conv.p, s->a_sf_tiled.p, s->w_raw.p, s->w_conv.p, y, M, N, K, N)) return rc;
   }
-  if (int rc = run_plan(plan, st)) return rc;
+  if (!s->pass_on_bf16)
+    if (int rc = run_plan(plan, st)) return rc;
   if (int rc = check_cuda(cudaMemcpyAsync(y_host, y, sizeof(float) * M * static_cast<size_t>(N), cudaMemcpyDeviceToHost, st), "D2H Y"))
     return rc;
   s->in_flight = true;
@@ -438,7 +504,15 @@ int adg_session_submit(adg_session* s, const void* a_int8_host, const void* a_sc
 int adg_session_wait(adg_session* s) {
   if (s == nullptr) return fail("session must not be NULL");
   s->in_flight = false;
-  return check_device_status(s->stream);
+  if (int rc = check_device_status(s->stream)) return rc;
+  if (s->pass_on_bf16 && *s->pass_flag != 0u) {
+    // an activation scale outside the BF16-operand kernel's exact range: that kernel did not
+    // compute; run the pass on the INT8 operands (A is still on the device)
+    s->pass_on_bf16 = false;
+    if (int rc = session_o1_int8_pass(s, s->pass_M, s->pass_y_host)) return rc;
+    return check_device_status(s->stream);
+  }
+  return 0;
 }
 
 int adg_session_run(adg_session* s, const void* a_int8_host, const void* a_scale_host, int M, float* y_host) {
@@ -449,6 +523,7 @@ int adg_session_run(adg_session* s, const void* a_int8_host, const void* a_scale
 void adg_session_destroy(adg_session* s) {
   if (s == nullptr) return;
   if (s->stream) cudaStreamDestroy(s->stream);
+  if (s->pass_flag) cudaFreeHost(s->pass_flag);
   delete s;
 }
 

@@ -73,12 +73,13 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) 
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const float* __restrict__ a_scale, float* __restrict__ y, const uint32_t* __restrict__ range_flag,
-                    int M, int N, int K, int ldy, uint32_t* status) {
-  // operands outside the exact range: refuse loudly, before any barrier or tensor memory exists
+                    int quiet_refusal, int M, int N, int K, int ldy, uint32_t* status) {
+  // operands outside the exact range: refuse, before any barrier or tensor memory exists -- loudly (an
+  // error status for the next check) unless the caller watches the flag itself and falls back
   if (range_flag != nullptr) {
     const uint32_t flag = *range_flag;
     if (flag != 0u) {
-      if (threadIdx.x == 0 && atomicCAS(status, 0u, static_cast<uint32_t>(kStatusOperandRange)) == 0u) {
+      if (!quiet_refusal && threadIdx.x == 0 && atomicCAS(status, 0u, static_cast<uint32_t>(kStatusOperandRange)) == 0u) {
         status[1] = flag;
         status[2] = blockIdx.x;
         status[3] = 0;
@@ -292,7 +293,7 @@ int o1_bf16_block_n() { return kBlockN; }
 int run_gemm_o1_bf16(const GemmPlan& p, cudaStream_t stream) {
   if (p.variant != 1 || !p.o1_bf16) return fail("run_gemm_o1_bf16: plan is not an O1 BF16-operand plan");
   gemm_o1_bf16_kernel<<<p.grid, kThreads, kSmemBytes, stream>>>(p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), p.y,
-                                                                p.range_flag, p.M, p.N, p.K, p.ldy, p.status);
+                                                                p.range_flag, p.quiet_refusal, p.M, p.N, p.K, p.ldy, p.status);
   return check_cuda(cudaGetLastError(), "gemm_o1_bf16_kernel launch");
 }
 

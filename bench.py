@@ -38,7 +38,6 @@ M = N_PER_GPU = K = 4096
 VARIANTS = ("o0", "o1", "o2")
 FLOP_PER_VARIANT = 2.0 * M * N_PER_GPU * K
 L2_BYTES = 126 * 1024 * 1024
-NOMINAL_TFLOPS = {"o0": 2250.0, "o1": 4500.0, "o2": 9000.0}  # dense FP16 / INT8 / FP4
 # dram__bytes_read.sum + dram__bytes_write.sum per launch at 4096^3 from an ncu capture of one
 # benchmark step (summary kept under profiles/; the 126 MB L2 keeps most of the 64 MiB output on chip)
 NCU_DRAM_TRAFFIC_BYTES = {"o0_int8_to_fp16": 16.8e6, "o0_gemm_f16": 109.1e6, "o1_gemm_i8": 52.1e6,
@@ -46,6 +45,8 @@ NCU_DRAM_TRAFFIC_BYTES = {"o0_int8_to_fp16": 16.8e6, "o0_gemm_f16": 109.1e6, "o1
 # every INT32 K32 partial of O1 is converted, multiplied and accumulated in FP32 by the epilogue warps:
 # 3 issue cycles per partial per warp (measured in isolation with four warps per scheduler), 4 schedulers per SM
 O1_ISSUE_CYCLES_PER_PARTIAL = 3.0
+# with BF16 operands (weight scale folded into W) the partial arrives as an exact FP32 product: multiply + add
+O1_BF16_ISSUE_CYCLES_PER_PARTIAL = 2.0
 
 
 def measured_peaks():
@@ -213,6 +214,12 @@ def run_native_arm(args) -> None:
     shard = parallel.ShardedWeights(n0, n1, w_mxfp4, w_scale)
     shard.w_fp16 = kernels.mxfp4_to_fp16(w_mxfp4, w_scale)
     shard.w_int8 = kernels.mxfp4_to_int8(w_mxfp4)
+    # O1 runs on BF16 operands (weight scale folded into W; bit-identical to the INT8-operand kernel) when
+    # the operands lie inside that kernel's exact range, which the conversions report in `o1_flag`
+    o1_flag = kernels.new_range_flag(dev)
+    shard.w_bf16 = kernels.mxfp4_to_bf16_scaled(w_mxfp4, w_scale, o1_flag)
+    a_bf16 = kernels.int8_to_bf16(a_int8, a_scale, o1_flag)
+    o1_on_bf16 = int(o1_flag.item()) == 0
     shard.w_sf_tiled = kernels.o2_tile_scales(w_scale)
 
     # per-variant buffers (distinct outputs so a step's working set exceeds L2)
@@ -225,7 +232,12 @@ def run_native_arm(args) -> None:
     sfa = torch.zeros((kernels.tiled_scale_bytes(M, K),), dtype=torch.uint8, device=dev)
     check = kernels._sm100._check
 
-    kernel_names = ("o0_int8_to_fp16", "o0_gemm_f16", "o1_gemm_i8", "o2_quantize", "o2_gemm_mxf4")
+    o1_gemm_name = "o1_gemm_bf16" if o1_on_bf16 else "o1_gemm_i8"
+    kernel_names = ("o0_int8_to_fp16", "o0_gemm_f16", "o1_int8_to_bf16", o1_gemm_name, "o2_quantize", "o2_gemm_mxf4")
+
+    def o1_int8_gemm():
+        check(lib.adg_gemm_o1(a_int8.data_ptr(), a_scale.data_ptr(), shard.w_int8.data_ptr(), shard.w_scale.data_ptr(),
+                              y["o1"].data_ptr(), None, M, N_PER_GPU, K, N_PER_GPU, sp))
 
     def step(events=None):
         def mark(i):
@@ -236,15 +248,21 @@ def run_native_arm(args) -> None:
         mark(1)
         check(lib.adg_gemm_o0(a16.data_ptr(), shard.w_fp16.data_ptr(), y["o0"].data_ptr(), M, N_PER_GPU, K, N_PER_GPU, sp))
         mark(2)
-        check(lib.adg_gemm_o1(a_int8.data_ptr(), a_scale.data_ptr(), shard.w_int8.data_ptr(), shard.w_scale.data_ptr(),
-                              y["o1"].data_ptr(), None, M, N_PER_GPU, K, N_PER_GPU, sp))
-        mark(3)
+        if o1_on_bf16:
+            check(lib.adg_int8_to_bf16(a_int8.data_ptr(), a_scale.data_ptr(), a_bf16.data_ptr(), o1_flag.data_ptr(), M, K, sp))
+            mark(3)
+            check(lib.adg_gemm_o1_bf16(a_bf16.data_ptr(), a_scale.data_ptr(), shard.w_bf16.data_ptr(), y["o1"].data_ptr(),
+                                       o1_flag.data_ptr(), M, N_PER_GPU, K, N_PER_GPU, sp))
+        else:
+            mark(3)
+            o1_int8_gemm()
+        mark(4)
         check(lib.adg_o2_quantize_activation(a_int8.data_ptr(), a_scale.data_ptr(), codes.data_ptr(), None,
                                              sfa.data_ptr(), M, K, sp))
-        mark(4)
+        mark(5)
         check(lib.adg_gemm_o2(codes.data_ptr(), sfa.data_ptr(), shard.w_mxfp4.data_ptr(), shard.w_sf_tiled.data_ptr(),
                               y["o2"].data_ptr(), M, N_PER_GPU, K, N_PER_GPU, sp))
-        mark(5)
+        mark(6)
 
     def barrier():
         if distributed:
@@ -269,7 +287,7 @@ def run_native_arm(args) -> None:
     barrier()
     total_ms = t_begin.elapsed_time(t_end)
     # breakdown pass: the same steps again with an event between consecutive kernels
-    events = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(args.steps)]
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(7)] for _ in range(args.steps)]
     for i in range(args.steps):
         step(events[i])
     barrier()
@@ -297,14 +315,22 @@ def run_native_arm(args) -> None:
     n_rot = 6  # 6 x (16 MiB in + 32 MiB out) > L2
     a_rot = [a_int8.clone() for _ in range(n_rot)]
     a16_rot = [torch.empty_like(a16) for _ in range(n_rot)]
+    abf_rot = [torch.empty_like(a_bf16) for _ in range(n_rot)]
     codes_rot = [torch.empty_like(codes) for _ in range(n_rot)]
     batched_ms = {
         "o0_int8_to_fp16": batched(lambda i: check(lib.adg_int8_to_fp16(
             a_rot[i % n_rot].data_ptr(), a_scale.data_ptr(), a16_rot[i % n_rot].data_ptr(), M, K, sp))),
+        "o1_int8_to_bf16": batched(lambda i: check(lib.adg_int8_to_bf16(
+            a_rot[i % n_rot].data_ptr(), a_scale.data_ptr(), abf_rot[i % n_rot].data_ptr(), o1_flag.data_ptr(), M, K, sp))),
         "o2_quantize": batched(lambda i: check(lib.adg_o2_quantize_activation(
             a_rot[i % n_rot].data_ptr(), a_scale.data_ptr(), codes_rot[i % n_rot].data_ptr(), None, sfa.data_ptr(), M, K, sp))),
     }
-    del a_rot, a16_rot, codes_rot
+    del a_rot, a16_rot, abf_rot, codes_rot
+    # the INT8-operand O1 kernel, for comparison (outside the timed region; same bits in y["o1"])
+    y1_bf16 = y["o1"].clone()
+    o1_int8_ms = batched(lambda i: o1_int8_gemm(), reps=10)
+    o1_same_bits = bool(torch.equal(y1_bf16, y["o1"]))
+    del y1_bf16
 
     # per-kernel durations from the events recorded inside the timed steps
     kernel_ms = {name: statistics.fmean(events[i][j].elapsed_time(events[i][j + 1]) for i in range(args.steps))
@@ -316,10 +342,17 @@ def run_native_arm(args) -> None:
             dist.destroy_process_group()
         return
 
-    conv_bytes = {"o0_int8_to_fp16": M * K + 4 * M + 2 * M * K, "o2_quantize": M * K + 4 * M + M * K // 2 + M * K // 32}
-    gemm_variant = {"o0_gemm_f16": "o0", "o1_gemm_i8": "o1", "o2_gemm_mxf4": "o2"}
-    peak_mult = {"o0": 1.0, "o1": 2.0, "o2": 4.0}
+    conv_bytes = {"o0_int8_to_fp16": M * K + 4 * M + 2 * M * K, "o1_int8_to_bf16": M * K + 4 * M + 2 * M * K,
+                  "o2_quantize": M * K + 4 * M + M * K // 2 + M * K // 32}
+    # tensor peak per kernel: the measured BF16 cuBLAS burst times the MMA kind's nominal ratio to BF16
+    peak_mult = {"o0_gemm_f16": 1.0, "o1_gemm_bf16": 1.0, "o1_gemm_i8": 2.0, "o2_gemm_mxf4": 4.0}
+    nominal = {"o0_gemm_f16": 2250.0, "o1_gemm_bf16": 2250.0, "o1_gemm_i8": 4500.0, "o2_gemm_mxf4": 9000.0}
     kernels_out = {}
+    if o1_on_bf16:
+        kernel_ms = dict(kernel_ms, o1_gemm_i8=o1_int8_ms)
+    else:
+        kernel_ms.pop("o1_int8_to_bf16")
+        batched_ms.pop("o1_int8_to_bf16")
     for name, ms in kernel_ms.items():
         if name in conv_bytes:
             ach = conv_bytes[name] / (ms * 1e-3) / 1e9
@@ -329,24 +362,27 @@ def run_native_arm(args) -> None:
                                  "frac": ach / peaks["hbm_gbs"], "algorithmic_bytes": conv_bytes[name],
                                  "batched_ms": bms, "batched_achieved": bach, "batched_frac": bach / peaks["hbm_gbs"]}
         else:
-            v = gemm_variant[name]
             ach = FLOP_PER_VARIANT / (ms * 1e-3) / 1e12
-            peak = peaks["bf16_tflops"] * peak_mult[v]
+            peak = peaks["bf16_tflops"] * peak_mult[name]
             kernels_out[name] = {"ms": ms, "bound": "tensor", "achieved": ach, "unit": "TFLOP/s", "peak": peak,
-                                 "frac": ach / peak, "frac_of_nominal": ach / NOMINAL_TFLOPS[v]}
-    dominant = max(kernel_ms, key=kernel_ms.get)
+                                 "frac": ach / peak, "frac_of_nominal": ach / nominal[name]}
+    if o1_on_bf16:
+        kernels_out["o1_gemm_i8"]["note"] = ("INT8-operand O1 kernel, timed outside the step for comparison; "
+                                             f"bit-identical output: {o1_same_bits}")
+    dominant = max((k for k in kernel_ms if not (o1_on_bf16 and k == "o1_gemm_i8")), key=kernel_ms.get)
     d = kernels_out[dominant]
     roofline = {"kernel": dominant, "bound": d["bound"], "achieved": d["achieved"], "peak": d["peak"], "unit": d["unit"],
                 "frac": d["frac"], "traffic": NCU_DRAM_TRAFFIC_BYTES.get(dominant),
-                "peak_source": f"{peaks['source']}: bf16 cuBLAS burst x{peak_mult[gemm_variant[dominant]]:g}" if d["bound"] == "tensor"
+                "peak_source": f"{peaks['source']}: bf16 cuBLAS burst x{peak_mult[dominant]:g}" if d["bound"] == "tensor"
                 else f"{peaks['source']}: HBM copy"}
 
-    if dominant == "o1_gemm_i8" and clocks and clocks.get("sm_mhz"):
+    if dominant in ("o1_gemm_i8", "o1_gemm_bf16") and clocks and clocks.get("sm_mhz"):
         partials = M * N_PER_GPU * (K // 32)
-        floor_s = partials * O1_ISSUE_CYCLES_PER_PARTIAL / 32 / (148 * 4 * clocks["sm_mhz"] * 1e6)
+        cycles = O1_ISSUE_CYCLES_PER_PARTIAL if dominant == "o1_gemm_i8" else O1_BF16_ISSUE_CYCLES_PER_PARTIAL
+        floor_s = partials * cycles / 32 / (148 * 4 * clocks["sm_mhz"] * 1e6)
         roofline["secondary_bound"] = {
-            "what": "FP32/INT issue slots of the epilogue: every K32 INT32 partial is converted, scaled and accumulated "
-                    "separately (literal O1 semantics), 3 issue cycles per partial per warp",
+            "what": "FP32 issue slots of the epilogue: every K32 partial is scaled and accumulated separately (literal O1 "
+                    f"semantics: one rounding per step and operation), {cycles:g} issue cycles per partial per warp",
             "floor_ms": floor_s * 1e3, "frac_of_floor": floor_s * 1e3 / d["ms"]}
 
     # end to end through the host-buffer C ABI (N = 1 only): pinned A in, Y back, every variant, every step
@@ -388,12 +424,12 @@ def run_native_arm(args) -> None:
         rows = 512
         cpu = cpu_baseline_record(rows, time_cpu_oracle(rows, 3, 1))
 
-    working_set = (M * K + 2 * M * K + M * K // 2) + (2 + 1 + 0.5) * N_PER_GPU * K + 3 * 4 * M * N_PER_GPU
+    working_set = (M * K + 2 * M * K + 2 * M * K + M * K // 2) + (2 + 2 + 0.5) * N_PER_GPU * K + 3 * 4 * M * N_PER_GPU
     line = {
         "metric": "O0+O1+O2 steady-state equivalent TFLOP/s at 4096^3 (2*M*N*K per variant)",
         "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f16/i8/mxf4 operands, f32 accumulate", "data": "synthetic",
+        "dtype": "f16 / bf16 (exact integers, O1) / mxf4 operands, f32 accumulate", "data": "synthetic",
         "config": {"workload": f"canonical M=4096 K=4096, N=4096 per GPU (W sharded by rows, global N={n_global}), "
                                "steady state: activation conversion + GEMM for O0, O1 and O2",
                    "l2": f"no flush: each step touches about {working_set / 2**20:.0f} MiB > 126 MiB L2",
@@ -401,7 +437,9 @@ def run_native_arm(args) -> None:
         "variants": {
             "o0": {"gemm_tflops": kernels_out["o0_gemm_f16"]["achieved"],
                    "steady_tflops": FLOP_PER_VARIANT / ((kernel_ms["o0_int8_to_fp16"] + kernel_ms["o0_gemm_f16"]) * 1e-3) / 1e12},
-            "o1": {"gemm_tflops": kernels_out["o1_gemm_i8"]["achieved"], "steady_tflops": kernels_out["o1_gemm_i8"]["achieved"]},
+            "o1": {"gemm_tflops": kernels_out[o1_gemm_name]["achieved"],
+                   "steady_tflops": FLOP_PER_VARIANT / ((kernel_ms.get("o1_int8_to_bf16", 0.0) + kernel_ms[o1_gemm_name]) * 1e-3) / 1e12,
+                   "operands": "bf16 (weight scale folded into W)" if o1_on_bf16 else "int8"},
             "o2": {"gemm_tflops": kernels_out["o2_gemm_mxf4"]["achieved"],
                    "steady_tflops": FLOP_PER_VARIANT / ((kernel_ms["o2_quantize"] + kernel_ms["o2_gemm_mxf4"]) * 1e-3) / 1e12},
         },
@@ -411,7 +449,7 @@ def run_native_arm(args) -> None:
         "clocks": clocks,
         "e2e": e2e,
         "cpu_baseline": cpu,
-        "gpu_launches": 5 * args.steps,
+        "gpu_launches": (6 if o1_on_bf16 else 5) * args.steps,
         "timing": "value: two CUDA events around all steps; kernels: a second pass with an event between kernels "
                   "(adds about a microsecond per boundary); batched_*: 50 back-to-back launches over rotating buffers",
     }

@@ -169,3 +169,31 @@ def test_host_sessions_overlapped_submit_wait(golden_dir):
     np.testing.assert_allclose(outs["o0"].numpy(), ref["o0_output"], rtol=1e-3, atol=1e-3)
     np.testing.assert_array_equal(outs["o1"].numpy(), ref["o1_output"])
     np.testing.assert_allclose(outs["o2"].numpy(), ref["o2_output"], rtol=1e-3, atol=1e-3)
+
+
+def test_o1_host_session_operand_paths(golden_dir):
+    # an O1 session runs on BF16 operands (weight scale folded into W) and must fall back to the INT8
+    # operands, with the oracle's bits, when a weight scale code or an activation scale leaves that
+    # kernel's exact range, and for decode-sized M
+    from adangel_oyzl_b200.kernels import HostSession
+    from oracle import adangel_oracle as orc
+
+    a_int8, a_scale, w_mx, w_sc = (np.ascontiguousarray(a) for a in orc.canonical_inputs(160, 256, 256, seed=41))
+    want = orc.run_o1(a_int8, a_scale, w_mx, w_sc)["output"]
+    y = np.empty((160, 256), dtype=np.float32)
+    session = HostSession("o1", 256, w_mx, w_sc)
+    np.testing.assert_array_equal(session.run(a_int8, a_scale, y), want)            # BF16 operands
+    y40 = np.empty((40, 256), dtype=np.float32)
+    np.testing.assert_array_equal(session.run(a_int8[:40], a_scale[:40], y40), want[:40])  # decode kernel
+    odd_scale = a_scale.copy()
+    odd_scale[7] = np.float32(2.0 ** -50)                                               # outside [2^-46, 2^30]
+    want_odd = orc.run_o1(a_int8, odd_scale, w_mx, w_sc)["output"]
+    np.testing.assert_array_equal(session.run(a_int8, odd_scale, y), want_odd)        # refused, INT8 fallback
+    np.testing.assert_array_equal(session.run(a_int8, a_scale, y), want)              # and back
+    session.close()
+    odd_w = w_sc.copy()
+    odd_w[3, 2] = 230                                                                   # outside [48, 208]
+    want_w = orc.run_o1(a_int8, a_scale, w_mx, odd_w)["output"]
+    session = HostSession("o1", 256, w_mx, odd_w)
+    np.testing.assert_array_equal(session.run(a_int8, a_scale, y), want_w)
+    session.close()
