@@ -9,10 +9,13 @@ library's CUDA kernels.  Errors reported by the library surface as ``RuntimeErro
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_uint32, c_void_p
 from pathlib import Path
 
-_LIB_PATH = Path(__file__).resolve().parents[1] / "lib" / "libadangel_b200.so"
+# ADANGEL_B200_LIB points the package at an instrumented build of the library (see build.py --define)
+_LIB_PATH = Path(os.environ["ADANGEL_B200_LIB"]).resolve() if os.environ.get("ADANGEL_B200_LIB") else (
+    Path(__file__).resolve().parents[1] / "lib" / "libadangel_b200.so")
 _lib = None
 
 DEFAULT_CONVERSION_INNER_REPEATS = 100  # include/adangel/kernel_api.h:9 of the reference
