@@ -175,7 +175,15 @@ def kernel_metadata(variant: str, m: int, n: int, k: int) -> dict:
         "tile": [128, block_n],
         "persistent": True,
     }
-    if variant == "o0":
+    # the planner's rule for CTA pairs (csrc/runtime.cu, pair_enabled)
+    row_blocks = (m + 127) // 128
+    pair = (os.environ.get("ADG_TWO_CTA", "1")[:1] != "0" and m >= 256 and n >= 256
+            and (row_blocks % 2 == 0 or row_blocks >= 33))
+    if variant == "o0" and pair:
+        common.update(mma_family="tcgen05.mma.cta_group::2.kind::f16", kernel_symbol="gemm_pair_kernel<0>",
+                      stages=6, accumulator_stages=2, threads=384, tile=[256, 256], cluster=[2, 1, 1],
+                      mma_shape=[256, 256, 16])
+    elif variant == "o0":
         common.update(mma_family="tcgen05.mma.cta_group::1.kind::f16", kernel_symbol="gemm_acc_kernel<0>",
                       stages=4 if block_n == 256 else 6, accumulator_stages=2, threads=384,
                       mma_shape=[128, block_n, 16])
@@ -196,6 +204,11 @@ def kernel_metadata(variant: str, m: int, n: int, k: int) -> dict:
         common.update(mma_family="tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32",
                       kernel_symbol="gemm_o2_skinny_kernel", stages=4, threads=192, tile=[m_pad, 128],
                       persistent=False, mma_shape=[128, m_pad, 64], scale_format="UE8M0", weight_copy=False)
+    elif pair:
+        common.update(mma_family="tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32",
+                      kernel_symbol="gemm_pair_kernel<2>", stages=5, accumulator_stages=1, threads=384,
+                      tile=[256, 256], cluster=[2, 1, 1], mma_shape=[256, 256, 64], scale_format="UE8M0",
+                      weight_copy=False)
     else:
         common.update(mma_family="tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32",
                       kernel_symbol="gemm_acc_kernel<2>", stages=4 if block_n == 256 else 6,
