@@ -13,18 +13,28 @@
 // sums are integer multiples of 2**(W_scale-128) below 2**24 of them, hence exact.  The epilogue is
 // left with one multiply by A_scale[m] and one add per partial and element: no integer-to-float
 // conversion, no per-column factor, no scale ring in shared memory, no scale warp.  Measured at
-// 4096^3: 375 us against 414 us for the INT8-operand kernel, bit-identical; converting A to BF16
-// costs another 18 us per call, and W takes two bytes per element instead of one.
+// 4096^3: 326 us against 414 us for the INT8-operand kernel, bit-identical; converting A to BF16
+// costs another 12 us per call, and W takes two bytes per element instead of one.
 //
 // Preconditions (checked on the device by the conversion kernels, which set bits in `range_flag`):
 // W scale codes in [48, 208] and A scales in [2**-46, 2**30], so that no intermediate leaves the
 // normal FP32/BF16 range.  When the flag is set this kernel records an error status and returns
 // without computing; the INT8 kernel (gemm_o1.cu) covers every input.
 //
-// Roles (640 threads): warp 0 TMA producer, warp 1 MMA issuer + tensor-memory owner, warps 4-19
-// epilogue (4 per tensor-memory lane quarter, 32 columns each); warps 2-3 only complete the first
-// warp group, which hands its registers to the epilogue.  One 128-byte K slab (64 BF16 = two K32
-// groups = one "pair" of partials) per pipeline stage.
+// Roles (640 threads): warp 0 TMA producer; warps 1 and 2 MMA issuers (warp 1 owns tensor memory);
+// warps 4-19 epilogue (4 per tensor-memory lane quarter, 32 columns each); warp 3 only completes the
+// first warp group, which hands its registers to the epilogue.  One 128-byte K slab (64 BF16 = two
+// K32 groups) per pipeline stage.  Tensor memory holds four 128-column buffers, one K32 partial
+// each, handed over one by one: issuer 0 fills buffers 0 and 2 with the even groups, issuer 1
+// buffers 1 and 3 with the odd groups (the two MMAs of a group must come from one thread, in order;
+// different groups are independent), and an epilogue warp gives a buffer back as soon as its 32
+// columns are in registers -- in the middle of the previous partial's arithmetic -- and asks for the
+// next partial before its arithmetic if that partial is already there.  Measured at 4096^3: 375 us with two-group buffers and
+// one issuer, 365 us with per-group buffers, 342 us with the second issuer, 335 us with the early
+// request, 326 us with the next buffer released in the middle of the arithmetic; the kernel
+// without the arithmetic takes 199 us, so the hand-over chain
+// (MMA -> commit -> load -> release, about a thousand cycles, over four buffers) and the arithmetic
+// (137 us, near the FP32 pipe's rate) add up instead of overlapping.
 #include "common.cuh"
 #include "launch.h"
 
@@ -35,13 +45,13 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
 constexpr int kStages = 6;      // A 128 x 128 B + W 128 x 128 B each: two K32 groups
-constexpr int kPairs = 2;       // tensor-memory halves, each holding the partials of two K32 groups
+constexpr int kBufs = 4;         // 128-column tensor-memory buffers, one K32 partial each
 constexpr int kEpiWarps = 4 * (kBlockN / 32);
 constexpr int kFirstEpiWarp = 4;
 constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
 constexpr int kTile = kBlockM * 128;
 constexpr int kStageBytes = kTile + kBlockN * 128;
-constexpr int kTmemCols = kPairs * 2 * kBlockN;
+constexpr int kTmemCols = kBufs * kBlockN;
 constexpr int kEpiRegs = 112;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
 constexpr int kGroupM = 8;
@@ -93,8 +103,8 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full_bar = empty_bar + kStages;
-  uint64_t* tmem_empty_bar = tmem_full_bar + kPairs;
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + kPairs);
+  uint64_t* tmem_empty_bar = tmem_full_bar + kBufs;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + kBufs);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -111,9 +121,9 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+      mbar_init(&empty_bar[s], 2);  // both issuers commit the MMAs that read the stage
     }
-    for (int s = 0; s < kPairs; ++s) {
+    for (int s = 0; s < kBufs; ++s) {
       mbar_init(&tmem_full_bar[s], 1);
       mbar_init(&tmem_empty_bar[s], kEpiWarps);
     }
@@ -157,35 +167,32 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           }
         }
       }
-    } else if (warp == 1) {
-      // ------------------------------- MMA issuer -----------------------------------------------
+    } else if (warp == 1 || warp == 2) {
+      // ------------------------------- two MMA issuers: warp 1 takes the even K32 groups, warp 2 the odd
       if (lane == 0) {
-        int stage = 0, pair = 0;
-        uint32_t phase = 0, pair_phase = 0;
+        const int id = warp - 1;
+        int stage = 0, buf = id;
+        uint32_t phase = 0, buf_phase = 0;
         bool ok = true;
         constexpr uint32_t idesc = make_idesc(1, kFmtBF16, kFmtBF16, kBlockM, kBlockN);
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
           for (int kb = 0; ok && kb < num_pairs; ++kb) {
             ok = mbar_wait_a(full_a + stage * 8, phase, status, abort_a, kTagFull | stage);
             if (!ok) break;
-            ok = mbar_wait_a(tmem_empty_a + pair * 8, pair_phase ^ 1u, status, abort_a, kTagTmemEmpty | pair);
+            ok = mbar_wait_a(tmem_empty_a + buf * 8, buf_phase ^ 1u, status, abort_a, kTagTmemEmpty | buf);
             if (!ok) break;
             tc_fence_after();
             const uint32_t st = smem_u32(smem + stage * kStageBytes);
-            const uint64_t adesc = make_desc_sw128(st);
-            const uint64_t bdesc = make_desc_sw128(st + kTile);
-            const uint32_t d = tmem_base + static_cast<uint32_t>(pair * 2 * kBlockN);
-            // each K32 group: two K16 MMAs into a fresh accumulator
+            const uint64_t adesc = make_desc_sw128(st) + id * 4;
+            const uint64_t bdesc = make_desc_sw128(st + kTile) + id * 4;
+            const uint32_t d = tmem_base + static_cast<uint32_t>(buf * kBlockN);
+            // one K32 group: two K16 MMAs into a fresh buffer
             umma_f16(d, adesc, bdesc, idesc, 0u);
             umma_f16(d, adesc + 2, bdesc + 2, idesc, 1u);
-            umma_f16(d + kBlockN, adesc + 4, bdesc + 4, idesc, 0u);
-            umma_f16(d + kBlockN, adesc + 6, bdesc + 6, idesc, 1u);
-            umma_commit_a(tmem_full_a + pair * 8);
+            umma_commit_a(tmem_full_a + buf * 8);
             umma_commit_a(empty_a + stage * 8);
-            if (++pair == kPairs) {
-              pair = 0;
-              pair_phase ^= 1u;
-            }
+            buf ^= 2;
+            if (buf == id) buf_phase ^= 1u;
             if (++stage == kStages) {
               stage = 0;
               phase ^= 1u;
@@ -197,26 +204,34 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   } else {
     reg_alloc<kEpiRegs>();
     // ------------------------------- epilogue ---------------------------------------------------
-    // Each warp owns 32 columns of one lane quarter.  The two partials of a pair go to two register
-    // buffers: while one partial is scaled and accumulated, the load of the next is in flight.
+    // Each warp owns 32 columns of one lane quarter and alternates between two register buffers:
+    // while one partial is scaled and accumulated, the load of the next is in flight.
     const int q = warp & 3;                     // tensor-memory lane quarter
     const int cs = (warp - kFirstEpiWarp) >> 2;  // 32-column slice of the 128-column partial
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(cs * 32);
-    int pair = 0;
+    int pair = 0;  // tensor-memory buffer of the next partial
     uint32_t pair_phase = 0;
     bool ok = true;
 
-    // Two passes, each a run of independent instructions: u = RN(partial * A_scale), acc = RN(acc + u).
+    // The arithmetic (accumulate_part below) is two passes, each a run of independent instructions:
+    // u = RN(partial * A_scale), acc = RN(acc + u).
     // Scalar on purpose: the packed forms (mul.rn.f32x2 followed by add.rn.f32x2, or by an fma with a
     // multiplier of one) were measured to come out contracted into one fused multiply-add -- a
     // single rounding where the recurrence has two, which changes 30 % of the results by an ulp.
-    auto accumulate = [&](uint32_t (&p)[32], float2 (&acc)[16], const float a) {
+
+    // elements of a partial handled before the next buffer is released (8, 16 and 24 measure alike)
+    constexpr int kSplit = 16;
+    // elements [lo, hi) of a partial (both even)
+    auto accumulate_part = [&](uint32_t (&p)[32], float2 (&acc)[16], const float a, const int lo, const int hi) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) p[j] = __float_as_uint(__fmul_rn(__uint_as_float(p[j]), a));
+      for (int j = 0; j < 32; ++j)
+        if (j >= lo && j < hi) p[j] = __float_as_uint(__fmul_rn(__uint_as_float(p[j]), a));
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        acc[j].x = __fadd_rn(acc[j].x, __uint_as_float(p[2 * j]));
-        acc[j].y = __fadd_rn(acc[j].y, __uint_as_float(p[2 * j + 1]));
+        if (2 * j >= lo && 2 * j < hi) {
+          acc[j].x = __fadd_rn(acc[j].x, __uint_as_float(p[2 * j]));
+          acc[j].y = __fadd_rn(acc[j].y, __uint_as_float(p[2 * j + 1]));
+        }
       }
     };
 
@@ -229,33 +244,56 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
       for (int j = 0; j < 16; ++j) acc[j] = make_float2(0.0f, 0.0f);
       uint32_t pa[32], pb[32];
-      // prologue: the first partial of the tile's first pair
-      ok = mbar_wait_a(tmem_full_a + pair * 8, pair_phase, status, abort_a, kTagTmemFull | pair);
-      if (!ok) break;
-      tc_fence_after();
-      tmem_ld_32x32(t_lane + pair * 2 * kBlockN, pa);
-      for (int kb = 0; ok && kb < num_pairs; ++kb) {
-        // ---- first partial of the pair: wait for it, start loading the second, compute
-        tmem_wait_ld_for(pa);
-        tmem_ld_32x32(t_lane + (pair * 2 + 1) * kBlockN, pb);
-        accumulate(pa, acc, a_m);
-        // ---- second partial: wait for it, start loading the next pair's first, hand the pair back
-        tmem_wait_ld_for(pb);
-        const int done_pair = pair;
-        if (++pair == kPairs) {
+      // Per-partial hand-over: a buffer goes back to the MMA thread as soon as its 32 columns are in
+      // registers; the load of partial i+1 is in flight while partial i is scaled and accumulated.
+      auto next_buf = [&]() {
+        if (++pair == kBufs) {
           pair = 0;
           pair_phase ^= 1u;
         }
-        if (kb + 1 < num_pairs) {
-          ok = mbar_wait_a(tmem_full_a + pair * 8, pair_phase, status, abort_a, kTagTmemFull | pair);
-          if (!ok) break;
-          tc_fence_after();
-          tmem_ld_32x32(t_lane + pair * 2 * kBlockN, pa);
-        }
-        tc_fence_before();  // tcgen05.wait::ld is warp-collective: every lane's loads have landed
-        if (lane == 0) mbar_arrive_a(tmem_empty_a + done_pair * 8);
-        accumulate(pb, acc, a_m);
+      };
+      // The partial in `cur` has landed and its buffer is released.  The next partial is requested
+      // first (if it is there), and its buffer is released in the MIDDLE of the current partial's
+      // arithmetic, as soon as its load can have landed -- not after the arithmetic.
+      auto release_buf = [&]() {
+        tc_fence_before();
+        if (lane == 0) mbar_arrive_a(tmem_empty_a + pair * 8);
+        next_buf();
+      };
+      ok = mbar_wait_a(tmem_full_a + pair * 8, pair_phase, status, abort_a, kTagTmemFull | pair);
+      if (!ok) break;
+      tc_fence_after();
+      tmem_ld_32x32(t_lane + pair * kBlockN, pa);
+      tmem_wait_ld_for(pa);
+      release_buf();
+#define ADG_STEP(cur, nxt, more)                                                                              \
+  {                                                                                                           \
+    bool issued = false;                                                                                      \
+    if ((more) && mbar_test_wait_a(tmem_full_a + pair * 8, pair_phase)) {                                     \
+      tc_fence_after();                                                                                       \
+      tmem_ld_32x32(t_lane + pair * kBlockN, nxt);                                                            \
+      issued = true;                                                                                          \
+    }                                                                                                         \
+    accumulate_part(cur, acc, a_m, 0, kSplit);                                                                \
+    if (issued) {                                                                                             \
+      tmem_wait_ld_for(nxt);                                                                                  \
+      release_buf();                                                                                          \
+    }                                                                                                         \
+    accumulate_part(cur, acc, a_m, kSplit, 32);                                                               \
+    if ((more) && !issued) {                                                                                  \
+      ok = mbar_wait_a(tmem_full_a + pair * 8, pair_phase, status, abort_a, kTagTmemFull | pair);             \
+      if (!ok) break;                                                                                         \
+      tc_fence_after();                                                                                       \
+      tmem_ld_32x32(t_lane + pair * kBlockN, nxt);                                                            \
+      tmem_wait_ld_for(nxt);                                                                                  \
+      release_buf();                                                                                          \
+    }                                                                                                         \
+  }
+      for (int kb = 0; ok && kb < num_pairs; ++kb) {
+        ADG_STEP(pa, pb, true)
+        ADG_STEP(pb, pa, kb + 1 < num_pairs)
       }
+#undef ADG_STEP
       if (ok && row < M) {
         float* dst = y + static_cast<long>(row) * ldy + col0;
         if (col0 + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
