@@ -178,6 +178,43 @@ __device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity, uint3
   return true;
 }
 
+// Bounded wait that lets the hardware suspend the thread (mbarrier.try_wait with a time hint) instead
+// of probing in a loop: for one-thread roles whose probes would otherwise take issue slots from the
+// arithmetic warps of their scheduler.
+__device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_suspended_a(uint32_t bar, uint32_t parity, uint32_t* status, uint32_t abort_addr,
+                                                      uint32_t tag) {
+  if (mbar_test_wait_a(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  while (!mbar_try_wait_a(bar, parity, 2000u)) {
+    uint32_t aborted;
+    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(aborted) : "r"(abort_addr) : "memory");
+    if (aborted) return false;
+    if (global_timer_ns() - t0 > kWaitTimeoutNs) {
+      asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_addr), "r"(1u) : "memory");
+      if (atomicCAS(status, 0u, static_cast<uint32_t>(kStatusWaitTimeout)) == 0u) {
+        status[1] = tag;
+        status[2] = blockIdx.x;
+        status[3] = parity;
+      }
+      return false;
+    }
+  }
+  return true;
+}
+
 // ---- TMA --------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

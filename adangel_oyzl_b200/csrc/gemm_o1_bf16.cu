@@ -13,7 +13,7 @@
 // sums are integer multiples of 2**(W_scale-128) below 2**24 of them, hence exact.  The epilogue is
 // left with one multiply by A_scale[m] and one add per partial and element: no integer-to-float
 // conversion, no per-column factor, no scale ring in shared memory, no scale warp.  Measured at
-// 4096^3: 326 us against 414 us for the INT8-operand kernel, bit-identical; converting A to BF16
+// 4096^3: 323 us against 414 us for the INT8-operand kernel, bit-identical; converting A to BF16
 // costs another 12 us per call, and W takes two bytes per element instead of one.
 //
 // Preconditions (checked on the device by the conversion kernels, which set bits in `range_flag`):
@@ -31,7 +31,8 @@
 // columns are in registers -- in the middle of the previous partial's arithmetic -- and asks for the
 // next partial before its arithmetic if that partial is already there.  Measured at 4096^3: 375 us with two-group buffers and
 // one issuer, 365 us with per-group buffers, 342 us with the second issuer, 335 us with the early
-// request, 326 us with the next buffer released in the middle of the arithmetic; the kernel
+// request, 326 us with the next buffer released in the middle of the arithmetic, 323 us with the
+// one-thread roles waiting suspended; the kernel
 // without the arithmetic takes 199 us, so the hand-over chain
 // (MMA -> commit -> load -> release, about a thousand cycles, over four buffers) and the arithmetic
 // (137 us, near the FP32 pipe's rate) add up instead of overlapping.
@@ -64,6 +65,11 @@ enum : uint32_t {
   kTagTmemEmpty = 0x5300,
   kTagTmemFull = 0x5400,
 };
+
+// The one-thread roles wait suspended by the hardware: their probe loops would take issue slots from
+// the four arithmetic warps of their scheduler (-1 % measured).
+// (suspending the epilogue warps' waits as well changes nothing).
+#define ADG_ROLE_WAIT mbar_wait_suspended_a
 
 struct TileCoord {
   int m_blk, n_blk;
@@ -154,7 +160,7 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
           const TileCoord tc = tile_coord(tile, num_m, num_n);
           for (int kb = 0; kb < num_pairs; ++kb) {
-            ok = mbar_wait_a(empty_a + stage * 8, phase ^ 1u, status, abort_a, kTagEmpty | stage);
+            ok = ADG_ROLE_WAIT(empty_a + stage * 8, phase ^ 1u, status, abort_a, kTagEmpty | stage);
             if (!ok) break;
             uint8_t* st = smem + stage * kStageBytes;
             mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
@@ -177,9 +183,9 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         constexpr uint32_t idesc = make_idesc(1, kFmtBF16, kFmtBF16, kBlockM, kBlockN);
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
           for (int kb = 0; ok && kb < num_pairs; ++kb) {
-            ok = mbar_wait_a(full_a + stage * 8, phase, status, abort_a, kTagFull | stage);
+            ok = ADG_ROLE_WAIT(full_a + stage * 8, phase, status, abort_a, kTagFull | stage);
             if (!ok) break;
-            ok = mbar_wait_a(tmem_empty_a + buf * 8, buf_phase ^ 1u, status, abort_a, kTagTmemEmpty | buf);
+            ok = ADG_ROLE_WAIT(tmem_empty_a + buf * 8, buf_phase ^ 1u, status, abort_a, kTagTmemEmpty | buf);
             if (!ok) break;
             tc_fence_after();
             const uint32_t st = smem_u32(smem + stage * kStageBytes);
