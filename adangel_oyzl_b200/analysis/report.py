@@ -36,7 +36,7 @@ def generate_report(run_dir, output_dir, allow_unstable: bool = False) -> Path:
             flat.append({**base, "stage": stage, **stats})
     frame = pd.DataFrame(flat)
 
-    conversion_names = {"o0": ["weight_conversion", "activation_conversion"], "o1": ["weight_conversion"],
+    conversion_names = {"o0": ["weight_conversion", "activation_conversion"], "o1": ["weight_conversion", "activation_conversion"],
                         "o2": ["weight_conversion", "activation_conversion"]}
     conv = frame[frame["mode"].eq("conversion_only")].copy()
     conv = conv[conv.apply(lambda r: r["stage"] in conversion_names[r["variant"]], axis=1)]

@@ -50,11 +50,17 @@ def _conversion_bytes(variant: str, stage: str, m: int, n: int, k: int) -> int:
     return sizes.get((variant, stage), 0)
 
 
-def _fused_conversion_bytes(variant: str, stage: str, m: int, n: int, k: int) -> int:
-    """What the fused O2 activation kernel of this build actually moves (one natural and one tiled
-    scale write, no separate re-layout pass); equal to the reference figure for the other stages."""
+def _fused_conversion_bytes(variant: str, stage: str, m: int, n: int, k: int, o1_bf16: bool = False) -> int:
+    """What the conversion kernels of this build actually move: the fused O2 activation kernel (one
+    natural and one tiled scale write, no separate re-layout pass) and, when O1 runs on BF16 operands,
+    its activation conversion and the second (BF16) form of its weight; equal to the reference figure
+    for the other stages."""
     if (variant, stage) == ("o2", "activation_conversion"):
         return m * k + 4 * m + m * k // 2 + 2 * m * (k // 32)
+    if variant == "o1" and o1_bf16 and stage == "activation_conversion":
+        return m * k + 4 * m + 2 * m * k
+    if variant == "o1" and o1_bf16 and stage == "weight_conversion":
+        return (n * k // 2 + n * k) + (n * k // 2 + n * (k // 32) + 2 * n * k)
     return _conversion_bytes(variant, stage, m, n, k)
 
 
@@ -93,7 +99,7 @@ def _shapes(config: dict) -> list[tuple[int, int, int]]:
     return [(int(matrix["m"]), int(matrix["n"]), int(matrix["k"]))]
 
 
-def _roofline(variant: str, summaries: dict, m: int, n: int, k: int) -> dict:
+def _roofline(variant: str, summaries: dict, m: int, n: int, k: int, o1_bf16: bool = False) -> dict:
     out = {}
     gemm = summaries.get("gemm")
     if gemm and gemm["median_ms"] > 0:
@@ -102,7 +108,7 @@ def _roofline(variant: str, summaries: dict, m: int, n: int, k: int) -> dict:
                        "fraction_of_nominal": tf / NOMINAL_TFLOPS[variant]}
     for stage in ("weight_conversion", "activation_conversion"):
         stats = summaries.get(stage)
-        nbytes = _fused_conversion_bytes(variant, stage, m, n, k)
+        nbytes = _fused_conversion_bytes(variant, stage, m, n, k, o1_bf16)
         if stats and nbytes and stats["median_ms"] > 0:
             gbs = nbytes / stats["median_ms"] / 1.0e6
             out[stage] = {"bound": "hbm", "achieved_gbs": gbs, "nominal_peak_gbs": NOMINAL_HBM_GBS,
@@ -201,7 +207,8 @@ def run_experiment(config_path, output_dir, *, sample_limit=None, warmup_overrid
                         "timing_method": payload.get("timing_method"),
                         "stable_cv": stable,
                         "valid": stable,
-                        "roofline": _roofline(variant, summaries, m, n, k),
+                        "roofline": _roofline(variant, summaries, m, n, k,
+                                              o1_bf16=(payload.get("kernel") or {}).get("kernel_symbol") == "gemm_o1_bf16_kernel"),
                     }
                     records.append((record, payload["output"] if mode == "compute_only" else None))
                     del payload

@@ -78,7 +78,7 @@ struct DeviceBuffer {
 
 extern "C" {
 
-int adg_abi_version(void) { return 100; }
+int adg_abi_version(void) { return 101; }
 
 const char* adg_last_error(void) { return last_error_cstr(); }
 
@@ -222,11 +222,34 @@ int adg_benchmark(adg_bench_args* a) {
     conv_w = [&]() { return launch_mxfp4_to_fp16(a->w_mxfp4, a->w_scale, a->conv_weight, N, K, stream); };
     conv_a = [&]() { return launch_int8_to_fp16(a->a_int8, a->a_scale, a->conv_act, M, K, stream); };
   } else if (a->variant == 1) {
-    if (int rc = plan_o1(&plan, a->a_int8, a->a_scale, a->conv_weight, a->w_scale, a->output, nullptr, M, N, K, N))
-      return rc;
-    conv_w = [&]() { return launch_mxfp4_to_int8(a->w_mxfp4, a->conv_weight, N, K, stream); };
-    conv_a = []() { return 0; };
-    has_a = false;
+    bool on_bf16 = a->conv_weight_bf16 != nullptr && a->conv_act_bf16 != nullptr && a->range_flag != nullptr && M > 64;
+    if (on_bf16) {
+      // decided once, outside every timed region: are the operands inside the BF16-operand kernel's exact range?
+      uint32_t flag = 1;
+      if (int rc = check_cuda(cudaMemsetAsync(a->range_flag, 0, sizeof(uint32_t), stream), "cudaMemsetAsync")) return rc;
+      if (launch_mxfp4_to_bf16_scaled(a->w_mxfp4, a->w_scale, a->conv_weight_bf16, a->range_flag, N, K, stream) ||
+          launch_int8_to_bf16(a->a_int8, a->a_scale, a->conv_act_bf16, a->range_flag, M, K, stream))
+        return fail("O1 operand conversion launch failed");
+      if (int rc = check_cuda(cudaMemcpyAsync(&flag, a->range_flag, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream), "D2H flag"))
+        return rc;
+      if (int rc = check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize")) return rc;
+      on_bf16 = flag == 0;
+    }
+    if (on_bf16) {
+      if (int rc = plan_o1_bf16(&plan, a->conv_act_bf16, a->a_scale, a->conv_weight_bf16, a->output, a->range_flag, M, N, K, N))
+        return rc;
+      conv_w = [&]() {
+        if (int rc = launch_mxfp4_to_int8(a->w_mxfp4, a->conv_weight, N, K, stream)) return rc;
+        return launch_mxfp4_to_bf16_scaled(a->w_mxfp4, a->w_scale, a->conv_weight_bf16, a->range_flag, N, K, stream);
+      };
+      conv_a = [&]() { return launch_int8_to_bf16(a->a_int8, a->a_scale, a->conv_act_bf16, a->range_flag, M, K, stream); };
+    } else {
+      if (int rc = plan_o1(&plan, a->a_int8, a->a_scale, a->conv_weight, a->w_scale, a->output, nullptr, M, N, K, N))
+        return rc;
+      conv_w = [&]() { return launch_mxfp4_to_int8(a->w_mxfp4, a->conv_weight, N, K, stream); };
+      conv_a = []() { return 0; };
+      has_a = false;
+    }
   } else {
     if (int rc = plan_o2(&plan, a->conv_act, a->conv_act_sf_tiled, a->w_mxfp4, a->conv_weight, a->output, M, N, K, N))
       return rc;

@@ -37,6 +37,7 @@ class BenchArgs(ctypes.Structure):
         ("t_weight", POINTER(c_float)), ("t_activation", POINTER(c_float)),
         ("t_gemm", POINTER(c_float)), ("t_total", POINTER(c_float)),
         ("stages_out", c_uint32), ("stream", c_void_p),
+        ("conv_weight_bf16", c_void_p), ("conv_act_bf16", c_void_p), ("range_flag", c_void_p),
     ]
 
 
@@ -162,7 +163,7 @@ def _timing_metadata(mode: str, inner: int) -> dict:
     }
 
 
-def kernel_metadata(variant: str, m: int, n: int, k: int) -> dict:
+def kernel_metadata(variant: str, m: int, n: int, k: int, o1_bf16: bool = False) -> dict:
     block_n = 128 if variant == "o1" or n <= 128 else 256
     common = {
         "library": "hand-written sm_100a (no CUTLASS, no cuBLAS)",
@@ -193,6 +194,12 @@ def kernel_metadata(variant: str, m: int, n: int, k: int) -> dict:
                       stages=8, threads=384, tile=[16, 128], persistent=False, mma_shape=[128, 16, 32],
                       partial_rescale="per-K32, FP32 registers",
                       accumulator="INT32 partial in tensor memory, FP32 accumulate in registers")
+    elif variant == "o1" and o1_bf16:
+        # weight scale folded into a BF16 operand: the partial leaves the tensor core as float(P) * 2^(s-128)
+        common.update(mma_family="tcgen05.mma.cta_group::1.kind::f16 (bf16 operands; exact integer partials)",
+                      kernel_symbol="gemm_o1_bf16_kernel", stages=6, threads=640, mma_shape=[128, 128, 16],
+                      partial_rescale="per-K32, FP32 registers",
+                      accumulator="FP32 partial in tensor memory (four 128-column buffers), FP32 accumulate in registers")
     elif variant == "o1":
         common.update(mma_family="tcgen05.mma.cta_group::1.kind::i8", kernel_symbol="gemm_o1_kernel",
                       stages=6, scale_stages=8, threads=640, mma_shape=[128, 128, 32],
@@ -249,11 +256,17 @@ def benchmark(variant, mode, a_int8, a_scale, w_mxfp4, w_scale, warmup, repeats,
 
     output = empty((m, n), torch.float32)
     conv_weight = conv_act = conv_act_sf = conv_act_sf_tiled = None
+    conv_weight_bf16 = conv_act_bf16 = range_flag = None
     if variant == "o0":
         conv_weight = empty((n, k), torch.float16)
         conv_act = empty((m, k), torch.float16)
     elif variant == "o1":
         conv_weight = empty((n, k), torch.int8)
+        if m > 64:
+            # buffers of the BF16-operand O1 kernel (used while the operands are inside its exact range)
+            conv_weight_bf16 = empty((n, k), torch.bfloat16)
+            conv_act_bf16 = empty((m, k), torch.bfloat16)
+            range_flag = torch.zeros(1, dtype=torch.int32, device=device)
     else:
         conv_weight = empty((lib.adg_o2_tiled_scale_bytes(n, k),), torch.uint8)
         conv_act = empty((m, k // 2), torch.uint8)
@@ -272,6 +285,9 @@ def benchmark(variant, mode, a_int8, a_scale, w_mxfp4, w_scale, warmup, repeats,
     args.conv_act = conv_act.data_ptr() if conv_act is not None else None
     args.conv_act_sf = conv_act_sf.data_ptr() if conv_act_sf is not None else None
     args.conv_act_sf_tiled = conv_act_sf_tiled.data_ptr() if conv_act_sf_tiled is not None else None
+    args.conv_weight_bf16 = conv_weight_bf16.data_ptr() if conv_weight_bf16 is not None else None
+    args.conv_act_bf16 = conv_act_bf16.data_ptr() if conv_act_bf16 is not None else None
+    args.range_flag = range_flag.data_ptr() if range_flag is not None else None
     args.t_weight = ctypes.cast(times["weight_conversion"], POINTER(c_float))
     args.t_activation = ctypes.cast(times["activation_conversion"], POINTER(c_float))
     args.t_gemm = ctypes.cast(times["gemm"], POINTER(c_float))
@@ -293,7 +309,7 @@ def benchmark(variant, mode, a_int8, a_scale, w_mxfp4, w_scale, warmup, repeats,
         "converted_activation": converted_activation,
         "timings_ms": timings,
         "timing_method": _timing_metadata(mode, conversion_inner_repeats),
-        "kernel": kernel_metadata(variant, m, n, k),
+        "kernel": kernel_metadata(variant, m, n, k, o1_bf16=range_flag is not None and int(range_flag.item()) == 0),
     }
 
 

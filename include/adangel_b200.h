@@ -201,6 +201,14 @@ typedef struct adg_bench_args {
   float* t_total;
   uint32_t stages_out;
   void* stream;
+  /* O1 only, optional (all three or none; ABI 101): bf16 [N,K], bf16 [M,K] and one 32-bit device word.  When
+   * given, M > 64 and the operands lie inside adg_gemm_o1_bf16's exact range (decided once, before any
+   * timing, by converting both and reading the word), O1 runs on BF16 operands: the activation
+   * conversion stage is adg_int8_to_bf16, the weight conversion stage writes both conv_weight (INT8, the
+   * tensor returned to the caller) and conv_weight_bf16, the GEMM stage is adg_gemm_o1_bf16 -- same bits. */
+  void* conv_weight_bf16;
+  void* conv_act_bf16;
+  void* range_flag;
 } adg_bench_args;
 
 /* Runs the reference's timing protocol for one variant and mode (warm-up, `repeats` directly timed

@@ -78,7 +78,9 @@ def test_timing_mode_contract(golden_dir, variant, mode):
     _, _, cuda = _prepared(golden_dir)
     native = require_variant(variant)
     result = native.benchmark(variant, mode, cuda.A_int8, cuda.A_scale, cuda.W_mxfp4, cuda.W_scale, 2, 3)
-    has_act = variant != "o1"
+    # O1 has an activation conversion stage only when it runs on BF16 operands (M > 64, scales inside that
+    # kernel's exact range); on the reference's INT8 operands it has none
+    has_act = variant != "o1" or result["kernel"]["kernel_symbol"] == "gemm_o1_bf16_kernel"
     expected = {
         "conversion_only": {"weight_conversion", "total"} | ({"activation_conversion"} if has_act else set()),
         "compute_only": {"gemm", "total"},
@@ -197,3 +199,24 @@ def test_o1_host_session_operand_paths(golden_dir):
     session = HostSession("o1", 256, w_mx, odd_w)
     np.testing.assert_array_equal(session.run(a_int8, a_scale, y), want_w)
     session.close()
+
+
+def test_harness_o1_operand_paths():
+    # the timing harness runs O1 on BF16 operands while the scales are inside that kernel's exact range and on
+    # the reference's INT8 operands otherwise; both give the oracle's bits and the INT8 form of W is returned
+    import torch
+
+    from adangel_oyzl_b200.ops import _sm100
+
+    a_int8, a_scale, w_mx, w_sc = (np.ascontiguousarray(a) for a in orc.canonical_inputs(192, 256, 256, seed=43))
+    for odd in (False, True):
+        sc = w_sc.copy()
+        if odd:
+            sc[9, 1] = 231
+        dev = [torch.from_numpy(x).cuda() for x in (a_int8, a_scale, w_mx, sc)]
+        result = _sm100.benchmark("o1", "steady_state", *dev, 1, 2)
+        want = orc.run_o1(a_int8, a_scale, w_mx, sc)
+        assert result["kernel"]["kernel_symbol"] == ("gemm_o1_kernel" if odd else "gemm_o1_bf16_kernel")
+        assert ("activation_conversion" in result["timings_ms"]) == (not odd)
+        np.testing.assert_array_equal(result["output"].cpu().numpy(), want["output"])
+        np.testing.assert_array_equal(result["converted_weight"].cpu().numpy(), orc.mxfp4_to_int8_base(w_mx))
