@@ -212,3 +212,22 @@ def test_o1_bf16_operands_refuse_out_of_range(K):
     y1 = K.gemm_o1(da, ds, K.mxfp4_to_int8(dw), dws)
     K.check_status()
     np.testing.assert_array_equal(y1.cpu().numpy(), orc.run_o1(a_int8, a_scale, w_mx, w_sc)["output"])
+
+
+def test_cta_pair_output_column_block(K):
+    # pair-tile shapes writing Y as a column block of a wider matrix (ldy > N), O0 and O2
+    import torch
+
+    a_int8, a_scale, w_mx, w_sc = orc.canonical_inputs(512, 256, 256, seed=37)
+    da, ds, dw, dws = to_cuda(a_int8, a_scale, w_mx, w_sc)
+    wide = torch.full((512, 1024), -7.0, device="cuda")
+    K.gemm_o0(K.int8_to_fp16(da, ds), K.mxfp4_to_fp16(dw, dws), out=wide[:, 128:384])
+    codes, _, sfa = K.o2_quantize_activation(da, ds)
+    K.gemm_o2(codes, sfa, dw, K.o2_tile_scales(dws), out=wide[:, 640:896])
+    K.check_status()
+    got = wide.cpu().numpy()
+    np.testing.assert_allclose(got[:, 128:384], orc.run_o0(a_int8, a_scale, w_mx, w_sc)["output"], rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(got[:, 640:896], orc.run_o2(a_int8, a_scale, w_mx, w_sc)["output"], rtol=RTOL, atol=ATOL)
+    untouched = np.ones(1024, dtype=bool)
+    untouched[128:384] = untouched[640:896] = False
+    assert (got[:, untouched] == -7.0).all()
