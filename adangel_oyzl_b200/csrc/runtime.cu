@@ -139,15 +139,24 @@ int encode_word_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
   return 0;
 }
 
-// O0/O2 run on CTA pairs (cta_group::2, 256 x 256 tiles: 3 - 7 % faster at large shapes, bit-identical)
-// when the shape has at least one full pair tile and pairing rows wastes little: an even number of
-// 128-row blocks, or so many that the padded half block is under 3 %.  ADG_TWO_CTA=0 in the
-// environment (read at every plan) keeps every shape on the single-CTA kernel.
-bool pair_enabled(int M, int N) {
+// O0/O2 run on CTA pairs (cta_group::2, 256 x 256 tiles, bit-identical to the single-CTA kernels) where
+// that was measured to pay: the shape must hold a full pair tile and pair up its 128-row blocks with
+// little waste (an even number of them, or so many that the padded half block is under 3 %), and be
+// large -- at least two waves of pair tiles and K >= 2048 for O0 (3 - 7 % faster from there), at least
+// seven waves and K >= 4096 for O2 (3 - 7 %; below that its single accumulator stage and the longer
+// hand-overs between two CTAs cost more than the halved W traffic saves: -2 % at 2048 x 11008 x 4096,
+// -17 % at K = 512).  ADG_TWO_CTA in the environment (read at every plan): 0 = never, 1 = whenever the
+// shape holds a full pair tile.
+bool pair_enabled(int variant, int M, int N, int K, int sm_count) {
+  if (M < pair_tile_m() || N < pair_tile_n()) return false;
   const char* e = getenv("ADG_TWO_CTA");
   if (e != nullptr && e[0] == '0') return false;
+  if (e != nullptr && e[0] == '1') return true;
   const int row_blocks = (M + 127) / 128;
-  return M >= pair_tile_m() && N >= pair_tile_n() && (row_blocks % 2 == 0 || row_blocks >= 33);
+  if (row_blocks % 2 != 0 && row_blocks < 33) return false;
+  const long tiles = static_cast<long>((M + pair_tile_m() - 1) / pair_tile_m()) * ((N + pair_tile_n() - 1) / pair_tile_n());
+  const long clusters = sm_count / 2;
+  return variant == 0 ? (tiles >= 2 * clusters && K >= 2048) : (tiles >= 7 * clusters && K >= 4096);
 }
 
 int finish_pair_plan(GemmPlan* plan, int sm_count, uint32_t* status) {
@@ -206,7 +215,7 @@ int plan_o0(GemmPlan* plan, const void* a_fp16, const void* w_fp16, float* y, in
   if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a_fp16, M, K,
                                     static_cast<uint64_t>(K) * 2, 128, 64))
     return rc;
-  if (pair_enabled(M, N)) {
+  if (pair_enabled(0, M, N, K, ctx->sm_count)) {
     if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, w_fp16, N, K,
                                       static_cast<uint64_t>(K) * 2, pair_tile_n() / 2, 64))
       return rc;
@@ -283,7 +292,7 @@ int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const vo
   const uint64_t kbytes = static_cast<uint64_t>(K) / 2;
   if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_mxfp4, M, kbytes, kbytes, 128, 128))
     return rc;
-  if (pair_enabled(M, N)) {
+  if (pair_enabled(2, M, N, K, ctx->sm_count)) {
     if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_mxfp4, N, kbytes, kbytes,
                                       pair_tile_n() / 2, 128))
       return rc;

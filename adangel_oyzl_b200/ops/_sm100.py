@@ -176,10 +176,20 @@ def kernel_metadata(variant: str, m: int, n: int, k: int, o1_bf16: bool = False)
         "tile": [128, block_n],
         "persistent": True,
     }
-    # the planner's rule for CTA pairs (csrc/runtime.cu, pair_enabled)
+    # the planner's rule for CTA pairs (csrc/runtime.cu, pair_enabled; 148 SMs = 74 clusters)
     row_blocks = (m + 127) // 128
-    pair = (os.environ.get("ADG_TWO_CTA", "1")[:1] != "0" and m >= 256 and n >= 256
-            and (row_blocks % 2 == 0 or row_blocks >= 33))
+    pair_tiles = ((m + 255) // 256) * ((n + 255) // 256)
+    switch = os.environ.get("ADG_TWO_CTA", "")[:1]
+    if m < 256 or n < 256 or switch == "0":
+        pair = False
+    elif switch == "1":
+        pair = True
+    elif row_blocks % 2 != 0 and row_blocks < 33:
+        pair = False
+    elif variant == "o0":
+        pair = pair_tiles >= 2 * 74 and k >= 2048
+    else:
+        pair = pair_tiles >= 7 * 74 and k >= 4096
     if variant == "o0" and pair:
         common.update(mma_family="tcgen05.mma.cta_group::2.kind::f16", kernel_symbol="gemm_pair_kernel<0>",
                       stages=6, accumulator_stages=2, threads=384, tile=[256, 256], cluster=[2, 1, 1],

@@ -157,14 +157,14 @@ def test_full_size_4096(K):
 
 @pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 320), (1000, 777, 128), (4224, 512, 256)])
 def test_cta_pair_kernels_match_single_cta(K, shape, monkeypatch):
-    # O0/O2 on CTA pairs (cta_group::2, the default where a full 256 x 256 pair tile exists) give the
+    # O0/O2 on CTA pairs (cta_group::2, the default for large shapes) give the
     # same bits as the single-CTA kernels; (1000, 777, .) has ragged edges and an unaligned Y pitch,
     # (4224, ...) an odd number of row blocks
     m, n, k = shape
     args = orc.canonical_inputs(m, n, k, seed=23)
     monkeypatch.setenv("ADG_TWO_CTA", "0")
     single = _gpu_all(K, *args)
-    monkeypatch.delenv("ADG_TWO_CTA")
+    monkeypatch.setenv("ADG_TWO_CTA", "1")  # pairs wherever a full pair tile exists, not only where they pay
     paired = _gpu_all(K, *args)
     np.testing.assert_array_equal(paired[0], single[0])
     np.testing.assert_array_equal(paired[2], single[2])
@@ -214,9 +214,11 @@ def test_o1_bf16_operands_refuse_out_of_range(K):
     np.testing.assert_array_equal(y1.cpu().numpy(), orc.run_o1(a_int8, a_scale, w_mx, w_sc)["output"])
 
 
-def test_cta_pair_output_column_block(K):
+def test_cta_pair_output_column_block(K, monkeypatch):
     # pair-tile shapes writing Y as a column block of a wider matrix (ldy > N), O0 and O2
     import torch
+
+    monkeypatch.setenv("ADG_TWO_CTA", "1")
 
     a_int8, a_scale, w_mx, w_sc = orc.canonical_inputs(512, 256, 256, seed=37)
     da, ds, dw, dws = to_cuda(a_int8, a_scale, w_mx, w_sc)
