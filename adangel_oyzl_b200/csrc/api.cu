@@ -194,6 +194,29 @@ int adg_gemm_o1_bf16(const void* a_bf16, const void* a_scale, const void* w_bf16
   return run_plan(plan, as_stream(stream));
 }
 
+int adg_o1_linear(const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale, const void* w_bf16,
+                  void* a_bf16_workspace, void* flags, float* y, int M, int N, int K, int ldy, void* stream) {
+  if (flags == nullptr) return fail("flags must not be NULL");
+  cudaStream_t st = as_stream(stream);
+  GemmPlan plan;
+  if (M <= 64 || w_bf16 == nullptr || a_bf16_workspace == nullptr) {
+    if (int rc = plan_o1(&plan, a_int8, a_scale, w_int8, w_scale, y, nullptr, M, N, K, ldy)) return rc;
+    return run_plan(plan, st);
+  }
+  // flags[0]: the weight's word (set once by adg_mxfp4_to_bf16_scaled); flags[1]: this call's word =
+  // the weight's bits plus the activation's.  The BF16-operand kernel computes when the call's word is
+  // zero and returns at once otherwise; the INT8-operand kernel behind it does the opposite.
+  uint32_t* words = static_cast<uint32_t*>(flags);
+  if (int rc = check_cuda(cudaMemcpyAsync(words + 1, words, sizeof(uint32_t), cudaMemcpyDeviceToDevice, st), "flag copy")) return rc;
+  if (launch_int8_to_bf16(a_int8, a_scale, a_bf16_workspace, words + 1, M, K, st)) return fail("int8_to_bf16 launch failed");
+  if (int rc = plan_o1_bf16(&plan, a_bf16_workspace, a_scale, w_bf16, y, words + 1, M, N, K, ldy)) return rc;
+  plan.quiet_refusal = 1;
+  if (int rc = run_plan(plan, st)) return rc;
+  if (int rc = plan_o1(&plan, a_int8, a_scale, w_int8, w_scale, y, nullptr, M, N, K, ldy)) return rc;
+  plan.only_if_flag = words + 1;
+  return run_plan(plan, st);
+}
+
 int adg_gemm_o2(const void* a_mxfp4, const void* a_sf_tiled, const void* w_mxfp4, const void* w_sf_tiled, float* y,
                 int M, int N, int K, int ldy, void* stream) {
   GemmPlan plan;

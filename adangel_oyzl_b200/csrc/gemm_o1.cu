@@ -86,7 +86,10 @@ template <bool kDump>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const float* __restrict__ a_scale, const uint8_t* __restrict__ w_scale, float* __restrict__ y,
-               int32_t* __restrict__ partial_dump, int M, int N, int K, int ldy, uint32_t* status) {
+               int32_t* __restrict__ partial_dump, int M, int N, int K, int ldy, uint32_t* status,
+               const uint32_t* __restrict__ only_if_flag) {
+  // second half of a sync-free fallback: run only when the BF16-operand kernel in front refused
+  if (only_if_flag != nullptr && *only_if_flag == 0u) return;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* sc_ring = reinterpret_cast<float*>(smem + kStages * kStageBytes);
@@ -451,7 +454,7 @@ int run_gemm_o1(const GemmPlan& p, cudaStream_t stream) {
 #endif
     gemm_o1_kernel<true><<<p.grid, kThreads, kSmemBytes, stream>>>(
         p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y,
-        p.partial_dump, p.M, p.N, p.K, p.ldy, p.status);
+        p.partial_dump, p.M, p.N, p.K, p.ldy, p.status, p.only_if_flag);
   } else {
     gemm_o1_kernel<false><<<p.grid, kThreads, kSmemBytes, stream>>>(
         p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y,
@@ -460,7 +463,7 @@ int run_gemm_o1(const GemmPlan& p, cudaStream_t stream) {
 #else
         nullptr,
 #endif
-        p.M, p.N, p.K, p.ldy, p.status);
+        p.M, p.N, p.K, p.ldy, p.status, p.only_if_flag);
   }
   return check_cuda(cudaGetLastError(), "gemm_o1_kernel launch");
 }

@@ -86,6 +86,7 @@ struct GemmPlan {
   int skinny = 0, grid_y = 1;
   int o1_bf16 = 0;                       // O1 with BF16 operands (weight scale folded into W)
   const uint32_t* range_flag = nullptr;  // O1 BF16: device word set by the operand conversions
+  const uint32_t* only_if_flag = nullptr;  // O1 INT8: run only when this device word is non-zero
   int quiet_refusal = 0;                 // O1 BF16: a set flag makes the kernel return without an error status
   int pair = 0;  // O0/O2 on CTA pairs (cta_group::2): tm_b has 128-row boxes, grid = 2 x clusters
   uint32_t* status = nullptr;

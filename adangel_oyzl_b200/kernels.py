@@ -230,6 +230,41 @@ def gemm_o1_bf16(a_bf16, a_scale, w_bf16, range_flag, out=None):
     return out
 
 
+class O1Weights:
+    """W in both forms O1 can consume, made once: INT8 (every input) and BF16 with the scale folded in
+    (the fast kernel), plus the two flag words :func:`o1_linear` needs."""
+
+    def __init__(self, w_mxfp4, w_scale):
+        import torch
+
+        self.w_scale = w_scale
+        self.w_int8 = mxfp4_to_int8(w_mxfp4)
+        self.flags = torch.zeros(2, dtype=torch.int32, device=w_mxfp4.device)
+        self.w_bf16 = mxfp4_to_bf16_scaled(w_mxfp4, w_scale, self.flags)
+        self._workspace = None
+
+    def workspace(self, m, k):
+        import torch
+
+        if self._workspace is None or self._workspace.numel() < m * k:
+            self._workspace = torch.empty(m * k, dtype=torch.bfloat16, device=self.w_int8.device)
+        return self._workspace
+
+
+def o1_linear(a_int8, a_scale, weights: O1Weights, out=None):
+    """O1 for every input without a host synchronisation: the BF16-operand kernel, and behind it the
+    INT8-operand kernel, which runs only if the first one refused (``adg_o1_linear``)."""
+    m, k = a_int8.shape
+    n = weights.w_int8.shape[0]
+    out, ldy = _output(out, m, n, a_int8.device)
+    ws = weights.workspace(m, k)
+    with torch_device(a_int8.device):
+        _sm100._check(_lib().adg_o1_linear(
+            a_int8.data_ptr(), a_scale.data_ptr(), weights.w_int8.data_ptr(), weights.w_scale.data_ptr(),
+            weights.w_bf16.data_ptr(), ws.data_ptr(), weights.flags.data_ptr(), out.data_ptr(), m, n, k, ldy, _stream(out)))
+    return out
+
+
 def gemm_o2(a_mxfp4, a_sf_tiled, w_mxfp4, w_sf_tiled, out=None):
     import torch
 

@@ -71,7 +71,8 @@ class ShardedWeights:
     w_mxfp4: object
     w_scale: object
     w_fp16: object = None    # O0
-    w_int8: object = None    # O1
+    w_int8: object = None    # O1 (INT8 operands: every input)
+    o1: object = None        # O1: kernels.O1Weights (both operand forms + flag words) for kernels.o1_linear
     w_sf_tiled: object = None  # O2
 
     @property
@@ -95,7 +96,8 @@ def shard_weights(w_mxfp4, w_scale, world_size: int, rank: int, variants=("o0", 
     if "o0" in variants:
         shard.w_fp16 = kernels.mxfp4_to_fp16(wm, ws)
     if "o1" in variants:
-        shard.w_int8 = kernels.mxfp4_to_int8(wm)
+        shard.o1 = kernels.O1Weights(wm, ws)
+        shard.w_int8 = shard.o1.w_int8
     if "o2" in variants:
         shard.w_sf_tiled = kernels.o2_tile_scales(ws)
     return shard
@@ -110,6 +112,8 @@ def sharded_gemm(variant: str, a_int8, a_scale, shard: ShardedWeights, out=None)
     if variant == "o0":
         return kernels.gemm_o0(kernels.int8_to_fp16(a_int8, a_scale), shard.w_fp16, out=out)
     if variant == "o1":
+        if getattr(shard, "o1", None) is not None:
+            return kernels.o1_linear(a_int8, a_scale, shard.o1, out=out)
         return kernels.gemm_o1(a_int8, a_scale, shard.w_int8, shard.w_scale, out=out)
     if variant == "o2":
         codes, _, sfa = kernels.o2_quantize_activation(a_int8, a_scale, want_natural=False)

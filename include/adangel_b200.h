@@ -142,6 +142,15 @@ int adg_gemm_o1(const void* a_int8, const void* a_scale, const void* w_int8, con
 int adg_gemm_o1_bf16(const void* a_bf16, const void* a_scale, const void* w_bf16, float* y, const void* range_flag, int M,
                      int N, int K, int ldy, void* stream);
 
+/* O1 in one call, for every input and without a host synchronisation: converts A to BF16, runs
+ * adg_gemm_o1_bf16, and behind it the INT8-operand kernel, which returns at once unless the first
+ * one refused (operands outside its exact range).  flags points at two 32-bit device words: [0] is the
+ * weight's word, zeroed by the caller and then written by adg_mxfp4_to_bf16_scaled when w_bf16 was made;
+ * [1] is scratch.  a_bf16_workspace holds M*K BF16 values.  With M <= 64, or w_bf16 / the workspace NULL,
+ * only the INT8-operand kernels run.  No reference counterpart. */
+int adg_o1_linear(const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale, const void* w_bf16,
+                  void* a_bf16_workspace, void* flags, float* y, int M, int N, int K, int ldy, void* stream);
+
 /* O2 GEMM: block-scaled MXFP4 x MXFP4 (tcgen05 kind::mxf4.block_scale), scales in tiled layout.
  * Replaces the CUTLASS block-scaled GEMM (csrc/sm120/o2_cutlass.cu:35-93, :394-472). */
 int adg_gemm_o2(const void* a_mxfp4, const void* a_sf_tiled, const void* w_mxfp4, const void* w_sf_tiled, float* y,

@@ -233,3 +233,24 @@ def test_cta_pair_output_column_block(K, monkeypatch):
     untouched = np.ones(1024, dtype=bool)
     untouched[128:384] = untouched[640:896] = False
     assert (got[:, untouched] == -7.0).all()
+
+
+def test_o1_linear_every_input_without_sync(K):
+    # adg_o1_linear: the BF16-operand kernel, and behind it the INT8-operand kernel that runs only if the first
+    # refused; oracle bits for in-range operands, for an out-of-range activation scale, for an out-of-range
+    # weight scale code and for decode-sized M, and never an error status
+    import torch
+
+    a_int8, a_scale, w_mx, w_sc = orc.canonical_inputs(320, 384, 512, seed=47)
+    odd_a = a_scale.copy()
+    odd_a[11] = np.float32(2.0 ** -50)
+    odd_w = w_sc.copy()
+    odd_w[17, 3] = 240
+    for scale_a, scale_w, rows in ((a_scale, w_sc, 320), (odd_a, w_sc, 320), (a_scale, odd_w, 320), (a_scale, w_sc, 48)):
+        da, ds, dw, dws = to_cuda(a_int8[:rows], scale_a[:rows], w_mx, scale_w)
+        weights = K.O1Weights(dw, dws)
+        y = torch.full((rows, 384), float("nan"), device="cuda")
+        for _ in range(2):  # the per-call flag word is rebuilt on every call
+            K.o1_linear(da, ds, weights, out=y)
+        K.check_status()
+        np.testing.assert_array_equal(y.cpu().numpy(), orc.run_o1(a_int8[:rows], scale_a[:rows], w_mx, scale_w)["output"])
