@@ -18,7 +18,7 @@ from pathlib import Path
 
 from .build import ARCH_FLAGS, CSRC, INCLUDE, _nvcc
 
-# kernel name fragment -> (required instruction patterns, description)
+# kernel name pattern (regular expression on the mangled entry name) -> (required instruction patterns, description)
 REQUIRED = {
     "gemm_acc_kernelILi0E": ([r"cp\.async\.bulk\.tensor\.2d\.shared::cluster\.global", r"tcgen05\.mma\.cta_group::1\.kind::f16",
                               r"tcgen05\.ld\.sync\.aligned\.32x32b", r"cp\.async\.bulk\.tensor\.2d\.global\.shared::cta"],
@@ -46,6 +46,13 @@ REQUIRED = {
                               "O2 decode GEMM: TMA loads, block-scaled MXFP4 MMA"),
     "gemm_o1_skinny_kernel": ([r"cp\.async\.bulk\.tensor\.2d\.shared::cluster\.global", r"tcgen05\.mma\.cta_group::1\.kind::i8"],
                               "O1 decode GEMM: TMA loads, kind::i8 MMA"),
+    r"gemm_acc_kernelILi1E": ([r"cp\.async\.bulk\.tensor\.2d\.shared::cluster\.global", r"tcgen05\.mma\.cta_group::1\.kind::i8",
+                               r"tcgen05\.ld\.sync\.aligned\.32x32b", r"cvt\.rn\.f32\.s32"],
+                              "o1x GEMM: TMA loads, kind::i8 MMA over all of K, tensor-memory loads, one INT32 -> FP32 conversion"),
+    r"gemm_(acc|pair)_kernelILi[02]E(Li\d+E)?Lb1E": ([r"setmaxnreg", r"red\.release\.gpu\.global\.add", r"ld\.acquire\.gpu\.global",
+                                                        r"fence\.proxy\.async"],
+                                                       "O0 / O2 GEMMs with converter warps: register re-balancing, row counters "
+                                                       "published with release / read with acquire, proxy fences around them"),
     "o2_quantize_kernel": ([r"cvt\.rn\.satfinite\.e2m1x2\.f32"], "O2 activation re-quantization: hardware E2M1 conversion"),
     "mxfp4_to_fp16_kernel": ([r"cvt\.rn\.f16x2\.e2m1x2"], "O0 weight conversion: hardware E2M1 decode"),
 }
@@ -77,7 +84,7 @@ def audit(output_dir=None) -> dict:
             entries.update(_entries(ptx_path.read_text()))
     lines, ok = [], True
     for fragment, (patterns, what) in REQUIRED.items():
-        bodies = [body for name, body in entries.items() if fragment in name]
+        bodies = [body for name, body in entries.items() if re.search(fragment, name)]
         found = bool(bodies) and all(all(re.search(p, body) for p in patterns) for body in bodies)
         ok &= found
         lines.append(f"{'PASS' if found else 'FAIL'} {fragment} ({len(bodies)} entries): {what}")

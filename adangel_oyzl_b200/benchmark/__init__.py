@@ -1,3 +1,3 @@
-from .metrics import mse_fp64, percentile, summarize_samples
+from .metrics import bootstrap_median_ci, mse_fp64, percentile, summarize_samples
 
-__all__ = ["mse_fp64", "percentile", "summarize_samples"]
+__all__ = ["bootstrap_median_ci", "mse_fp64", "percentile", "summarize_samples"]

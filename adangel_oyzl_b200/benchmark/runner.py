@@ -21,7 +21,7 @@ from ..ops.extension import require_native
 from .metadata import write_environment
 from .metrics import mse_fp64, summarize_samples
 
-NOMINAL_TFLOPS = {"o0": 2250.0, "o1": 4500.0, "o2": 9000.0}  # dense FP16 / INT8 / FP4 on B200
+NOMINAL_TFLOPS = {"o0": 2250.0, "o1": 4500.0, "o1x": 4500.0, "o2": 9000.0}  # dense FP16 / INT8 / FP4 on B200
 NOMINAL_HBM_GBS = 8000.0
 
 
@@ -40,6 +40,7 @@ def _conversion_bytes(variant: str, stage: str, m: int, n: int, k: int) -> int:
         ("o0", "weight_conversion"): n * k // 2 + n * (k // 32) + 2 * n * k,
         ("o0", "activation_conversion"): m * k + 4 * m + 2 * m * k,
         ("o1", "weight_conversion"): n * k // 2 + n * k,
+        ("o1x", "weight_conversion"): 2 * (n * k // 2 + n * k) + n * (k // 32),  # both INT8 images, scales read once
         ("o2", "activation_conversion"): m * k + 4 * m + m * k // 2 + 3 * natural_sfa,
         ("o2", "weight_conversion"): 2 * natural_sfb,
     }

@@ -1,13 +1,11 @@
 """Build the native library ``libadangel_b200.so`` in-tree with nvcc for sm_100a.
 
-    python -m adangel_oyzl_b200.build [--force] [--verbose] [--define NAME ... --output PATH]
+    python -m adangel_oyzl_b200.build [--force] [--verbose]
 
 Each ``csrc/*.cu`` is compiled to an object file (in parallel) and linked into one shared library
 with a static CUDA runtime, so the library loads on machines without a GPU driver (the tensor-map
 encoder is looked up through the runtime at first use).  Objects are rebuilt only when a source or
-header is newer than the object.  ``--define`` builds an instrumented variant (for example
-``ADG_PAIR_PROF``, the stall accounting of the CTA-pair kernel) into its own object directory and
-writes it to ``--output``; ``ADANGEL_B200_LIB=<path>`` makes the package load such a variant.
+header is newer than the object; ``build/<name>.ptxas.log`` keeps ptxas' register / shared-memory report.
 """
 
 from __future__ import annotations
@@ -42,11 +40,12 @@ def _newest_header() -> float:
     return max(h.stat().st_mtime for h in headers)
 
 
-def _compile(src: Path, force: bool, verbose: bool, build_dir: Path = BUILD, defines=()) -> Path:
+def _compile(src: Path, force: bool, verbose: bool) -> Path:
+    build_dir = BUILD
     obj = build_dir / (src.stem + ".o")
     if not force and obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, _newest_header()):
         return obj
-    cmd = [_nvcc(), *ARCH_FLAGS, *COMMON, *(f"-D{d}" for d in defines), "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *ARCH_FLAGS, *COMMON, "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     log = build_dir / (src.stem + ".ptxas.log")
     log.write_text(proc.stderr)
@@ -57,32 +56,26 @@ def _compile(src: Path, force: bool, verbose: bool, build_dir: Path = BUILD, def
     return obj
 
 
-def build(force: bool = False, verbose: bool = False, defines=(), output=None) -> Path:
-    if defines and output is None:
-        raise ValueError("an instrumented build (--define) needs its own --output path")
-    build_dir = BUILD if not defines else PKG / ("build_" + "_".join(sorted(defines)))
-    lib = LIB if output is None else Path(output)
-    build_dir.mkdir(exist_ok=True)
-    lib.parent.mkdir(parents=True, exist_ok=True)
+def build(force: bool = False, verbose: bool = False) -> Path:
+    BUILD.mkdir(exist_ok=True)
+    LIB.parent.mkdir(parents=True, exist_ok=True)
     sources = sorted(CSRC.glob("*.cu"))
     with ThreadPoolExecutor(max_workers=min(len(sources), os.cpu_count() or 4)) as pool:
-        objs = list(pool.map(lambda s: _compile(s, force, verbose, build_dir, tuple(defines)), sources))
-    if force or not lib.exists() or any(o.stat().st_mtime > lib.stat().st_mtime for o in objs):
-        cmd = [_nvcc(), *ARCH_FLAGS, "-shared", "-cudart", "static", "-o", str(lib), *map(str, objs)]
+        objs = list(pool.map(lambda s: _compile(s, force, verbose), sources))
+    if force or not LIB.exists() or any(o.stat().st_mtime > LIB.stat().st_mtime for o in objs):
+        cmd = [_nvcc(), *ARCH_FLAGS, "-shared", "-cudart", "static", "-o", str(LIB), *map(str, objs)]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{proc.stderr}")
-    return lib
+    return LIB
 
 
 def main(argv=None) -> None:
     parser = argparse.ArgumentParser(description=__doc__)
     parser.add_argument("--force", action="store_true")
     parser.add_argument("--verbose", action="store_true")
-    parser.add_argument("--define", action="append", default=[], metavar="NAME", help="preprocessor symbol of an instrumented variant")
-    parser.add_argument("--output", default=None, help="library path of an instrumented variant")
     args = parser.parse_args(argv)
-    print(build(args.force, args.verbose, args.define, args.output))
+    print(build(args.force, args.verbose))
 
 
 if __name__ == "__main__":

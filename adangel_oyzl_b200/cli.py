@@ -78,6 +78,23 @@ def _analyze(args) -> None:
     print(generate_report(args.run, args.output, allow_unstable=args.allow_unstable))
 
 
+def _validate(args) -> None:
+    import json
+
+    from .synthetic import canonical_inputs
+    from .validate import validate_variant
+
+    inputs = canonical_inputs(args.m, args.n, args.k, device="cuda")
+    failed = False
+    for variant in args.variant:
+        report = validate_variant(variant, inputs, warmup=args.warmup, repeats=args.repeats,
+                                  max_compute_ms=args.max_compute_ms, max_cv_percent=args.max_cv_percent)
+        print(json.dumps(report, indent=2))
+        failed |= not report["passed"]
+    if failed:
+        raise SystemExit(1)
+
+
 def build_parser() -> argparse.ArgumentParser:
     parser = argparse.ArgumentParser(prog="adangel_oyzl_b200")
     commands = parser.add_subparsers(dest="command", required=True)
@@ -113,6 +130,18 @@ def build_parser() -> argparse.ArgumentParser:
     prepare.add_argument("--input", help="directory of a raw FP16 prefill trace (24 sample files + trace_manifest.json)")
     prepare.add_argument("--trace-config", help="trace selection YAML (with --input)")
     prepare.set_defaults(func=_prepare)
+
+    validate = commands.add_parser("validate", help="acceptance check of one or more variants: stage contract, cross-mode "
+                                               "consistency and, at 4096^3, the compute-only median / CV gate")
+    validate.add_argument("--variant", nargs="+", default=["o0", "o1", "o2"], choices=["o0", "o1", "o2", "o1x"])
+    validate.add_argument("--m", type=int, default=4096)
+    validate.add_argument("--n", type=int, default=4096)
+    validate.add_argument("--k", type=int, default=4096)
+    validate.add_argument("--warmup", type=int, default=10)
+    validate.add_argument("--repeats", type=int, default=50)
+    validate.add_argument("--max-compute-ms", type=float, default=None)
+    validate.add_argument("--max-cv-percent", type=float, default=3.0)
+    validate.set_defaults(func=_validate)
 
     analyze = commands.add_parser("analyze", help="generate the four tables of a finished run")
     analyze.add_argument("--run", required=True)

@@ -3,6 +3,7 @@
 #include <cmath>
 #include <cstring>
 #include <functional>
+#include <string>
 #include <vector>
 
 #include "../../include/adangel_b200.h"
@@ -19,6 +20,20 @@ int check_conv_dims(int64_t rows, int64_t k) {
   if (rows <= 0 || k <= 0) return fail("rows and K must be positive");
   if (k % 64 != 0) return fail("K must be divisible by 64");
   return 0;
+}
+
+// The kernels read and write these buffers with 16-byte vector accesses (4-byte for scale arrays and flag
+// words): a misaligned pointer is an error here, not a fault on the device.
+int check_ptr(const void* p, unsigned align, const char* name) {
+  if (p == nullptr) return fail(std::string(name) + " must not be NULL");
+  if ((reinterpret_cast<uintptr_t>(p) & (align - 1u)) != 0)
+    return fail(std::string(name) + " must be " + std::to_string(align) + "-byte aligned");
+  return 0;
+}
+
+int launched(int cuda_rc, const char* what) {
+  if (cuda_rc == 0) return 0;
+  return fail(std::string(what) + " launch failed: " + cudaGetErrorString(static_cast<cudaError_t>(cuda_rc)));
 }
 
 // ---- CUDA event helpers ----------------------------------------------------------------------------
@@ -78,7 +93,7 @@ struct DeviceBuffer {
 
 extern "C" {
 
-int adg_abi_version(void) { return 101; }
+int adg_abi_version(void) { return 102; }
 
 const char* adg_last_error(void) { return last_error_cstr(); }
 
@@ -102,39 +117,61 @@ int adg_device_info(char* name, int name_len, int* cc_major, int* cc_minor, int*
   return 0;
 }
 
-int adg_check_status(void* stream) { return check_device_status(as_stream(stream)); }
+int adg_check_status(void* stream) {
+  if (int rc = check_device_status(as_stream(stream))) return rc;
+  // asynchronous calls of adg_o2_linear_noalloc keep their status words in that entry point's own array
+  return noalloc_check_status(as_stream(stream), /*synchronize=*/false);
+}
+
+int adg_plan_info(int variant, int flags, int M, int N, int K, adg_plan_desc* out) {
+  if (out == nullptr) return fail("out must not be NULL");
+  PlanInfo info;
+  if (int rc = plan_info(variant, flags, M, N, K, &info)) return rc;
+  std::memset(out, 0, sizeof(*out));
+  out->tile_m = info.tile_m, out->tile_n = info.tile_n, out->stages = info.stages;
+  out->accumulator_stages = info.acc_stages, out->threads = info.threads, out->cluster = info.cluster;
+  out->mma_m = info.mma_m, out->mma_n = info.mma_n, out->mma_k = info.mma_k;
+  out->persistent = info.persistent, out->fused_activation = info.fused_activation;
+  std::strncpy(out->kernel_symbol, info.symbol, sizeof(out->kernel_symbol) - 1);
+  std::strncpy(out->mma_family, info.mma_family, sizeof(out->mma_family) - 1);
+  return 0;
+}
 
 int adg_mxfp4_to_fp16(const void* w_mxfp4, const void* w_scale, void* out_fp16, int64_t rows, int64_t K, void* stream) {
   if (int rc = check_conv_dims(rows, K)) return rc;
-  return launch_mxfp4_to_fp16(w_mxfp4, w_scale, out_fp16, rows, K, as_stream(stream)) ? fail("mxfp4_to_fp16 launch failed") : 0;
+  if (check_ptr(w_mxfp4, 16, "W_mxfp4") || check_ptr(w_scale, 1, "W_scale") || check_ptr(out_fp16, 16, "out_fp16")) return 1;
+  return launched(launch_mxfp4_to_fp16(w_mxfp4, w_scale, out_fp16, rows, K, as_stream(stream)), "mxfp4_to_fp16");
 }
 
 int adg_int8_to_fp16(const void* a_int8, const void* a_scale, void* out_fp16, int64_t rows, int64_t K, void* stream) {
   if (int rc = check_conv_dims(rows, K)) return rc;
-  return launch_int8_to_fp16(a_int8, a_scale, out_fp16, rows, K, as_stream(stream)) ? fail("int8_to_fp16 launch failed") : 0;
+  if (check_ptr(a_int8, 16, "A_int8") || check_ptr(a_scale, 4, "A_scale") || check_ptr(out_fp16, 16, "out_fp16")) return 1;
+  return launched(launch_int8_to_fp16(a_int8, a_scale, out_fp16, rows, K, as_stream(stream)), "int8_to_fp16");
 }
 
 int adg_mxfp4_to_int8(const void* w_mxfp4, void* out_int8, int64_t rows, int64_t K, void* stream) {
   if (int rc = check_conv_dims(rows, K)) return rc;
-  return launch_mxfp4_to_int8(w_mxfp4, out_int8, rows, K, as_stream(stream)) ? fail("mxfp4_to_int8 launch failed") : 0;
+  if (check_ptr(w_mxfp4, 16, "W_mxfp4") || check_ptr(out_int8, 16, "out_int8")) return 1;
+  return launched(launch_mxfp4_to_int8(w_mxfp4, out_int8, rows, K, as_stream(stream)), "mxfp4_to_int8");
 }
 
 int adg_mxfp4_to_bf16_scaled(const void* w_mxfp4, const void* w_scale, void* out_bf16, void* range_flag, int64_t rows,
                              int64_t K, void* stream) {
   if (int rc = check_conv_dims(rows, K)) return rc;
-  if (range_flag == nullptr) return fail("range_flag must not be NULL");
-  return launch_mxfp4_to_bf16_scaled(w_mxfp4, w_scale, out_bf16, range_flag, rows, K, as_stream(stream))
-             ? fail("mxfp4_to_bf16_scaled launch failed")
-             : 0;
+  if (check_ptr(w_mxfp4, 16, "W_mxfp4") || check_ptr(w_scale, 1, "W_scale") || check_ptr(out_bf16, 16, "out_bf16") ||
+      check_ptr(range_flag, 4, "range_flag"))
+    return 1;
+  return launched(launch_mxfp4_to_bf16_scaled(w_mxfp4, w_scale, out_bf16, range_flag, rows, K, as_stream(stream)),
+                  "mxfp4_to_bf16_scaled");
 }
 
 int adg_int8_to_bf16(const void* a_int8, const void* a_scale, void* out_bf16, void* range_flag, int64_t rows, int64_t K,
                      void* stream) {
   if (int rc = check_conv_dims(rows, K)) return rc;
-  if (range_flag == nullptr) return fail("range_flag must not be NULL");
-  return launch_int8_to_bf16(a_int8, a_scale, out_bf16, range_flag, rows, K, as_stream(stream))
-             ? fail("int8_to_bf16 launch failed")
-             : 0;
+  if (check_ptr(a_int8, 16, "A_int8") || check_ptr(a_scale, 4, "A_scale") || check_ptr(out_bf16, 16, "out_bf16") ||
+      check_ptr(range_flag, 4, "range_flag"))
+    return 1;
+  return launched(launch_int8_to_bf16(a_int8, a_scale, out_bf16, range_flag, rows, K, as_stream(stream)), "int8_to_bf16");
 }
 
 int64_t adg_o2_tiled_scale_bytes(int64_t rows, int64_t K) { return tiled_scale_bytes(rows, K); }
@@ -142,15 +179,17 @@ int64_t adg_o2_tiled_scale_bytes(int64_t rows, int64_t K) { return tiled_scale_b
 int adg_o2_quantize_activation(const void* a_int8, const void* a_scale, void* a_mxfp4, void* sf_natural,
                                void* sf_tiled, int64_t M, int64_t K, void* stream) {
   if (int rc = check_conv_dims(M, K)) return rc;
-  if (sf_tiled == nullptr) return fail("sf_tiled must not be NULL");
-  return launch_o2_quantize(a_int8, a_scale, a_mxfp4, sf_natural, sf_tiled, M, K, as_stream(stream))
-             ? fail("o2_quantize launch failed")
-             : 0;
+  if (check_ptr(a_int8, 16, "A_int8") || check_ptr(a_scale, 4, "A_scale") || check_ptr(a_mxfp4, 16, "A_mxfp4") ||
+      check_ptr(sf_tiled, 16, "sf_tiled"))
+    return 1;
+  if (sf_natural != nullptr && check_ptr(sf_natural, 4, "sf_natural")) return 1;
+  return launched(launch_o2_quantize(a_int8, a_scale, a_mxfp4, sf_natural, sf_tiled, M, K, as_stream(stream)), "o2_quantize");
 }
 
 int adg_o2_tile_scales(const void* sf_natural, void* sf_tiled, int64_t rows, int64_t K, void* stream) {
   if (int rc = check_conv_dims(rows, K)) return rc;
-  return launch_o2_tile_scales(sf_natural, sf_tiled, rows, K, as_stream(stream)) ? fail("o2_tile_scales launch failed") : 0;
+  if (check_ptr(sf_natural, 1, "sf_natural") || check_ptr(sf_tiled, 16, "sf_tiled")) return 1;
+  return launched(launch_o2_tile_scales(sf_natural, sf_tiled, rows, K, as_stream(stream)), "o2_tile_scales");
 }
 
 int adg_quantize_int8_per_row(const void* x, int x_dtype, void* q_int8, void* scale, int64_t rows, int64_t K,
@@ -159,9 +198,10 @@ int adg_quantize_int8_per_row(const void* x, int x_dtype, void* q_int8, void* sc
   if (K % 4 != 0) return fail("K must be divisible by 4");
   if (x_dtype != 0 && x_dtype != 1) return fail("x_dtype must be 0 (FP32) or 1 (FP16)");
   if (rows > 0x7fffffffL) return fail("too many rows");
+  if (check_ptr(x, 16, "x") || check_ptr(q_int8, 16, "q_int8") || check_ptr(scale, 4, "scale")) return 1;
   DeviceCtx* ctx = nullptr;
   if (int rc = device_ctx(&ctx)) return rc;
-  return launch_quantize_int8_rows(x, x_dtype, q_int8, scale, rows, K, as_stream(stream)) ? fail("quantize_int8_per_row launch failed") : 0;
+  return launched(launch_quantize_int8_rows(x, x_dtype, q_int8, scale, rows, K, as_stream(stream)), "quantize_int8_per_row");
 }
 
 int adg_quantize_mxfp4(const void* x, int x_dtype, void* packed, void* scale_codes, int64_t rows, int64_t K,
@@ -169,9 +209,10 @@ int adg_quantize_mxfp4(const void* x, int x_dtype, void* packed, void* scale_cod
   if (rows <= 0 || K <= 0) return fail("rows and K must be positive");
   if (K % 32 != 0) return fail("K must be divisible by 32");
   if (x_dtype != 0 && x_dtype != 1) return fail("x_dtype must be 0 (FP32) or 1 (FP16)");
+  if (check_ptr(x, 16, "x") || check_ptr(packed, 16, "packed") || check_ptr(scale_codes, 1, "scale_codes")) return 1;
   DeviceCtx* ctx = nullptr;
   if (int rc = device_ctx(&ctx)) return rc;
-  return launch_quantize_mxfp4(x, x_dtype, packed, scale_codes, rows, K, as_stream(stream)) ? fail("quantize_mxfp4 launch failed") : 0;
+  return launched(launch_quantize_mxfp4(x, x_dtype, packed, scale_codes, rows, K, as_stream(stream)), "quantize_mxfp4");
 }
 
 int adg_gemm_o0(const void* a_fp16, const void* w_fp16, float* y, int M, int N, int K, int ldy, void* stream) {
@@ -224,24 +265,71 @@ int adg_gemm_o2(const void* a_mxfp4, const void* a_sf_tiled, const void* w_mxfp4
   return run_plan(plan, as_stream(stream));
 }
 
+int64_t adg_fused_workspace_bytes(int64_t M) { return 4 * ((M + 127) / 128 + 1); }
+
+int adg_o0_linear(const void* a_int8, const void* a_scale, const void* w_fp16, void* a_fp16_workspace, void* row_counters,
+                  float* y, int M, int N, int K, int ldy, void* stream) {
+  GemmPlan plan;
+  if (M > 64 && row_counters != nullptr && fusion_enabled()) {
+    if (int rc = plan_o0_fused(&plan, a_int8, a_scale, a_fp16_workspace, w_fp16, y, row_counters, M, N, K, ldy)) return rc;
+    return run_plan(plan, as_stream(stream));
+  }
+  if (int rc = adg_int8_to_fp16(a_int8, a_scale, a_fp16_workspace, M, K, stream)) return rc;
+  if (int rc = plan_o0(&plan, a_fp16_workspace, w_fp16, y, M, N, K, ldy)) return rc;
+  return run_plan(plan, as_stream(stream));
+}
+
+int adg_o2_linear(const void* a_int8, const void* a_scale, const void* w_mxfp4, const void* w_sf_tiled, void* a_mxfp4_workspace,
+                  void* a_sf_tiled_workspace, void* a_sf_natural, void* row_counters, float* y, int M, int N, int K, int ldy,
+                  void* stream) {
+  GemmPlan plan;
+  if (M > 64 && row_counters != nullptr && fusion_enabled()) {
+    if (a_sf_natural != nullptr && check_ptr(a_sf_natural, 4, "a_sf_natural")) return 1;
+    if (int rc = plan_o2_fused(&plan, a_int8, a_scale, a_mxfp4_workspace, a_sf_tiled_workspace, a_sf_natural, w_mxfp4,
+                               w_sf_tiled, y, row_counters, M, N, K, ldy))
+      return rc;
+    return run_plan(plan, as_stream(stream));
+  }
+  if (int rc = adg_o2_quantize_activation(a_int8, a_scale, a_mxfp4_workspace, a_sf_natural, a_sf_tiled_workspace, M, K, stream))
+    return rc;
+  if (int rc = plan_o2(&plan, a_mxfp4_workspace, a_sf_tiled_workspace, w_mxfp4, w_sf_tiled, y, M, N, K, ldy)) return rc;
+  return run_plan(plan, as_stream(stream));
+}
+
 // ---- timing harness ----------------------------------------------------------------------------------
 int adg_benchmark(adg_bench_args* a) {
   if (a == nullptr) return fail("args must not be NULL");
   if (a->warmup < 0) return fail("warmup must be non-negative");
   if (a->repeats <= 0) return fail("repeats must be positive");
   if (a->conversion_inner_repeats <= 1) return fail("conversion_inner_repeats must exceed one");
-  if (a->variant < 0 || a->variant > 2) return fail("unknown variant");
+  if (a->variant < 0 || a->variant > 3) return fail("unknown variant");
   if (a->mode < 0 || a->mode > 3) return fail("unknown timing mode");
   const int M = a->M, N = a->N, K = a->K;
   if (M <= 0 || N <= 0 || K <= 0) return fail("M, N, and K must be positive");
   if (K % 64 != 0) return fail("K must be divisible by 64");
   cudaStream_t stream = as_stream(a->stream);
 
-  GemmPlan plan;
+  GemmPlan plan, fused_plan;
   Op conv_w, conv_a, gemm;
   bool has_a = true;
-  if (a->variant == 0) {
+  // O0 / O2 in the cold and steady-state modes: the activation conversion runs inside the GEMM kernel
+  const bool fused = (a->flags & ADG_BENCH_FUSE_ACTIVATION) != 0 && a->row_counters != nullptr && M > 64 &&
+                     (a->variant == 0 || a->variant == 2) && (a->mode == ADG_MODE_COLD || a->mode == ADG_MODE_STEADY_STATE);
+  if (a->variant == 3) {
+    if (a->o1x_col_factor == nullptr || a->o1x_workspace == nullptr || a->o1x_w_int8 == nullptr)
+      return fail("the o1x benchmark needs o1x_col_factor, o1x_workspace and o1x_w_int8");
+    conv_w = [&]() {
+      if (int rc = launch_mxfp4_to_int8(a->w_mxfp4, a->o1x_w_int8, N, K, stream)) return rc;
+      return adg_o1x_prepare_weight(a->w_mxfp4, a->w_scale, a->conv_weight, a->o1x_col_factor, a->o1x_workspace, N, K, stream);
+    };
+    conv_a = []() { return 0; };
+    has_a = false;
+  } else if (a->variant == 0) {
     if (int rc = plan_o0(&plan, a->conv_act, a->conv_weight, a->output, M, N, K, N)) return rc;
+    if (fused)
+      if (int rc = plan_o0_fused(&fused_plan, a->a_int8, a->a_scale, a->conv_act, a->conv_weight, a->output, a->row_counters,
+                                 M, N, K, N))
+        return rc;
     conv_w = [&]() { return launch_mxfp4_to_fp16(a->w_mxfp4, a->w_scale, a->conv_weight, N, K, stream); };
     conv_a = [&]() { return launch_int8_to_fp16(a->a_int8, a->a_scale, a->conv_act, M, K, stream); };
   } else if (a->variant == 1) {
@@ -266,6 +354,9 @@ int adg_benchmark(adg_bench_args* a) {
         return launch_mxfp4_to_bf16_scaled(a->w_mxfp4, a->w_scale, a->conv_weight_bf16, a->range_flag, N, K, stream);
       };
       conv_a = [&]() { return launch_int8_to_bf16(a->a_int8, a->a_scale, a->conv_act_bf16, a->range_flag, M, K, stream); };
+      // the reference's O1 has no activation stage (csrc/sm120/o1_gemm.cu:431-566): by default the INT8 -> BF16
+      // conversion is part of this build's GEMM stage; ADG_BENCH_O1_SPLIT_ACTIVATION reports it on its own
+      has_a = (a->flags & ADG_BENCH_O1_SPLIT_ACTIVATION) != 0;
     } else {
       if (int rc = plan_o1(&plan, a->a_int8, a->a_scale, a->conv_weight, a->w_scale, a->output, nullptr, M, N, K, N))
         return rc;
@@ -276,12 +367,32 @@ int adg_benchmark(adg_bench_args* a) {
   } else {
     if (int rc = plan_o2(&plan, a->conv_act, a->conv_act_sf_tiled, a->w_mxfp4, a->conv_weight, a->output, M, N, K, N))
       return rc;
+    if (fused)
+      if (int rc = plan_o2_fused(&fused_plan, a->a_int8, a->a_scale, a->conv_act, a->conv_act_sf_tiled, a->conv_act_sf,
+                                 a->w_mxfp4, a->conv_weight, a->output, a->row_counters, M, N, K, N))
+        return rc;
     conv_w = [&]() { return launch_o2_tile_scales(a->w_scale, a->conv_weight, N, K, stream); };
     conv_a = [&]() {
       return launch_o2_quantize(a->a_int8, a->a_scale, a->conv_act, a->conv_act_sf, a->conv_act_sf_tiled, M, K, stream);
     };
   }
-  gemm = [&]() { return run_plan(plan, stream); };
+  const bool o1_folded = a->variant == 1 && plan.o1_bf16 && !has_a && (a->mode == ADG_MODE_COLD || a->mode == ADG_MODE_STEADY_STATE);
+  if (a->variant == 3) {
+    gemm = [&]() {
+      return adg_gemm_o1x(a->a_int8, a->a_scale, a->conv_weight, a->o1x_col_factor, a->o1x_workspace, a->o1x_w_int8,
+                          a->w_scale, a->output, M, N, K, N, stream);
+    };
+  } else if (o1_folded) {
+    gemm = [&]() {
+      if (int rc = conv_a()) return rc;
+      return run_plan(plan, stream);
+    };
+  } else if (fused) {
+    gemm = [&]() { return run_plan(fused_plan, stream); };
+  } else {
+    gemm = [&]() { return run_plan(plan, stream); };
+  }
+  const bool a_in_seq = has_a && !fused;  // a fused GEMM stage contains the activation conversion
 
   // which operations run inside one directly timed iteration
   std::vector<std::pair<uint32_t, Op*>> seq;
@@ -297,12 +408,12 @@ int adg_benchmark(adg_bench_args* a) {
       break;
     case ADG_MODE_COLD:
       seq.push_back({ADG_STAGE_WEIGHT, &conv_w});
-      if (has_a) seq.push_back({ADG_STAGE_ACTIVATION, &conv_a});
+      if (a_in_seq) seq.push_back({ADG_STAGE_ACTIVATION, &conv_a});
       seq.push_back({ADG_STAGE_GEMM, &gemm});
       break;
     default:  // steady state: the weight conversion is cached
       if (conv_w()) return fail("weight conversion launch failed");
-      if (has_a) seq.push_back({ADG_STAGE_ACTIVATION, &conv_a});
+      if (a_in_seq) seq.push_back({ADG_STAGE_ACTIVATION, &conv_a});
       seq.push_back({ADG_STAGE_GEMM, &gemm});
       break;
   }

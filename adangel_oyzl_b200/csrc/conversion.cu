@@ -13,7 +13,7 @@
 //   o2_tile_scales     O2 weight-scale re-layout (reference csrc/sm120/o2_cutlass.cu:261-274)
 #include <cuda_bf16.h>
 
-#include "codecs.cuh"
+#include "convert_device.cuh"
 #include "launch.h"
 
 namespace adg {
@@ -22,247 +22,234 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
+constexpr int kChunk = kThreads * kUnroll;  // items one CTA handles per loop trip
+
+// Every kernel below is a grid-stride loop over chunks of kChunk items, launched with at most
+// kCtasPerSm resident CTAs per SM: the launch ramp and tail are paid once, and each thread keeps
+// kUnroll independent vector loads in flight per trip.  Item counts are below 2**31 (checked by the
+// launchers), so all index arithmetic is 32-bit.
+constexpr int kCtasPerSm = 8;
+constexpr int kQuantCtasPerSm = 5;  // the re-quantizer needs 48 registers per thread
 
 // ---- O0 weight: packed E2M1 + UE8M0 -> FP16 -------------------------------------------------
-// One 32-bit word (8 elements) per thread per step; `words` = rows*K/8.  The scale of word i is
-// scales[i / 4] because both tensors are contiguous and K is a multiple of 32.
-__global__ void __launch_bounds__(kThreads) mxfp4_to_fp16_kernel(const uint32_t* __restrict__ packed,
+// One 32-bit word (8 elements) per item; the scale of word i is scales[i / 4] because both tensors
+// are contiguous and K is a multiple of 32.
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) mxfp4_to_fp16_kernel(const uint32_t* __restrict__ packed,
                                                                  const uint8_t* __restrict__ scales,
-                                                                 uint4* __restrict__ out, long words) {
-  const long base = (static_cast<long>(blockIdx.x) * kUnroll) * kThreads + threadIdx.x;
-  uint32_t w[kUnroll];
-  uint32_t sc[kUnroll];
+                                                                 uint4* __restrict__ out, uint32_t words) {
+  for (uint32_t base = blockIdx.x * kChunk + threadIdx.x; base - threadIdx.x < words; base += gridDim.x * kChunk) {
+    uint32_t w[kUnroll];
+    uint32_t sc[kUnroll];
 #pragma unroll
-  for (int u = 0; u < kUnroll; ++u) {
-    const long i = base + static_cast<long>(u) * kThreads;
-    if (i < words) {
-      w[u] = __ldg(packed + i);
-      sc[u] = __ldg(scales + (i >> 2));
-    }
-  }
-#pragma unroll
-  for (int u = 0; u < kUnroll; ++u) {
-    const long i = base + static_cast<long>(u) * kThreads;
-    if (i >= words) continue;
-    const int k = static_cast<int>(sc[u]) - 127;
-    __half2 h[4];
-#pragma unroll
-    for (int b = 0; b < 4; ++b) h[b] = e2m1x2_to_half2((w[u] >> (8 * b)) & 0xFFu);
-    if (k >= -23 && k <= 13) {
-      // every product is exactly representable in FP16, so one FP16 multiply equals
-      // round_to_half(fp32 product)
-      const __half2 s2 = __half2half2(__ushort_as_half(
-          k >= -14 ? static_cast<unsigned short>((k + 15) << 10) : static_cast<unsigned short>(1u << (k + 24))));
-#pragma unroll
-      for (int b = 0; b < 4; ++b) h[b] = __hmul2(h[b], s2);
-    } else {
-      const float s = ue8m0_to_float(sc[u]);
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const float2 f = __half22float2(h[b]);
-        h[b] = __floats2half2_rn(f.x * s, f.y * s);
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * kThreads;
+      if (i < words) {
+        w[u] = __ldg(packed + i);
+        sc[u] = __ldg(scales + (i >> 2));
       }
     }
-    uint4 v;
-    v.x = *reinterpret_cast<uint32_t*>(&h[0]);
-    v.y = *reinterpret_cast<uint32_t*>(&h[1]);
-    v.z = *reinterpret_cast<uint32_t*>(&h[2]);
-    v.w = *reinterpret_cast<uint32_t*>(&h[3]);
-    out[i] = v;
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * kThreads;
+      if (i >= words) continue;
+      const int k = static_cast<int>(sc[u]) - 127;
+      __half2 h[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) h[b] = e2m1x2_to_half2((w[u] >> (8 * b)) & 0xFFu);
+      if (k >= -23 && k <= 13) {
+        // every product is exactly representable in FP16, so one FP16 multiply equals
+        // round_to_half(fp32 product)
+        const __half2 s2 = __half2half2(__ushort_as_half(
+            k >= -14 ? static_cast<unsigned short>((k + 15) << 10) : static_cast<unsigned short>(1u << (k + 24))));
+#pragma unroll
+        for (int b = 0; b < 4; ++b) h[b] = __hmul2(h[b], s2);
+      } else {
+        const float s = ue8m0_to_float(sc[u]);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const float2 f = __half22float2(h[b]);
+          h[b] = __floats2half2_rn(f.x * s, f.y * s);
+        }
+      }
+      uint4 v;
+      v.x = *reinterpret_cast<uint32_t*>(&h[0]);
+      v.y = *reinterpret_cast<uint32_t*>(&h[1]);
+      v.z = *reinterpret_cast<uint32_t*>(&h[2]);
+      v.w = *reinterpret_cast<uint32_t*>(&h[3]);
+      out[i] = v;
+    }
   }
 }
 
 // ---- O0 activation: INT8 * row scale -> FP16 --------------------------------------------------
-// Eight elements (one 64-bit load, one 128-bit store) per thread per step; `oct` = rows*K/8.
-__global__ void __launch_bounds__(kThreads) int8_to_fp16_kernel(const uint2* __restrict__ in,
+// Eight elements (one 64-bit load, one 128-bit store) per item; `octs` = rows*K/8.
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) int8_to_fp16_kernel(const uint2* __restrict__ in,
                                                                 const float* __restrict__ row_scale,
-                                                                uint4* __restrict__ out, long octs, int octs_per_row) {
-  const long base = (static_cast<long>(blockIdx.x) * kUnroll) * kThreads + threadIdx.x;
-  uint2 v[kUnroll];
-  float s[kUnroll];
+                                                                uint4* __restrict__ out, uint32_t octs,
+                                                                uint32_t octs_per_row, uint32_t magic) {
+  for (uint32_t base = blockIdx.x * kChunk + threadIdx.x; base - threadIdx.x < octs; base += gridDim.x * kChunk) {
+    uint2 v[kUnroll];
+    float s[kUnroll];
 #pragma unroll
-  for (int u = 0; u < kUnroll; ++u) {
-    const long i = base + static_cast<long>(u) * kThreads;
-    if (i < octs) {
-      v[u] = __ldg(in + i);
-      s[u] = __ldg(row_scale + i / octs_per_row);
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * kThreads;
+      if (i < octs) {
+        v[u] = __ldg(in + i);
+        s[u] = __ldg(row_scale + fast_div(i, octs_per_row, magic));
+      }
     }
-  }
 #pragma unroll
-  for (int u = 0; u < kUnroll; ++u) {
-    const long i = base + static_cast<long>(u) * kThreads;
-    if (i >= octs) continue;
-    uint32_t o[4];
-    float lo[4], hi[4];
-    int8x4_to_float4(v[u].x, lo);
-    int8x4_to_float4(v[u].y, hi);
-    const __half2 h0 = __floats2half2_rn(lo[0] * s[u], lo[1] * s[u]);
-    const __half2 h1 = __floats2half2_rn(lo[2] * s[u], lo[3] * s[u]);
-    const __half2 h2 = __floats2half2_rn(hi[0] * s[u], hi[1] * s[u]);
-    const __half2 h3 = __floats2half2_rn(hi[2] * s[u], hi[3] * s[u]);
-    o[0] = *reinterpret_cast<const uint32_t*>(&h0);
-    o[1] = *reinterpret_cast<const uint32_t*>(&h1);
-    o[2] = *reinterpret_cast<const uint32_t*>(&h2);
-    o[3] = *reinterpret_cast<const uint32_t*>(&h3);
-    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * kThreads;
+      if (i < octs) out[i] = int8x8_to_half8(v[u], s[u]);
+    }
   }
 }
 
 // ---- O1 (BF16 operands) weight: packed E2M1 + UE8M0 -> BF16 of e2m1 * 2^(scale-127) ------------
-// Exact: the value has two significant bits.  One 32-bit word (8 elements) per thread per step.
+// Exact: the value has two significant bits.  One 32-bit word (8 elements) per item.
 // A scale code outside [kO1MinScaleCode, kO1MaxScaleCode] sets bit 0 of *range_flag.
-__global__ void __launch_bounds__(kThreads) mxfp4_to_bf16_scaled_kernel(const uint32_t* __restrict__ packed,
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) mxfp4_to_bf16_scaled_kernel(const uint32_t* __restrict__ packed,
                                                                         const uint8_t* __restrict__ scales,
-                                                                        uint4* __restrict__ out, long words,
+                                                                        uint4* __restrict__ out, uint32_t words,
                                                                         uint32_t* __restrict__ range_flag) {
-  const long base = (static_cast<long>(blockIdx.x) * kUnroll) * kThreads + threadIdx.x;
   bool bad = false;
+  for (uint32_t base = blockIdx.x * kChunk + threadIdx.x; base - threadIdx.x < words; base += gridDim.x * kChunk) {
+    uint32_t w[kUnroll];
+    uint32_t sc[kUnroll];
 #pragma unroll
-  for (int u = 0; u < kUnroll; ++u) {
-    const long i = base + static_cast<long>(u) * kThreads;
-    if (i >= words) continue;
-    const uint32_t w = __ldg(packed + i);
-    const uint32_t code = __ldg(scales + (i >> 2));
-    bad |= code < kO1MinScaleCode || code > kO1MaxScaleCode;
-    const float s = __uint_as_float((code == 0u ? 1u : code) << 23);  // 2^(code-127); unused when out of range
-    uint32_t o[4];
-#pragma unroll
-    for (int b = 0; b < 4; ++b) {
-      const float2 f = __half22float2(e2m1x2_to_half2((w >> (8 * b)) & 0xFFu));
-      const __nv_bfloat162 v = __floats2bfloat162_rn(f.x * s, f.y * s);
-      o[b] = *reinterpret_cast<const uint32_t*>(&v);
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * kThreads;
+      if (i < words) {
+        w[u] = __ldg(packed + i);
+        sc[u] = __ldg(scales + (i >> 2));
+      }
     }
-    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * kThreads;
+      if (i >= words) continue;
+      const uint32_t code = sc[u];
+      bad |= code < kO1MinScaleCode || code > kO1MaxScaleCode;
+      const float s = __uint_as_float((code == 0u ? 1u : code) << 23);  // 2^(code-127); unused when out of range
+      uint32_t o[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const float2 f = __half22float2(e2m1x2_to_half2((w[u] >> (8 * b)) & 0xFFu));
+        const __nv_bfloat162 v = __floats2bfloat162_rn(f.x * s, f.y * s);
+        o[b] = *reinterpret_cast<const uint32_t*>(&v);
+      }
+      out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
   }
   if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(range_flag, 1u);
 }
 
 // ---- O1 (BF16 operands) activation: INT8 -> BF16 of the integer itself, exact ------------------
-// Eight elements per thread per step.  The first `rows` threads of the grid also check the row
-// scales: one outside [2^kO1MinAScaleExp, 2^kO1MaxAScaleExp] (or not finite) sets bit 1 of *range_flag.
-__global__ void __launch_bounds__(kThreads) int8_to_bf16_kernel(const uint2* __restrict__ in,
+// Eight elements per item.  The grid's threads also check the row scales (grid-stride): one outside
+// [2^kO1MinAScaleExp, 2^kO1MaxAScaleExp] (or not finite) sets bit 1 of *range_flag.
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) int8_to_bf16_kernel(const uint2* __restrict__ in,
                                                                 const float* __restrict__ row_scale,
-                                                                uint4* __restrict__ out, long octs, long rows,
+                                                                uint4* __restrict__ out, uint32_t octs, uint32_t rows,
                                                                 uint32_t* __restrict__ range_flag) {
-  const long base = (static_cast<long>(blockIdx.x) * kUnroll) * kThreads + threadIdx.x;
-  uint2 v[kUnroll];
-#pragma unroll
-  for (int u = 0; u < kUnroll; ++u) {
-    const long i = base + static_cast<long>(u) * kThreads;
-    if (i < octs) v[u] = __ldg(in + i);
-  }
   bool bad = false;
-  const long gid = static_cast<long>(blockIdx.x) * kThreads + threadIdx.x;
-  if (gid < rows) {
-    const float s = __ldg(row_scale + gid);
-    bad = !(s >= exp2f(static_cast<float>(kO1MinAScaleExp)) && s <= exp2f(static_cast<float>(kO1MaxAScaleExp)));
+  for (uint32_t r = blockIdx.x * kThreads + threadIdx.x; r < rows; r += gridDim.x * kThreads) {
+    const float s = __ldg(row_scale + r);
+    bad |= !(s >= exp2f(static_cast<float>(kO1MinAScaleExp)) && s <= exp2f(static_cast<float>(kO1MaxAScaleExp)));
   }
+  for (uint32_t base = blockIdx.x * kChunk + threadIdx.x; base - threadIdx.x < octs; base += gridDim.x * kChunk) {
+    uint2 v[kUnroll];
 #pragma unroll
-  for (int u = 0; u < kUnroll; ++u) {
-    const long i = base + static_cast<long>(u) * kThreads;
-    if (i >= octs) continue;
-    float lo[4], hi[4];
-    int8x4_to_float4(v[u].x, lo);
-    int8x4_to_float4(v[u].y, hi);
-    const __nv_bfloat162 b0 = __floats2bfloat162_rn(lo[0], lo[1]);
-    const __nv_bfloat162 b1 = __floats2bfloat162_rn(lo[2], lo[3]);
-    const __nv_bfloat162 b2 = __floats2bfloat162_rn(hi[0], hi[1]);
-    const __nv_bfloat162 b3 = __floats2bfloat162_rn(hi[2], hi[3]);
-    out[i] = make_uint4(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1),
-                        *reinterpret_cast<const uint32_t*>(&b2), *reinterpret_cast<const uint32_t*>(&b3));
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * kThreads;
+      if (i < octs) v[u] = __ldg(in + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * kThreads;
+      if (i >= octs) continue;
+      float lo[4], hi[4];
+      int8x4_to_float4(v[u].x, lo);
+      int8x4_to_float4(v[u].y, hi);
+      const __nv_bfloat162 b0 = __floats2bfloat162_rn(lo[0], lo[1]);
+      const __nv_bfloat162 b1 = __floats2bfloat162_rn(lo[2], lo[3]);
+      const __nv_bfloat162 b2 = __floats2bfloat162_rn(hi[0], hi[1]);
+      const __nv_bfloat162 b3 = __floats2bfloat162_rn(hi[2], hi[3]);
+      out[i] = make_uint4(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1),
+                          *reinterpret_cast<const uint32_t*>(&b2), *reinterpret_cast<const uint32_t*>(&b3));
+    }
   }
   if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(range_flag, 2u);
 }
 
 // ---- O1 weight: packed E2M1 -> INT8 (2*E2M1) ---------------------------------------------------
-// Sixteen elements (64-bit load, 128-bit store) per thread per step; `pairs` = rows*K/16.
-__global__ void __launch_bounds__(kThreads) mxfp4_to_int8_kernel(const uint2* __restrict__ packed,
-                                                                 uint4* __restrict__ out, long pairs) {
-  const long base = (static_cast<long>(blockIdx.x) * kUnroll) * kThreads + threadIdx.x;
-  uint2 v[kUnroll];
+// Sixteen elements (64-bit load, 128-bit store) per item; `pairs` = rows*K/16.
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) mxfp4_to_int8_kernel(const uint2* __restrict__ packed,
+                                                                 uint4* __restrict__ out, uint32_t pairs) {
+  for (uint32_t base = blockIdx.x * kChunk + threadIdx.x; base - threadIdx.x < pairs; base += gridDim.x * kChunk) {
+    uint2 v[kUnroll];
 #pragma unroll
-  for (int u = 0; u < kUnroll; ++u) {
-    const long i = base + static_cast<long>(u) * kThreads;
-    if (i < pairs) v[u] = __ldg(packed + i);
-  }
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * kThreads;
+      if (i < pairs) v[u] = __ldg(packed + i);
+    }
 #pragma unroll
-  for (int u = 0; u < kUnroll; ++u) {
-    const long i = base + static_cast<long>(u) * kThreads;
-    if (i >= pairs) continue;
-    uint4 o;
-    e2m1x8_to_int8x8(v[u].x, o.x, o.y);
-    e2m1x8_to_int8x8(v[u].y, o.z, o.w);
-    out[i] = o;
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * kThreads;
+      if (i >= pairs) continue;
+      uint4 o;
+      e2m1x8_to_int8x8(v[u].x, o.x, o.y);
+      e2m1x8_to_int8x8(v[u].y, o.z, o.w);
+      out[i] = o;
+    }
   }
 }
 
 // ---- O2 activation: INT8 * row scale -> MXFP4 codes + UE8M0 scales -------------------------------
-// One K32 block per thread: 32 bytes in, 16 bytes of packed codes out, one scale byte written to
-// the natural [M, K/32] array (optional) and to the 512-byte-atom layout the tensor core reads.
-__device__ __forceinline__ long tiled_sf_offset(int row, int g, int katoms) {
-  return (static_cast<long>(row >> 7) * katoms + (g >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (g & 3);
-}
-
-__global__ void __launch_bounds__(kThreads) o2_quantize_kernel(const uint4* __restrict__ in,
+// Half a K32 block per item: 16 bytes in (a warp's load covers 512 contiguous bytes), 8 bytes of packed
+// codes out; lane pairs share a block (one shuffle for its maximum), and the eight lanes that hold four
+// consecutive blocks of a row gather their scale bytes into one 32-bit word of the natural [M, K/32]
+// array (optional) and of the 512-byte-atom layout the tensor core reads.  `halves` = rows*K/16,
+// `halves_per_row` = K/16 (a multiple of 4, so a block never straddles two warps or two rows).
+__global__ void __launch_bounds__(kThreads, kQuantCtasPerSm) o2_quantize_kernel(const uint4* __restrict__ in,
                                                                const float* __restrict__ row_scale,
-                                                               uint4* __restrict__ codes, uint8_t* __restrict__ sf_natural,
-                                                               uint8_t* __restrict__ sf_tiled, long blocks, int groups,
-                                                               int katoms) {
-  const long gid = static_cast<long>(blockIdx.x) * kThreads + threadIdx.x;
-  const bool valid = gid < blocks;
-  const long g_safe = valid ? gid : 0;
-  const int row = static_cast<int>(g_safe / groups);
-  const int g = static_cast<int>(g_safe - static_cast<long>(row) * groups);
-  const uint4 lo = __ldg(in + 2 * g_safe);
-  const uint4 hi = __ldg(in + 2 * g_safe + 1);
-  const float s = __ldg(row_scale + row);
-  const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-  float v[32];
-  float amax = 0.0f;
+                                                               uint2* __restrict__ codes, uint8_t* __restrict__ sf_natural,
+                                                               uint8_t* __restrict__ sf_tiled, uint32_t halves,
+                                                               uint32_t halves_per_row, uint32_t magic, int katoms) {
+  const bool words_ok = (halves_per_row & 7u) == 0;  // K/32 a multiple of 4: whole scale words per row
+  for (uint32_t base = blockIdx.x * kChunk + threadIdx.x; base - threadIdx.x < halves; base += gridDim.x * kChunk) {
+    uint4 v[kUnroll];
+    float s[kUnroll];
+    uint32_t row[kUnroll];
 #pragma unroll
-  for (int wi = 0; wi < 8; ++wi) {
-    float f[4];
-    int8x4_to_float4(words[wi], f);
-#pragma unroll
-    for (int b = 0; b < 4; ++b) {
-      v[wi * 4 + b] = f[b] * s;
-      amax = fmaxf(amax, fabsf(v[wi * 4 + b]));
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * kThreads;
+      const uint32_t i_safe = i < halves ? i : 0u;
+      row[u] = fast_div(i_safe, halves_per_row, magic);
+      v[u] = __ldg(in + i_safe);
+      s[u] = __ldg(row_scale + row[u]);
     }
-  }
-  // exact floor(log2(amax)) - 2, clamped; an all-zero block uses exponent 0
-  int e = 0;
-  if (amax != 0.0f) {
-    e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xFFu) - 127 - 2;
-    e = e < -127 ? -127 : (e > 127 ? 127 : e);
-  }
-  const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);  // 2**-e, exact
-  uint32_t o[4];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    uint32_t word = 0;
-#pragma unroll
-    for (int b = 0; b < 4; ++b) {
-      const int i = q * 8 + b * 2;
-      // the fused add of +0 turns a product of -0 into +0, which must encode as code 0
-      const float x0 = __fmaf_rn(v[i], inv, 0.0f);
-      const float x1 = __fmaf_rn(v[i + 1], inv, 0.0f);
-      word |= float2_to_e2m1x2(x0, x1) << (8 * b);
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * kThreads;
+      const bool valid = i < halves;
+      uint32_t code;
+      const uint2 c = o2_quantize_half_block(v[u], s[u], code);  // all lanes: shuffles inside
+      if (valid) codes[i] = c;
+      const int g = static_cast<int>((valid ? i : 0u) - row[u] * halves_per_row) >> 1;
+      if (words_ok) {
+        // lanes 0,2,4,6 of each group of eight hold the four blocks of one scale word
+        uint32_t word = code | (__shfl_down_sync(0xffffffffu, code, 2) << 8);
+        word |= __shfl_down_sync(0xffffffffu, word, 4) << 16;
+        if (valid && (threadIdx.x & 7) == 0) {
+          if (sf_natural != nullptr) *reinterpret_cast<uint32_t*>(sf_natural + (i >> 1)) = word;
+          *reinterpret_cast<uint32_t*>(sf_tiled + tiled_sf_offset(static_cast<int>(row[u]), g, katoms)) = word;
+        }
+      } else if (valid && (threadIdx.x & 1) == 0) {
+        if (sf_natural != nullptr) sf_natural[i >> 1] = static_cast<uint8_t>(code);
+        sf_tiled[tiled_sf_offset(static_cast<int>(row[u]), g, katoms)] = static_cast<uint8_t>(code);
+      }
     }
-    o[q] = word;
-  }
-  if (valid) codes[gid] = make_uint4(o[0], o[1], o[2], o[3]);
-  const uint32_t code = static_cast<uint32_t>(e + 127);
-  if ((groups & 3) == 0) {
-    // four consecutive lanes hold the four blocks of one tiled-layout word: gather and store once
-    uint32_t packed = code | (__shfl_down_sync(0xffffffffu, code, 1) << 8);
-    packed |= __shfl_down_sync(0xffffffffu, packed, 2) << 16;
-    if (valid && (threadIdx.x & 3) == 0) {
-      if (sf_natural != nullptr) *reinterpret_cast<uint32_t*>(sf_natural + gid) = packed;
-      *reinterpret_cast<uint32_t*>(sf_tiled + tiled_sf_offset(row, g, katoms)) = packed;
-    }
-  } else if (valid) {
-    if (sf_natural != nullptr) sf_natural[gid] = static_cast<uint8_t>(code);
-    sf_tiled[tiled_sf_offset(row, g, katoms)] = static_cast<uint8_t>(code);
   }
 }
 
@@ -286,26 +273,48 @@ __global__ void __launch_bounds__(kThreads) o2_tile_scales_kernel(const uint8_t*
   tiled[tiled_sf_offset(row, ka * 4, katoms) >> 2] = word;
 }
 
+// Grid of a grid-stride kernel: enough CTAs for the items, at most kCtasPerSm per SM.
+unsigned persistent_grid(long items, int per_block, int ctas_per_sm = kCtasPerSm) {
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      sm_count = n;
+    else
+      return static_cast<unsigned>((items + per_block - 1) / per_block);
+  }
+  const long need = (items + per_block - 1) / per_block;
+  const long cap = static_cast<long>(sm_count) * ctas_per_sm;
+  return static_cast<unsigned>(need < cap ? need : cap);
+}
+
 inline unsigned grid_for(long items, int per_block) {
   return static_cast<unsigned>((items + per_block - 1) / per_block);
 }
+
+constexpr long kMaxItems = 0x7fffffffL - 2 * kChunk;
+int too_large() { return static_cast<int>(cudaErrorInvalidValue); }
 
 }  // namespace
 
 int launch_mxfp4_to_fp16(const void* packed, const void* scales, void* out, long rows, long k, cudaStream_t stream) {
   const long words = rows * k / 8;
   if (words == 0) return 0;
-  mxfp4_to_fp16_kernel<<<grid_for(words, kThreads * kUnroll), kThreads, 0, stream>>>(
-      static_cast<const uint32_t*>(packed), static_cast<const uint8_t*>(scales), static_cast<uint4*>(out), words);
+  if (words > kMaxItems) return too_large();
+  mxfp4_to_fp16_kernel<<<persistent_grid(words, kChunk), kThreads, 0, stream>>>(
+      static_cast<const uint32_t*>(packed), static_cast<const uint8_t*>(scales), static_cast<uint4*>(out),
+      static_cast<uint32_t>(words));
   return static_cast<int>(cudaGetLastError());
 }
 
 int launch_int8_to_fp16(const void* in, const void* row_scale, void* out, long rows, long k, cudaStream_t stream) {
   const long octs = rows * k / 8;
   if (octs == 0) return 0;
-  int8_to_fp16_kernel<<<grid_for(octs, kThreads * kUnroll), kThreads, 0, stream>>>(
-      static_cast<const uint2*>(in), static_cast<const float*>(row_scale), static_cast<uint4*>(out), octs,
-      static_cast<int>(k / 8));
+  if (octs > kMaxItems) return too_large();
+  const uint32_t per_row = static_cast<uint32_t>(k / 8);
+  int8_to_fp16_kernel<<<persistent_grid(octs, kChunk), kThreads, 0, stream>>>(
+      static_cast<const uint2*>(in), static_cast<const float*>(row_scale), static_cast<uint4*>(out),
+      static_cast<uint32_t>(octs), per_row, fast_div_magic(per_row));
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -313,9 +322,10 @@ int launch_mxfp4_to_bf16_scaled(const void* packed, const void* scales, void* ou
                                 cudaStream_t stream) {
   const long words = rows * k / 8;
   if (words == 0) return 0;
-  mxfp4_to_bf16_scaled_kernel<<<grid_for(words, kThreads * kUnroll), kThreads, 0, stream>>>(
-      static_cast<const uint32_t*>(packed), static_cast<const uint8_t*>(scales), static_cast<uint4*>(out), words,
-      static_cast<uint32_t*>(range_flag));
+  if (words > kMaxItems) return too_large();
+  mxfp4_to_bf16_scaled_kernel<<<persistent_grid(words, kChunk), kThreads, 0, stream>>>(
+      static_cast<const uint32_t*>(packed), static_cast<const uint8_t*>(scales), static_cast<uint4*>(out),
+      static_cast<uint32_t>(words), static_cast<uint32_t*>(range_flag));
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -323,29 +333,32 @@ int launch_int8_to_bf16(const void* in, const void* row_scale, void* out, void* 
                         cudaStream_t stream) {
   const long octs = rows * k / 8;
   if (octs == 0) return 0;
-  // K >= 32, so the grid has at least `rows` threads for the row-scale check
-  int8_to_bf16_kernel<<<grid_for(octs, kThreads * kUnroll), kThreads, 0, stream>>>(
-      static_cast<const uint2*>(in), static_cast<const float*>(row_scale), static_cast<uint4*>(out), octs, rows,
-      static_cast<uint32_t*>(range_flag));
+  if (octs > kMaxItems) return too_large();
+  int8_to_bf16_kernel<<<persistent_grid(octs, kChunk), kThreads, 0, stream>>>(
+      static_cast<const uint2*>(in), static_cast<const float*>(row_scale), static_cast<uint4*>(out),
+      static_cast<uint32_t>(octs), static_cast<uint32_t>(rows), static_cast<uint32_t*>(range_flag));
   return static_cast<int>(cudaGetLastError());
 }
 
 int launch_mxfp4_to_int8(const void* packed, void* out, long rows, long k, cudaStream_t stream) {
   const long pairs = rows * k / 16;
   if (pairs == 0) return 0;
-  mxfp4_to_int8_kernel<<<grid_for(pairs, kThreads * kUnroll), kThreads, 0, stream>>>(
-      static_cast<const uint2*>(packed), static_cast<uint4*>(out), pairs);
+  if (pairs > kMaxItems) return too_large();
+  mxfp4_to_int8_kernel<<<persistent_grid(pairs, kChunk), kThreads, 0, stream>>>(
+      static_cast<const uint2*>(packed), static_cast<uint4*>(out), static_cast<uint32_t>(pairs));
   return static_cast<int>(cudaGetLastError());
 }
 
 int launch_o2_quantize(const void* a_int8, const void* row_scale, void* codes, void* sf_natural, void* sf_tiled,
                        long rows, long k, cudaStream_t stream) {
-  const long blocks = rows * (k / 32);
-  if (blocks == 0) return 0;
-  o2_quantize_kernel<<<grid_for(blocks, kThreads), kThreads, 0, stream>>>(
-      static_cast<const uint4*>(a_int8), static_cast<const float*>(row_scale), static_cast<uint4*>(codes),
-      static_cast<uint8_t*>(sf_natural), static_cast<uint8_t*>(sf_tiled), blocks, static_cast<int>(k / 32),
-      static_cast<int>(tiled_scale_katoms(k)));
+  const long halves = rows * (k / 16);
+  if (halves == 0) return 0;
+  if (halves > kMaxItems) return too_large();
+  const uint32_t per_row = static_cast<uint32_t>(k / 16);
+  o2_quantize_kernel<<<persistent_grid(halves, kChunk, kQuantCtasPerSm), kThreads, 0, stream>>>(
+      static_cast<const uint4*>(a_int8), static_cast<const float*>(row_scale), static_cast<uint2*>(codes),
+      static_cast<uint8_t*>(sf_natural), static_cast<uint8_t*>(sf_tiled), static_cast<uint32_t>(halves), per_row,
+      fast_div_magic(per_row), static_cast<int>(tiled_scale_katoms(k)));
   return static_cast<int>(cudaGetLastError());
 }
 

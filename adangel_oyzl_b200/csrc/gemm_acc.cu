@@ -5,20 +5,31 @@
 //
 //   Y[M,N] (f32) = A[M,K] . W[N,K]^T        both operands K-major, W is used as stored
 //
+// A third kind, kind::i8 with INT32 accumulation over the whole K extent and one scaling at the end, serves
+// the exact-integer O1 variant ("o1x": W pre-shifted per row so that one factor per output column remains).
+//
 // One CTA per SM walks output tiles of 128 x BLOCK_N.  Roles:
 //   warp 0      TMA producer: A/W tiles (128-byte-wide K slabs, 128-byte swizzle) and, for O2, the
 //               scale-factor atoms, into a multi-stage shared-memory ring guarded by mbarriers
-//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (and, for O2, the shared ->
-//               tensor-memory scale-factor copies) and commits completion to the mbarriers
-//   warp 10     (O2) one lane copies each stage's scale-factor atoms from shared to tensor memory
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma and commits completion to the
+//               mbarriers
+//   warp 2      (O2) one lane copies each stage's scale-factor atoms from shared to tensor memory
 //               (tcgen05.cp) and commits to a per-stage mbarrier, so that the MMA lane, whose
 //               instruction issue is the scarce resource, issues nothing but MMAs
-//   warps 2-9   epilogue: two warps per 32-lane quarter of tensor memory, each draining half of the
+//   warps 4-11  epilogue: two warps per 32-lane quarter of tensor memory, each draining half of the
 //               accumulator's columns into registers in one go (so the accumulator is released
 //               after a few hundred cycles), then writing 32x16 blocks through swizzled
 //               shared-memory staging with TMA stores while the next tile's MMAs already run
+//   warps 12-15 (FUSED kernels only) activation converters: they turn A_int8 into the operand the MMAs
+//               read (FP16 for O0, MXFP4 codes + tiled scales for O2) row by row while the tensor cores
+//               work, and publish per-row-block counters that the TMA producer waits on before it loads
+//               a row block's tiles -- the conversion that the reference runs as a kernel of its own in
+//               front of every GEMM (csrc/sm120/o0_gemm.cu:351-531, o2_cutlass.cu:207-259 then :451-472)
+//               leaves the critical path.  Registers are re-balanced between the warp groups
+//               (setmaxnreg) so that the 512-thread CTA keeps the epilogue's 128-register drain.
 // All waits are bounded (see common.cuh); on a timeout the kernel records an error and returns.
 #include "common.cuh"
+#include "convert_device.cuh"
 #include "launch.h"
 
 namespace adg {
@@ -27,8 +38,16 @@ namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kEpiWarps = 8;
-constexpr int kSfWarp = 2 + kEpiWarps;  // copies scale factors into tensor memory (O2 only)
-constexpr int kAccThreads = (2 + kEpiWarps + 2) * 32;
+constexpr int kSfWarp = 2;        // copies scale factors into tensor memory (O2 only)
+constexpr int kFirstEpiWarp = 4;  // the epilogue is warp groups 1 and 2
+constexpr int kFirstConvWarp = kFirstEpiWarp + kEpiWarps;  // warp group 3 (FUSED kernels)
+constexpr int kAccThreads = kFirstConvWarp * 32;
+constexpr int kFusedThreads = kAccThreads + kConvThreads;
+// Register budget of a FUSED CTA (512 threads, 128 registers each at launch = the whole file): the
+// one-thread roles give back 64, the converters 16, and the two epilogue warp groups take 40 each.
+constexpr int kFusedRegsRoles = 64, kFusedRegsConv = 112, kFusedRegsEpi = 168;
+static_assert(128 * (kFusedRegsRoles + kFusedRegsConv + 2 * kFusedRegsEpi) == 65536, "register budget");
+constexpr int kConvBarrier = 1;  // named barrier of the converter warp group
 constexpr int kStagingPerWarp = 2048;  // one 32-row x 16-column FP32 block
 constexpr int kGroupM = 8;  // tile rasterisation: sweep 8 row-blocks before moving to the next column-block
 
@@ -38,7 +57,31 @@ enum : uint32_t {  // wait tags reported on timeout
   kTagTmemEmpty = 0x300,
   kTagTmemFull = 0x400,
   kTagSfFull = 0x500,
+  kTagRowsReady = 0x600,
 };
+
+// Bounded wait until `*counter` has reached `need` (rows of a row block converted by the converter
+// warps of all CTAs).  Returns false when the CTA is aborting.
+__device__ __forceinline__ bool wait_rows_ready(const uint32_t* counter, uint32_t need, const WaitEnv& env, uint32_t tag) {
+  if (ld_acquire_gpu(counter) >= need) return true;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (ld_acquire_gpu(counter) < need) {
+    if ((++spins & 0xFFu) == 0) {
+      if (*env.abort) return false;
+      if (global_timer_ns() - t0 > kWaitTimeoutNs) {
+        *env.abort = 1;
+        if (atomicCAS(env.status, 0u, static_cast<uint32_t>(kStatusWaitTimeout)) == 0u) {
+          env.status[1] = tag;
+          env.status[2] = blockIdx.x;
+          env.status[3] = need;
+        }
+        return false;
+      }
+    }
+  }
+  return true;
+}
 
 template <int KIND, int BLOCK_N>
 struct AccCfg {
@@ -77,12 +120,13 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) 
   return t;
 }
 
-template <int KIND, int BLOCK_N>
-__global__ void __launch_bounds__(kAccThreads, 1)
+template <int KIND, int BLOCK_N, bool FUSED>
+__global__ void __launch_bounds__(FUSED ? kFusedThreads : kAccThreads, 1)
 gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const __grid_constant__ CUtensorMap tm_y, const uint8_t* __restrict__ sfa,
                 const uint8_t* __restrict__ sfb, float* __restrict__ y, int M, int N, int K, int ldy,
-                int use_tma_store, uint32_t* status) {
+                int use_tma_store, uint32_t* status, const FusedConvert conv, const float* __restrict__ row_factor,
+                const float* __restrict__ col_factor) {
   using Cfg = AccCfg<KIND, BLOCK_N>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -133,6 +177,11 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
+  // Warp group 0: the one-thread roles.  (FUSED: each warp group starts its branch with the register
+  // re-balancing, all four warps of the group at the same instruction.)
+  if (warp < kFirstEpiWarp) {
+    if constexpr (FUSED) reg_dealloc<kFusedRegsRoles>();
+  }
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------------------
     if (lane == 0) {
@@ -141,6 +190,13 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         const TileCoord tc = tile_coord(tile, num_m, num_n);
+        if constexpr (FUSED) {
+          // the row block's operand is being written by the converter warps of all CTAs
+          const uint32_t need = static_cast<uint32_t>(min(kBlockM, M - tc.m_blk * kBlockM));
+          ok = wait_rows_ready(conv.ready + tc.m_blk, need, env, kTagRowsReady);
+          if (!ok) break;
+          fence_proxy_async_all();
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage);
           if (!ok) break;
@@ -260,12 +316,13 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         }
       }
     }
-  } else if (warp >= 2 && warp < 2 + kEpiWarps) {
+  } else if (warp >= kFirstEpiWarp && warp < kFirstConvWarp) {
+    if constexpr (FUSED) reg_alloc<kFusedRegsEpi>();
     // ------------------------------- epilogue ---------------------------------------------------
-    const int q = warp & 3;         // the 32-lane quarter of tensor memory this warp can read
-    const int h = (warp - 2) >> 2;  // which half of the accumulator's columns this warp drains
+    const int q = warp & 3;                     // the 32-lane quarter of tensor memory this warp can read
+    const int h = (warp - kFirstEpiWarp) >> 2;  // which half of the accumulator's columns this warp drains
     constexpr int CW = Cfg::kColsPerWarp;
-    uint8_t* buf = staging + (warp - 2) * kStagingPerWarp;
+    uint8_t* buf = staging + (warp - kFirstEpiWarp) * kStagingPerWarp;
     const uint32_t buf_row = smem_u32(buf) + lane * 64;
     const uint32_t swz = static_cast<uint32_t>((lane >> 1) & 3);
     const uint64_t store_policy = l2_policy_evict_first();
@@ -290,6 +347,19 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+      if constexpr (KIND == 1) {
+        // exact-integer O1: y = RN(float(S) * RN(A_scale[m] * c[n])), S the INT32 sum over all of K
+        const float a_m = row0 + lane < M ? __ldg(row_factor + row0 + lane) : 0.0f;
+#pragma unroll
+        for (int i = 0; i < CW / 32; ++i) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = col0 + i * 32 + j;
+            const float c_n = col < N ? __ldg(col_factor + col) : 0.0f;
+            r[i][j] = __float_as_uint(__fmul_rn(__int2float_rn(static_cast<int>(r[i][j])), __fmul_rn(a_m, c_n)));
+          }
+        }
+      }
       if (use_tma_store) {
 #pragma unroll
         for (int c = 0; c < CW / 16; ++c) {
@@ -325,45 +395,124 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       }
     }
     if (lane == 0) bulk_wait_group<0>();
+  } else if (warp >= kFirstConvWarp) {
+    // ------------------------------- activation converters (FUSED) ------------------------------
+    if constexpr (FUSED) {
+      reg_dealloc<kFusedRegsConv>();
+      convert_rows_role<KIND>(conv, M, K, static_cast<int>(threadIdx.x) - kAccThreads, blockIdx.x, gridDim.x, kConvBarrier);
+    }
   }
 
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  if constexpr (FUSED) {
+    // the last CTA to get here puts the counters back to zero for the next launch: by then every CTA
+    // has finished waiting on them
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(conv.ready + num_m, 1u) == gridDim.x - 1) {
+        for (int i = 0; i <= num_m; ++i) conv.ready[i] = 0u;
+        __threadfence();
+      }
+    }
+  }
 }
 
-template <int KIND, int BLOCK_N>
+template <int KIND, int BLOCK_N, bool FUSED>
 int set_attr() {
   using Cfg = AccCfg<KIND, BLOCK_N>;
-  return check_cuda(cudaFuncSetAttribute(gemm_acc_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  return check_cuda(cudaFuncSetAttribute(gemm_acc_kernel<KIND, BLOCK_N, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes),
                     "cudaFuncSetAttribute(gemm_acc_kernel)");
 }
 
-template <int KIND, int BLOCK_N>
+template <int KIND, int BLOCK_N, bool FUSED>
 int launch(const GemmPlan& p, cudaStream_t stream) {
   using Cfg = AccCfg<KIND, BLOCK_N>;
-  gemm_acc_kernel<KIND, BLOCK_N><<<p.grid, kAccThreads, Cfg::kSmemBytes, stream>>>(
+  FusedConvert conv{};
+  if constexpr (FUSED) {
+    conv.a_int8 = static_cast<const uint4*>(p.fused_a_int8);
+    conv.a_scale = static_cast<const float*>(p.a_scale);
+    conv.a_out = p.fused_a_out;
+    conv.sf_natural = static_cast<uint8_t*>(p.fused_sf_natural);
+    conv.sf_tiled = static_cast<uint8_t*>(const_cast<void*>(p.sfa));
+    conv.ready = p.fused_ready;
+  }
+  gemm_acc_kernel<KIND, BLOCK_N, FUSED><<<p.grid, FUSED ? kFusedThreads : kAccThreads, Cfg::kSmemBytes, stream>>>(
       p.tm_a, p.tm_b, p.tm_y, static_cast<const uint8_t*>(p.sfa), static_cast<const uint8_t*>(p.sfb), p.y, p.M, p.N,
-      p.K, p.ldy, p.use_tma_store, p.status);
+      p.K, p.ldy, p.use_tma_store, p.status, conv, static_cast<const float*>(p.a_scale),
+      static_cast<const float*>(p.col_factor));
   return check_cuda(cudaGetLastError(), "gemm_acc_kernel launch");
+}
+
+template <int KIND, bool FUSED>
+int launch_n(const GemmPlan& p, cudaStream_t stream) {
+  return p.block_n == 256 ? launch<KIND, 256, FUSED>(p, stream) : launch<KIND, 128, FUSED>(p, stream);
 }
 
 }  // namespace
 
 int init_gemm_acc_attributes() {
-  if (int rc = set_attr<0, 256>()) return rc;
-  if (int rc = set_attr<0, 128>()) return rc;
-  if (int rc = set_attr<2, 256>()) return rc;
-  if (int rc = set_attr<2, 128>()) return rc;
+  if (int rc = set_attr<0, 256, false>()) return rc;
+  if (int rc = set_attr<0, 128, false>()) return rc;
+  if (int rc = set_attr<1, 256, false>()) return rc;
+  if (int rc = set_attr<1, 128, false>()) return rc;
+  if (int rc = set_attr<2, 256, false>()) return rc;
+  if (int rc = set_attr<2, 128, false>()) return rc;
+  if (int rc = set_attr<0, 256, true>()) return rc;
+  if (int rc = set_attr<0, 128, true>()) return rc;
+  if (int rc = set_attr<2, 256, true>()) return rc;
+  if (int rc = set_attr<2, 128, true>()) return rc;
   return 0;
 }
 
 int run_gemm_acc(const GemmPlan& p, cudaStream_t stream) {
-  if (p.variant == 0) return p.block_n == 256 ? launch<0, 256>(p, stream) : launch<0, 128>(p, stream);
-  if (p.variant == 2) return p.block_n == 256 ? launch<2, 256>(p, stream) : launch<2, 128>(p, stream);
-  return fail("run_gemm_acc: plan is not an O0/O2 plan");
+  if (p.fused) {
+    if (p.fused_ready == nullptr || p.fused_a_int8 == nullptr || p.fused_a_out == nullptr)
+      return fail("run_gemm_acc: a fused plan needs A_int8, the operand buffer and the row counters");
+    if (p.variant == 0) return launch_n<0, true>(p, stream);
+    if (p.variant == 2) return launch_n<2, true>(p, stream);
+    return fail("run_gemm_acc: only O0 and O2 convert their activations inside the GEMM");
+  }
+  if (p.variant == 0) return launch_n<0, false>(p, stream);
+  if (p.variant == 2) return launch_n<2, false>(p, stream);
+  if (p.variant == 3) {
+    if (p.a_scale == nullptr || p.col_factor == nullptr) return fail("run_gemm_acc: the o1x plan lacks its factors");
+    return launch_n<1, false>(p, stream);
+  }
+  return fail("run_gemm_acc: plan is not an O0/O2/o1x plan");
+}
+
+void describe_gemm_acc(int variant, int block_n, bool fused, PlanInfo* info) {
+  info->tile_m = kBlockM;
+  info->tile_n = block_n;
+  info->threads = fused ? kFusedThreads : kAccThreads;
+  info->cluster = 1;
+  info->persistent = 1;
+  info->fused_activation = fused ? 1 : 0;
+  info->mma_m = kBlockM;
+  info->mma_n = block_n;
+  if (variant == 0) {
+    info->stages = block_n == 256 ? AccCfg<0, 256>::kStages : AccCfg<0, 128>::kStages;
+    info->acc_stages = 2;
+    info->mma_k = 16;
+    info->symbol = fused ? "gemm_acc_kernel<0,fused>" : "gemm_acc_kernel<0>";
+    info->mma_family = "tcgen05.mma.cta_group::1.kind::f16";
+  } else if (variant == 2) {
+    info->stages = block_n == 256 ? AccCfg<2, 256>::kStages : AccCfg<2, 128>::kStages;
+    info->acc_stages = block_n == 256 ? AccCfg<2, 256>::kAccStages : AccCfg<2, 128>::kAccStages;
+    info->mma_k = 64;
+    info->symbol = fused ? "gemm_acc_kernel<2,fused>" : "gemm_acc_kernel<2>";
+    info->mma_family = "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32";
+  } else {
+    info->stages = block_n == 256 ? AccCfg<1, 256>::kStages : AccCfg<1, 128>::kStages;
+    info->acc_stages = 2;
+    info->mma_k = 32;
+    info->symbol = "gemm_acc_kernel<1>";
+    info->mma_family = "tcgen05.mma.cta_group::1.kind::i8";
+  }
 }
 
 }  // namespace adg

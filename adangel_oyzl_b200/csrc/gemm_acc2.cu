@@ -19,11 +19,13 @@
 //   tmem_empty[a]  the LEADER's barrier counts the epilogue warps of both CTAs (the follower's warps
 //                  arrive remotely)
 //   sf_full[s]     (O2) the leader's copier thread commits the stage's scale-factor copies to it
+// FUSED kernels add a fourth warp group to every CTA that converts A_int8 into the operand (FP16 for O0, MXFP4
+// codes + tiled scales for O2) while the tensor cores run; each producer waits for the row counters of its
+// own 128 rows before loading them (see gemm_acc.cu for the role and the register re-balancing).
 // All waits are bounded (see common.cuh); the two cluster-wide barriers at start and end are reached
 // by every thread after its bounded loops.
-#include <cstdio>
-
 #include "common.cuh"
+#include "convert_device.cuh"
 #include "launch.h"
 
 namespace adg {
@@ -36,8 +38,14 @@ constexpr int kHalfN = kBlockN / 2;
 constexpr int kTileA = kBlockM * 128;
 constexpr int kTileB = kHalfN * 128;
 constexpr int kEpiWarps = 8;
-constexpr int kSfWarp = 2 + kEpiWarps;
-constexpr int kThreads = (2 + kEpiWarps + 2) * 32;
+constexpr int kSfWarp = 2;
+constexpr int kFirstEpiWarp = 4;  // the epilogue is warp groups 1 and 2
+constexpr int kFirstConvWarp = kFirstEpiWarp + kEpiWarps;  // warp group 3 (FUSED kernels)
+constexpr int kThreads = kFirstConvWarp * 32;
+constexpr int kFusedThreads = kThreads + kConvThreads;
+constexpr int kFusedRegsRoles = 64, kFusedRegsConv = 112, kFusedRegsEpi = 168;  // see gemm_acc.cu
+static_assert(128 * (kFusedRegsRoles + kFusedRegsConv + 2 * kFusedRegsEpi) == 65536, "register budget");
+constexpr int kConvBarrier = 1;
 constexpr int kStagingPerWarp = 2048;
 constexpr int kStagingBytes = kEpiWarps * kStagingPerWarp;
 constexpr int kGroupM = 4;  // tile rasterisation: sweep 4 row-pairs before moving to the next column block
@@ -59,7 +67,30 @@ struct PairCfg {
   static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
 };
 
-enum : uint32_t { kTagEmpty = 0x4100, kTagFull = 0x4200, kTagTmemEmpty = 0x4300, kTagTmemFull = 0x4400, kTagSfFull = 0x4500 };
+enum : uint32_t { kTagEmpty = 0x4100, kTagFull = 0x4200, kTagTmemEmpty = 0x4300, kTagTmemFull = 0x4400, kTagSfFull = 0x4500,
+                  kTagRowsReady = 0x4600 };
+
+// Bounded wait until `*counter` has reached `need` (see gemm_acc.cu).
+__device__ __forceinline__ bool wait_rows_ready(const uint32_t* counter, uint32_t need, const WaitEnv& env, uint32_t tag) {
+  if (ld_acquire_gpu(counter) >= need) return true;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (ld_acquire_gpu(counter) < need) {
+    if ((++spins & 0xFFu) == 0) {
+      if (*env.abort) return false;
+      if (global_timer_ns() - t0 > kWaitTimeoutNs) {
+        *env.abort = 1;
+        if (atomicCAS(env.status, 0u, static_cast<uint32_t>(kStatusWaitTimeout)) == 0u) {
+          env.status[1] = tag;
+          env.status[2] = blockIdx.x;
+          env.status[3] = need;
+        }
+        return false;
+      }
+    }
+  }
+  return true;
+}
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -126,24 +157,6 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
 }
 
-// Optional stall accounting (compile with -DADG_PAIR_PROF): cycles each role of cluster 0 spends in
-// its waits, printed when the role ends.
-#ifdef ADG_PAIR_PROF
-#define PROF_DECL(...) long long __VA_ARGS__
-#define PROF_WAIT(ctr, call)       \
-  do {                             \
-    const long long t_ = clock64(); \
-    ok = (call);                   \
-    ctr += clock64() - t_;         \
-  } while (0)
-#define PROF_PRINT(...) \
-  if (cluster_id == 0) printf(__VA_ARGS__)
-#else
-#define PROF_DECL(...)
-#define PROF_WAIT(ctr, call) ok = (call)
-#define PROF_PRINT(...)
-#endif
-
 struct TileCoord {
   int m_pair, n_blk;
 };
@@ -159,12 +172,12 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_mp, int num_n)
   return t;
 }
 
-template <int KIND>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int KIND, bool FUSED>
+__global__ void __launch_bounds__(FUSED ? kFusedThreads : kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_sfa,
                  const __grid_constant__ CUtensorMap tm_sfb, float* __restrict__ y, int M, int N, int K, int ldy,
-                 int use_tma_store, uint32_t* status) {
+                 int use_tma_store, uint32_t* status, const FusedConvert conv) {
   using Cfg = PairCfg<KIND>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -223,6 +236,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
+  // Warp group 0: the one-thread roles.  (FUSED: each warp group starts its branch with the register
+  // re-balancing, all four warps of the group at the same instruction.)
+  if (warp < kFirstEpiWarp) {
+    if constexpr (FUSED) reg_dealloc<kFusedRegsRoles>();
+  }
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs) ---------------------------------
     if (lane == 0) {
@@ -230,14 +248,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       const uint32_t full_leader = map_to_cta(smem_u32(full_bar), 0);
-      PROF_DECL(w_empty = 0, t_start = clock64());
       for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
         const TileCoord tc = tile_coord(tile, num_mp, num_n);
         const int m_blk = tc.m_pair * 2 + static_cast<int>(rank);
         const int row0 = m_blk * kBlockM;
         const int wrow0 = tc.n_blk * kBlockN + static_cast<int>(rank) * kHalfN;
+        if constexpr (FUSED) {
+          // this CTA's 128 rows of the operand are being written by the converter warps of all CTAs
+          // (a pair's second row block may lie wholly beyond M: nothing to wait for, the loads read zeros)
+          const int rows_left = M - row0;
+          if (rows_left > 0) {
+            ok = wait_rows_ready(conv.ready + m_blk, static_cast<uint32_t>(min(kBlockM, rows_left)), env, kTagRowsReady);
+            if (!ok) break;
+          }
+          fence_proxy_async_all();
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
-          PROF_WAIT(w_empty, mbar_wait(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage));
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage);
           if (!ok) break;
           uint8_t* st = smem + stage * Cfg::kStageBytes;
           if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
@@ -257,7 +284,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
         }
       }
-      PROF_PRINT("producer rank %u: total %lld, waiting for a free stage %lld\n", rank, clock64() - t_start, w_empty);
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (leader CTA only) -----------------------------
@@ -268,29 +294,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       bool ok = true;
       const uint32_t empty_own = smem_u32(empty_bar), empty_peer = map_to_cta(empty_own, peer);
       const uint32_t tfull_own = smem_u32(tmem_full_bar), tfull_peer = map_to_cta(tfull_own, peer);
-      PROF_DECL(w_full = 0, w_sf = 0, w_acc = 0, t_start = clock64());
       for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++local_tile) {
         const int acc = local_tile % Cfg::kAccStages;
         const uint32_t acc_phase = static_cast<uint32_t>(local_tile / Cfg::kAccStages) & 1u;
-#ifndef ADG_PAIR_NOACCWAIT
-        PROF_WAIT(w_acc, mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, env, kTagTmemEmpty | acc));
+        ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, env, kTagTmemEmpty | acc);
         if (!ok) break;
-#endif
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBlockN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          PROF_WAIT(w_full, mbar_wait(&full_bar[stage], phase, env, kTagFull | stage));
+          ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | stage);
           if (!ok) break;
           tc_fence_after();
           const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
           const uint64_t adesc = make_desc_sw128(st);
           const uint64_t bdesc = make_desc_sw128(st + kTileA);
           if constexpr (Cfg::kScaled) {
-#ifndef ADG_PAIR_NOSFWAIT
-            PROF_WAIT(w_sf, mbar_wait(&sf_full_bar[stage], phase, env, kTagSfFull | stage));
+            ok = mbar_wait(&sf_full_bar[stage], phase, env, kTagSfFull | stage);
             if (!ok) break;
             tc_fence_after();
-#endif
             const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
             const uint32_t sfb_t = sfa_t + 8;
 #pragma unroll
@@ -318,8 +339,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           umma_commit_pair(tfull_peer + acc * 8);
         }
       }
-      PROF_PRINT("MMA thread: total %lld, waiting for data %lld, for scale copies %lld, for a free accumulator %lld\n",
-                 clock64() - t_start, w_full, w_sf, w_acc);
     }
   } else if (warp == kSfWarp) {
     // ------------------------------- scale-factor copier (O2, leader CTA only) ----------------
@@ -341,7 +360,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const uint32_t sfb_s = sfa_s + Cfg::kSfa;
             const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
             const uint32_t sfb_t = sfa_t + 8;
-#ifndef ADG_PAIR_NOSFCP
 #pragma unroll
             for (int ka = 0; ka < 2; ++ka) {
               tmem_cp_pair_32x128b_warpx4(sfa_t + ka * 4, make_desc_sf(sfa_s + ka * 512));
@@ -350,7 +368,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 tmem_cp_pair_32x128b_warpx4(sfb_t + ka * (kBlockN / 32) + rb * 4, make_desc_sf(sfb_s + rb * 1024 + ka * 512));
               }
             }
-#endif
             umma_commit_pair(sf_full_own + stage * 8);
             if (++stage == Cfg::kStages) {
               stage = 0;
@@ -360,24 +377,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
       }
     }
-  } else if (warp >= 2 && warp < 2 + kEpiWarps) {
+  } else if (warp >= kFirstEpiWarp && warp < kFirstConvWarp) {
+    if constexpr (FUSED) reg_alloc<kFusedRegsEpi>();
     // ------------------------------- epilogue (both CTAs) -------------------------------------
     const int q = warp & 3;
-    const int h = (warp - 2) >> 2;
+    const int h = (warp - kFirstEpiWarp) >> 2;
     constexpr int CW = kBlockN / 2;
-    uint8_t* buf = staging + (warp - 2) * kStagingPerWarp;
+    uint8_t* buf = staging + (warp - kFirstEpiWarp) * kStagingPerWarp;
     const uint32_t buf_row = smem_u32(buf) + lane * 64;
     const uint32_t swz = static_cast<uint32_t>((lane >> 1) & 3);
     const uint64_t store_policy = l2_policy_evict_first();
     const uint32_t tempty_leader = map_to_cta(smem_u32(tmem_empty_bar), 0);
     int local_tile = 0;
     bool ok = true;
-    PROF_DECL(w_tfull = 0, t_start = clock64());
     for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++local_tile) {
       const TileCoord tc = tile_coord(tile, num_mp, num_n);
       const int acc = local_tile % Cfg::kAccStages;
       const uint32_t acc_phase = static_cast<uint32_t>(local_tile / Cfg::kAccStages) & 1u;
-      PROF_WAIT(w_tfull, mbar_wait(&tmem_full_bar[acc], acc_phase, env, kTagTmemFull | acc));
+      ok = mbar_wait(&tmem_full_bar[acc], acc_phase, env, kTagTmemFull | acc);
       if (!ok) break;
       tc_fence_after();
       const int row0 = (tc.m_pair * 2 + static_cast<int>(rank)) * kBlockM + q * 32;
@@ -423,9 +440,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       }
     }
     if (lane == 0) bulk_wait_group<0>();
-    if (lane == 0 && warp == 2) {
-      PROF_PRINT("epilogue warp 2 rank %u: total %lld, waiting for an accumulator %lld (%d tiles)\n", rank,
-                 clock64() - t_start, w_tfull, local_tile);
+  } else if (warp >= kFirstConvWarp) {
+    // ------------------------------- activation converters (FUSED, both CTAs) ------------------
+    if constexpr (FUSED) {
+      reg_dealloc<kFusedRegsConv>();
+      convert_rows_role<KIND>(conv, M, K, static_cast<int>(threadIdx.x) - kThreads, blockIdx.x, gridDim.x, kConvBarrier);
     }
   }
 
@@ -436,13 +455,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   cluster_sync_all();
   tc_fence_after();
   if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
+  if constexpr (FUSED) {
+    // the last CTA to get here zeroes the row counters for the next launch (see gemm_acc.cu)
+    if (threadIdx.x == 0) {
+      const int num_m = (M + kBlockM - 1) / kBlockM;
+      __threadfence();
+      if (atomicAdd(conv.ready + num_m, 1u) == gridDim.x - 1) {
+        for (int i = 0; i <= num_m; ++i) conv.ready[i] = 0u;
+        __threadfence();
+      }
+    }
+  }
 }
 
-template <int KIND>
+template <int KIND, bool FUSED>
 int launch_pair(const GemmPlan& p, cudaStream_t stream) {
   cudaLaunchConfig_t config{};
   config.gridDim = dim3(static_cast<unsigned>(p.grid));
-  config.blockDim = dim3(kThreads);
+  config.blockDim = dim3(FUSED ? kFusedThreads : kThreads);
   config.dynamicSmemBytes = PairCfg<KIND>::kSmemBytes;
   config.stream = stream;
   cudaLaunchAttribute attr{};
@@ -452,32 +482,76 @@ int launch_pair(const GemmPlan& p, cudaStream_t stream) {
   attr.val.clusterDim.z = 1;
   config.attrs = &attr;
   config.numAttrs = 1;
-  return check_cuda(cudaLaunchKernelEx(&config, gemm_pair_kernel<KIND>, p.tm_a, p.tm_b, p.tm_y, p.tm_sfa, p.tm_sfb, p.y,
-                                       p.M, p.N, p.K, p.ldy, p.use_tma_store, p.status),
+  FusedConvert conv{};
+  if constexpr (FUSED) {
+    conv.a_int8 = static_cast<const uint4*>(p.fused_a_int8);
+    conv.a_scale = static_cast<const float*>(p.a_scale);
+    conv.a_out = p.fused_a_out;
+    conv.sf_natural = static_cast<uint8_t*>(p.fused_sf_natural);
+    conv.sf_tiled = static_cast<uint8_t*>(const_cast<void*>(p.sfa));
+    conv.ready = p.fused_ready;
+  }
+  return check_cuda(cudaLaunchKernelEx(&config, gemm_pair_kernel<KIND, FUSED>, p.tm_a, p.tm_b, p.tm_y, p.tm_sfa, p.tm_sfb,
+                                       p.y, p.M, p.N, p.K, p.ldy, p.use_tma_store, p.status, conv),
                     "gemm_pair_kernel launch");
+}
+
+template <int KIND, bool FUSED>
+int set_pair_attr() {
+  return check_cuda(cudaFuncSetAttribute(gemm_pair_kernel<KIND, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         PairCfg<KIND>::kSmemBytes),
+                    "cudaFuncSetAttribute(gemm_pair_kernel)");
 }
 
 }  // namespace
 
 int init_gemm_pair_attributes() {
-  if (int rc = check_cuda(cudaFuncSetAttribute(gemm_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               PairCfg<0>::kSmemBytes),
-                          "cudaFuncSetAttribute(gemm_pair_kernel<0>)"))
-    return rc;
-  return check_cuda(cudaFuncSetAttribute(gemm_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         PairCfg<2>::kSmemBytes),
-                    "cudaFuncSetAttribute(gemm_pair_kernel<2>)");
+  if (int rc = set_pair_attr<0, false>()) return rc;
+  if (int rc = set_pair_attr<2, false>()) return rc;
+  if (int rc = set_pair_attr<0, true>()) return rc;
+  return set_pair_attr<2, true>();
 }
 
 // The plan's tm_b must have 128-row boxes (one CTA's half of the W tile); grid = 2 x clusters; an O2
 // plan also carries the tensor maps of the two tiled scale arrays.
 int run_gemm_pair(const GemmPlan& p, cudaStream_t stream) {
-  if (p.variant == 0) return launch_pair<0>(p, stream);
-  if (p.variant == 2) return launch_pair<2>(p, stream);
+  if (p.fused) {
+    if (p.fused_ready == nullptr || p.fused_a_int8 == nullptr || p.fused_a_out == nullptr)
+      return fail("run_gemm_pair: a fused plan needs A_int8, the operand buffer and the row counters");
+    if (p.variant == 0) return launch_pair<0, true>(p, stream);
+    if (p.variant == 2) return launch_pair<2, true>(p, stream);
+  } else {
+    if (p.variant == 0) return launch_pair<0, false>(p, stream);
+    if (p.variant == 2) return launch_pair<2, false>(p, stream);
+  }
   return fail("run_gemm_pair: plan is not an O0/O2 plan");
 }
 
 int pair_tile_m() { return 2 * kBlockM; }
 int pair_tile_n() { return kBlockN; }
+
+void describe_gemm_pair(int variant, bool fused, PlanInfo* info) {
+  info->tile_m = 2 * kBlockM;
+  info->tile_n = kBlockN;
+  info->threads = fused ? kFusedThreads : kThreads;
+  info->cluster = 2;
+  info->persistent = 1;
+  info->fused_activation = fused ? 1 : 0;
+  info->mma_m = 2 * kBlockM;
+  info->mma_n = kBlockN;
+  if (variant == 0) {
+    info->stages = PairCfg<0>::kStages;
+    info->acc_stages = PairCfg<0>::kAccStages;
+    info->mma_k = 16;
+    info->symbol = fused ? "gemm_pair_kernel<0,fused>" : "gemm_pair_kernel<0>";
+    info->mma_family = "tcgen05.mma.cta_group::2.kind::f16";
+  } else {
+    info->stages = PairCfg<2>::kStages;
+    info->acc_stages = PairCfg<2>::kAccStages;
+    info->mma_k = 64;
+    info->symbol = fused ? "gemm_pair_kernel<2,fused>" : "gemm_pair_kernel<2>";
+    info->mma_family = "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32";
+  }
+}
 
 }  // namespace adg

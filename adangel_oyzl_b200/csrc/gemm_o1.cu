@@ -27,20 +27,8 @@ namespace adg {
 
 namespace {
 
-#ifdef ADG_TRACE
-#define TR(slot_, idx_)                                                                                      \
-  do {                                                                                                       \
-    if (blockIdx.x == 0 && (idx_) < 256) trace[(slot_) * 256 + (idx_)] = static_cast<uint32_t>(clock64());     \
-  } while (0)
-#else
-#define TR(slot_, idx_) do {} while (0)
-#endif
-
-#ifndef ADG_O1_BN
-#define ADG_O1_BN 128
-#endif
 constexpr int kBlockM = 128;
-constexpr int kBlockN = ADG_O1_BN;
+constexpr int kBlockN = 128;
 constexpr int kCtasPerSm = 128 / kBlockN;
 constexpr int kStages = kBlockN == 128 ? 6 : 4;  // A 128x128 B + W kBlockN x 128 B (4 groups) each
 constexpr int kScStages = 8;    // 4 groups x kBlockN FP32 factors each
@@ -68,7 +56,9 @@ enum : uint32_t {
 struct TileCoord {
   int m_blk, n_blk;
 };
-__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) {
+// `n_list`, if given, restricts the launch to some column blocks: n_list[0] of them, listed from n_list[1]
+// (the exact-integer O1 variant sends only the column blocks that hold an ineligible W row through here).
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, const int32_t* __restrict__ n_list) {
   const int per_group = kGroupM * num_n;
   const int group = tile / per_group;
   const int first_m = group * kGroupM;
@@ -77,6 +67,7 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) 
   TileCoord t;
   t.m_blk = first_m + in_group % gsize;
   t.n_blk = in_group / gsize;
+  if (n_list != nullptr) t.n_blk = __ldg(n_list + 1 + t.n_blk);
   return t;
 }
 
@@ -87,9 +78,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const float* __restrict__ a_scale, const uint8_t* __restrict__ w_scale, float* __restrict__ y,
                int32_t* __restrict__ partial_dump, int M, int N, int K, int ldy, uint32_t* status,
-               const uint32_t* __restrict__ only_if_flag) {
+               const uint32_t* __restrict__ only_if_flag, const int32_t* __restrict__ n_list) {
   // second half of a sync-free fallback: run only when the BF16-operand kernel in front refused
   if (only_if_flag != nullptr && *only_if_flag == 0u) return;
+  if (n_list != nullptr && __ldg(n_list) <= 0) return;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* sc_ring = reinterpret_cast<float*>(smem + kStages * kStageBytes);
@@ -111,14 +103,10 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   const uint32_t full_a = smem_u32(full_bar), empty_a = smem_u32(empty_bar);
 
   const int num_m = (M + kBlockM - 1) / kBlockM;
-  const int num_n = (N + kBlockN - 1) / kBlockN;
+  const int num_n = n_list != nullptr ? __ldg(n_list) : (N + kBlockN - 1) / kBlockN;
   const int num_tiles = num_m * num_n;
   const int groups = K / 32;
   const int num_kb = (groups + 3) / 4;
-#ifdef ADG_TRACE
-  uint32_t* trace = reinterpret_cast<uint32_t*>(partial_dump);
-  int tr_i = 0;
-#endif
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -158,7 +146,7 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const TileCoord tc = tile_coord(tile, num_m, num_n);
+        const TileCoord tc = tile_coord(tile, num_m, num_n, n_list);
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait_a(empty_a + stage * 8, phase ^ 1u, status, abort_a, kTagEmpty | stage);
           if (!ok) break;
@@ -182,29 +170,21 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       constexpr uint32_t idesc = make_idesc(2, kFmtS8, kFmtS8, kBlockM, kBlockN);
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         for (int kb = 0; ok && kb < num_kb; ++kb) {
-          TR(3, tr_i >> 1);
           ok = mbar_wait_a(full_a + stage * 8, phase, status, abort_a, kTagFull | stage);
           if (!ok) break;
-          TR(4, tr_i >> 1);
           tc_fence_after();
           const uint32_t st = smem_u32(smem + stage * kStageBytes);
           const uint64_t adesc = make_desc_sw128(st);
           const uint64_t bdesc = make_desc_sw128(st + kTile);
           const int ng = min(4, groups - kb * 4);  // K is a multiple of 64, so ng is 2 or 4
           for (int g = 0; g < ng; g += 2) {
-            TR(0, tr_i);
             ok = mbar_wait_a(tmem_empty_a + pair * 8, pair_phase ^ 1u, status, abort_a, kTagTmemEmpty | pair);
             if (!ok) break;
-            TR(1, tr_i);
             tc_fence_after();
             const uint32_t d = tmem_base + static_cast<uint32_t>(pair * 2 * kBlockN);
             umma_i8(d, adesc + g * 2, bdesc + g * 2, idesc, 0u);
             umma_i8(d + kBlockN, adesc + (g + 1) * 2, bdesc + (g + 1) * 2, idesc, 0u);
             umma_commit_a(tmem_full_a + pair * 8);
-            TR(2, tr_i);
-#ifdef ADG_TRACE
-            ++tr_i;
-#endif
             if (++pair == kPairs) {
               pair = 0;
               pair_phase ^= 1u;
@@ -247,9 +227,9 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     };
     uint32_t next_codes[kRowsPerLane];
     int tile = blockIdx.x;
-    if (tile < num_tiles) load_codes(tile_coord(tile, num_m, num_n).n_blk, 0, next_codes);
+    if (tile < num_tiles) load_codes(tile_coord(tile, num_m, num_n, n_list).n_blk, 0, next_codes);
     for (; ok && tile < num_tiles; tile += gridDim.x) {
-      const int n_blk = tile_coord(tile, num_m, num_n).n_blk;
+      const int n_blk = tile_coord(tile, num_m, num_n, n_list).n_blk;
       for (int kb = 0; kb < num_kb; ++kb) {
         uint32_t codes[kRowsPerLane];
 #pragma unroll
@@ -257,12 +237,10 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (kb + 1 < num_kb) {
           load_codes(n_blk, kb + 1, next_codes);
         } else if (tile + static_cast<int>(gridDim.x) < num_tiles) {
-          load_codes(tile_coord(tile + gridDim.x, num_m, num_n).n_blk, 0, next_codes);
+          load_codes(tile_coord(tile + gridDim.x, num_m, num_n, n_list).n_blk, 0, next_codes);
         }
-        if (lane == 0) TR(15, tr_i);
         ok = mbar_wait_a(sc_empty_a + scs * 8, sc_phase ^ 1u, status, abort_a, kTagScEmpty | scs);
         if (!ok) break;
-        if (lane == 0) TR(16, tr_i);
         float* dst = sc_ring + scs * (kScBytes / 4);
 #pragma unroll
         for (int i = 0; i < kRowsPerLane; ++i) {
@@ -275,10 +253,6 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           }
         }
         mbar_arrive_a(sc_full_a + scs * 8);
-        if (lane == 0) TR(17, tr_i);
-#ifdef ADG_TRACE
-        ++tr_i;
-#endif
         if (++scs == kScStages) {
           scs = 0;
           sc_phase ^= 1u;
@@ -320,7 +294,7 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     };
 
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      const TileCoord tc = tile_coord(tile, num_m, num_n);
+      const TileCoord tc = tile_coord(tile, num_m, num_n, n_list);
       const int row = tc.m_blk * kBlockM + q * 32 + lane;
       const int col0 = tc.n_blk * kBlockN + cs * 32;
       const float a_m = row < M ? __ldg(a_scale + row) : 0.0f;
@@ -341,14 +315,7 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         }
         const uint32_t sc = sc_base + static_cast<uint32_t>(scs * kScBytes + ((g & 3) * kBlockN) * 4);
         // ---- first partial of the pair: wait for it, start loading the second, compute
-#ifdef ADG_TRACE
-        const int tslot = warp == kFirstEpiWarp ? 5 : 10;
-        const bool tr_on = lane == 0 && (warp == kFirstEpiWarp || warp == kFirstEpiWarp + kEpiWarps - 1);
-#endif
         tmem_wait_ld_for(pa);
-#ifdef ADG_TRACE
-        if (tr_on) TR(tslot, tr_i);
-#endif
         tmem_ld_32x32(t_lane + (pair * 2 + 1) * kBlockN, pb);
         if constexpr (kDump) {
           if (row < M) {
@@ -358,14 +325,8 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           }
         }
         accumulate(pa, acc, a2, sc);
-#ifdef ADG_TRACE
-        if (tr_on) TR(tslot + 1, tr_i);
-#endif
         // ---- second partial: wait for it, hand the pair back, start loading the next pair's first
         tmem_wait_ld_for(pb);
-#ifdef ADG_TRACE
-        if (tr_on) TR(tslot + 2, tr_i);
-#endif
         // the next pair's first load goes out before this pair is handed back, so that the warp
         // has no load in flight only for the length of one barrier probe
         const int done_pair = pair;
@@ -378,9 +339,6 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           ok = mbar_wait_a(tmem_full_a + pair * 8, pair_phase, status, abort_a, kTagTmemFull | pair);
           if (!ok) break;
           tc_fence_after();
-#ifdef ADG_TRACE
-          if (tr_on) TR(tslot + 3, tr_i);
-#endif
           tmem_ld_32x32(t_lane + pair * 2 * kBlockN, pa);
         }
         tc_fence_before();  // tcgen05.wait::ld is warp-collective: every lane's loads have landed
@@ -393,10 +351,6 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           }
         }
         accumulate(pb, acc, a2, sc + kBlockN * 4);
-#ifdef ADG_TRACE
-        if (tr_on) TR(tslot + 4, tr_i);
-        ++tr_i;
-#endif
         if ((g & 3) == 2 || !more) {
           __syncwarp();
           if (lane == 0) mbar_arrive_a(sc_empty_a + scs * 8);
@@ -447,25 +401,25 @@ int init_gemm_o1_attributes() {
 
 int run_gemm_o1(const GemmPlan& p, cudaStream_t stream) {
   if (p.variant != 1) return fail("run_gemm_o1: plan is not an O1 plan");
-#ifdef ADG_TRACE
-  if (false) {
-#else
   if (p.partial_dump != nullptr) {
-#endif
     gemm_o1_kernel<true><<<p.grid, kThreads, kSmemBytes, stream>>>(
         p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y,
-        p.partial_dump, p.M, p.N, p.K, p.ldy, p.status, p.only_if_flag);
+        p.partial_dump, p.M, p.N, p.K, p.ldy, p.status, p.only_if_flag, p.n_list);
   } else {
     gemm_o1_kernel<false><<<p.grid, kThreads, kSmemBytes, stream>>>(
         p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y,
-#ifdef ADG_TRACE
-        p.partial_dump,
-#else
         nullptr,
-#endif
-        p.M, p.N, p.K, p.ldy, p.status, p.only_if_flag);
+        p.M, p.N, p.K, p.ldy, p.status, p.only_if_flag, p.n_list);
   }
   return check_cuda(cudaGetLastError(), "gemm_o1_kernel launch");
+}
+
+void describe_gemm_o1(PlanInfo* info) {
+  info->symbol = "gemm_o1_kernel";
+  info->mma_family = "tcgen05.mma.cta_group::1.kind::i8";
+  info->tile_m = kBlockM, info->tile_n = kBlockN, info->stages = kStages, info->acc_stages = kPairs;
+  info->threads = kThreads, info->cluster = 1, info->mma_m = kBlockM, info->mma_n = kBlockN, info->mma_k = 32;
+  info->persistent = 1;
 }
 
 }  // namespace adg

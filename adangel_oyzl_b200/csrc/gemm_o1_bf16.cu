@@ -341,4 +341,12 @@ int run_gemm_o1_bf16(const GemmPlan& p, cudaStream_t stream) {
   return check_cuda(cudaGetLastError(), "gemm_o1_bf16_kernel launch");
 }
 
+void describe_gemm_o1_bf16(PlanInfo* info) {
+  info->symbol = "gemm_o1_bf16_kernel";
+  info->mma_family = "tcgen05.mma.cta_group::1.kind::f16 (bf16 operands; exact integer partials)";
+  info->tile_m = kBlockM, info->tile_n = kBlockN, info->stages = kStages, info->acc_stages = kBufs;
+  info->threads = kThreads, info->cluster = 1, info->mma_m = kBlockM, info->mma_n = kBlockN, info->mma_k = 16;
+  info->persistent = 1;
+}
+
 }  // namespace adg

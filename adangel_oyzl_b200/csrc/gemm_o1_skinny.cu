@@ -278,4 +278,12 @@ int run_gemm_o1_skinny(const GemmPlan& p, cudaStream_t stream) {
   return check_cuda(cudaGetLastError(), "gemm_o1_skinny_kernel launch");
 }
 
+void describe_gemm_o1_skinny(PlanInfo* info) {
+  info->symbol = "gemm_o1_skinny_kernel";
+  info->mma_family = "tcgen05.mma.cta_group::1.kind::i8";
+  info->tile_m = kCols, info->tile_n = kRows, info->stages = kStages, info->acc_stages = kSlots;
+  info->threads = kThreads, info->cluster = 1, info->mma_m = kRows, info->mma_n = kCols, info->mma_k = 32;
+  info->persistent = 0;
+}
+
 }  // namespace adg

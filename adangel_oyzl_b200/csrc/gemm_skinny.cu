@@ -226,4 +226,13 @@ int run_gemm_o2_skinny(const GemmPlan& p, cudaStream_t stream) {
   return check_cuda(cudaGetLastError(), "gemm_o2_skinny_kernel launch");
 }
 
+void describe_gemm_o2_skinny(int M, PlanInfo* info) {
+  const int m_pad = (M + 15) / 16 * 16;
+  info->symbol = "gemm_o2_skinny_kernel";
+  info->mma_family = "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32";
+  info->tile_m = m_pad, info->tile_n = kRows, info->stages = kStages, info->acc_stages = 1;
+  info->threads = kThreads, info->cluster = 1, info->mma_m = kRows, info->mma_n = m_pad, info->mma_k = 64;
+  info->persistent = 0;
+}
+
 }  // namespace adg

@@ -30,6 +30,10 @@ int device_ctx(DeviceCtx** out);
 // `stream` first), clears them, and returns non-zero with a message if a kernel reported an error.
 int check_device_status(cudaStream_t stream);
 
+// Status words of asynchronous adg_o2_linear_noalloc calls (noalloc.cu); a no-op when that entry point
+// has not been used on the current device.
+int noalloc_check_status(cudaStream_t stream, bool synchronize);
+
 // ---- scale-factor tiled layout ---------------------------------------------------------------------
 // 512-byte atoms of 128 rows x 4 K32 blocks, ordered row-block major / K-atom minor; rows are
 // padded to a multiple of 256 and K32 blocks to a multiple of 8 (zero bytes).
@@ -68,7 +72,7 @@ int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_b
 // A plan holds the encoded tensor maps and launch geometry of one GEMM on fixed buffers; running it
 // only launches the kernel.
 struct GemmPlan {
-  int variant = -1;  // 0 = O0 (f16), 1 = O1 (i8 + per-K32 rescale), 2 = O2 (mxf4 block-scaled)
+  int variant = -1;  // 0 = O0 (f16), 1 = O1 (i8 + per-K32 rescale), 2 = O2 (mxf4 block-scaled), 3 = o1x (i8, exact integer)
   int M = 0, N = 0, K = 0, ldy = 0;
   int block_n = 0;
   int grid = 0;
@@ -89,14 +93,51 @@ struct GemmPlan {
   const uint32_t* only_if_flag = nullptr;  // O1 INT8: run only when this device word is non-zero
   int quiet_refusal = 0;                 // O1 BF16: a set flag makes the kernel return without an error status
   int pair = 0;  // O0/O2 on CTA pairs (cta_group::2): tm_b has 128-row boxes, grid = 2 x clusters
+  const int32_t* n_list = nullptr;   // O1 INT8: restrict the launch to the listed column blocks ([0] = count)
+  const void* col_factor = nullptr;  // o1x: float [N], 2**(emin[n]-128)
+  // O0/O2 with the activation conversion done by converter warps inside the GEMM kernel: tm_a maps
+  // `fused_a_out`, which those warps write from `fused_a_int8` (a_scale = the row scales); `fused_ready`
+  // holds ceil(M/128) + 1 zeroed counters
+  int fused = 0;
+  const void* fused_a_int8 = nullptr;
+  void* fused_a_out = nullptr;
+  void* fused_sf_natural = nullptr;
+  uint32_t* fused_ready = nullptr;
   uint32_t* status = nullptr;
 };
+
+// What a plan would run, for callers that report it (adg_plan_info).
+struct PlanInfo {
+  const char* symbol = "";
+  const char* mma_family = "";
+  int tile_m = 0, tile_n = 0, stages = 0, acc_stages = 0, threads = 0, cluster = 1;
+  int mma_m = 0, mma_n = 0, mma_k = 0, persistent = 0, fused_activation = 0;
+};
+constexpr int kPlanO1Bf16 = 1, kPlanFusedActivation = 2, kPlanPartialDump = 4;
+int plan_info(int variant, int flags, int M, int N, int K, PlanInfo* info);
+void describe_gemm_acc(int variant, int block_n, bool fused, PlanInfo* info);
+void describe_gemm_pair(int variant, bool fused, PlanInfo* info);
+void describe_gemm_o1(PlanInfo* info);
+void describe_gemm_o1_bf16(PlanInfo* info);
+void describe_gemm_o1_skinny(PlanInfo* info);
+void describe_gemm_o2_skinny(int M, PlanInfo* info);
 
 int plan_o0(GemmPlan* plan, const void* a_fp16, const void* w_fp16, float* y, int M, int N, int K, int ldy);
 int plan_o1(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale, float* y,
             int32_t* partial_dump, int M, int N, int K, int ldy);
 int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const void* w_mxfp4, const void* sfb_tiled,
             float* y, int M, int N, int K, int ldy);
+// plan_o1 without the decode-shape dispatch: always the 128 x 128-tile INT8-operand kernel
+int plan_o1_tiled(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale,
+                  float* y, int32_t* partial_dump, int M, int N, int K, int ldy);
+int plan_o1x(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8x, const void* col_factor, float* y,
+             int M, int N, int K, int ldy);
+// O0 / O2 with the activation conversion inside the GEMM kernel (M > 64; `ready`: adg_fused_workspace_bytes)
+int plan_o0_fused(GemmPlan* plan, const void* a_int8, const void* a_scale, void* a_fp16, const void* w_fp16, float* y,
+                  void* ready, int M, int N, int K, int ldy);
+int plan_o2_fused(GemmPlan* plan, const void* a_int8, const void* a_scale, void* a_mxfp4, void* sfa_tiled, void* sf_natural,
+                  const void* w_mxfp4, const void* sfb_tiled, float* y, void* ready, int M, int N, int K, int ldy);
+bool fusion_enabled();  // ADG_FUSE_A in the environment: 0 = callers of the *_linear entries get separate kernels
 int plan_o1_bf16(GemmPlan* plan, const void* a_bf16, const void* a_scale, const void* w_bf16, float* y,
                  const void* range_flag, int M, int N, int K, int ldy);
 int run_plan(const GemmPlan& plan, cudaStream_t stream);

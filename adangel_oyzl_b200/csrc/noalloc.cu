@@ -93,7 +93,49 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, ui
   return 0;
 }
 
+// Reads (and, if set, clears) the status words that this entry point's kernels keep in the scratch array.
+int read_status(Setup* s, const char* who) {
+  uint32_t* status = reinterpret_cast<uint32_t*>(s->base + kCodesBytes + kScalesBytes);
+  uint32_t words[4] = {};
+  if (int rc = check_cuda(cudaMemcpy(words, status, sizeof(words), cudaMemcpyDeviceToHost), "cudaMemcpy(status)")) return rc;
+  if (words[0] == kStatusOk) return 0;
+  check_cuda(cudaMemset(status, 0, kStatusBytes), "cudaMemset(status)");
+  return fail(std::string(who) + ": kernel wait timeout: code=" + std::to_string(words[0]) + " tag=" + std::to_string(words[1]) +
+              " block=" + std::to_string(words[2]));
+}
+
 }  // namespace
+
+namespace adg {
+// Status of asynchronous adg_o2_linear_noalloc calls on the current device; does nothing (and sets
+// nothing up) when the entry point has not been used on this device.
+int noalloc_check_status(cudaStream_t stream, bool synchronize) {
+  int dev = -1;
+  if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+  if (dev < 0 || dev >= kMaxDevices) return 0;
+  Setup* s = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_setup[dev].ready) return 0;
+    s = &g_setup[dev];
+  }
+  if (synchronize)
+    if (int rc = check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize")) return rc;
+  return read_status(s, "adg_o2_linear_noalloc");
+}
+}  // namespace adg
+
+extern "C" int adg_o2_linear_noalloc_status(void* stream) {
+  return noalloc_check_status(static_cast<cudaStream_t>(stream), /*synchronize=*/true);
+}
+
+extern "C" int adg_o2_linear_noalloc_status_words(void** device_address, int* bytes) {
+  Setup* s = nullptr;
+  if (int rc = setup_current_device(&s)) return rc;
+  if (device_address) *device_address = s->base + kCodesBytes + kScalesBytes;
+  if (bytes) *bytes = static_cast<int>(kStatusBytes);
+  return 0;
+}
 
 extern "C" int adg_o2_linear_noalloc(const void* a_int8, const void* a_scale, const void* w_mxfp4,
                                      const void* w_sf_tiled, float* y, int M, int N, int K, int ldy, void* stream_v,
@@ -110,6 +152,9 @@ extern "C" int adg_o2_linear_noalloc(const void* a_int8, const void* a_scale, co
                 "); use adg_o2_quantize_activation + adg_gemm_o2 with caller-provided buffers");
   }
   if ((reinterpret_cast<uintptr_t>(w_sf_tiled) & 15u) != 0) return fail("tiled scale buffers must be 16-byte aligned");
+  if (a_int8 == nullptr || a_scale == nullptr || w_mxfp4 == nullptr || y == nullptr) return fail("adg_o2_linear_noalloc: NULL buffer");
+  if ((reinterpret_cast<uintptr_t>(a_int8) & 15u) != 0) return fail("A_int8 must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(a_scale) & 3u) != 0) return fail("A_scale must be 4-byte aligned");
   Setup* s = nullptr;
   if (int rc = setup_current_device(&s)) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
@@ -147,12 +192,5 @@ extern "C" int adg_o2_linear_noalloc(const void* a_int8, const void* a_scale, co
   if (!synchronize) return 0;
 
   if (int rc = check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize")) return rc;
-  uint32_t words[4] = {};
-  if (int rc = check_cuda(cudaMemcpy(words, status, sizeof(words), cudaMemcpyDeviceToHost), "cudaMemcpy(status)")) return rc;
-  if (words[0] != kStatusOk) {
-    check_cuda(cudaMemset(status, 0, kStatusBytes), "cudaMemset(status)");
-    return fail("adg_o2_linear_noalloc: kernel wait timeout: code=" + std::to_string(words[0]) + " tag=" +
-                std::to_string(words[1]) + " block=" + std::to_string(words[2]));
-  }
-  return 0;
+  return read_status(s, "adg_o2_linear_noalloc");
 }

@@ -231,10 +231,16 @@ int plan_o0(GemmPlan* plan, const void* a_fp16, const void* w_fp16, float* y, in
 
 int plan_o1(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale, float* y,
             int32_t* partial_dump, int M, int N, int K, int ldy) {
+  if (int rc = check_shape(M, N, K, ldy)) return rc;
+  if (M <= 64 && partial_dump == nullptr) return plan_o1_skinny(plan, a_int8, a_scale, w_int8, w_scale, y, M, N, K, ldy);
+  return plan_o1_tiled(plan, a_int8, a_scale, w_int8, w_scale, y, partial_dump, M, N, K, ldy);
+}
+
+int plan_o1_tiled(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale,
+                  float* y, int32_t* partial_dump, int M, int N, int K, int ldy) {
   DeviceCtx* ctx = nullptr;
   if (int rc = device_ctx(&ctx)) return rc;
   if (int rc = check_shape(M, N, K, ldy)) return rc;
-  if (M <= 64 && partial_dump == nullptr) return plan_o1_skinny(plan, a_int8, a_scale, w_int8, w_scale, y, M, N, K, ldy);
   *plan = GemmPlan{};
   plan->variant = 1;
   plan->M = M, plan->N = N, plan->K = K, plan->ldy = ldy;
@@ -309,10 +315,95 @@ int plan_o2(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, const vo
   return finish_plan(plan, block_n);
 }
 
+int plan_o1x(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8x, const void* col_factor, float* y,
+             int M, int N, int K, int ldy) {
+  if (int rc = check_shape(M, N, K, ldy)) return rc;
+  if ((reinterpret_cast<uintptr_t>(a_scale) | reinterpret_cast<uintptr_t>(col_factor)) & 3u)
+    return fail("o1x: the factor arrays must be 4-byte aligned");
+  *plan = GemmPlan{};
+  plan->variant = 3;
+  plan->M = M, plan->N = N, plan->K = K, plan->ldy = ldy;
+  plan->a_scale = a_scale;
+  plan->col_factor = col_factor;
+  const int block_n = N > 128 ? 256 : 128;
+  if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_int8, M, K, K, 128, 128)) return rc;
+  if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_int8x, N, K, K, block_n, 128)) return rc;
+  if (int rc = plan_output(plan, y)) return rc;
+  return finish_plan(plan, block_n);
+}
+
+bool fusion_enabled() {
+  const char* e = getenv("ADG_FUSE_A");
+  return !(e != nullptr && e[0] == '0');
+}
+
+namespace {
+int finish_fused(GemmPlan* plan, const void* a_int8, const void* a_scale, void* a_out, void* ready) {
+  if (plan->skinny) return fail("the decode-shape kernels do not convert their activations themselves");
+  if ((reinterpret_cast<uintptr_t>(a_int8) | reinterpret_cast<uintptr_t>(a_out)) & 15u)
+    return fail("A_int8 and the operand workspace must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(a_scale) | reinterpret_cast<uintptr_t>(ready)) & 3u)
+    return fail("A_scale and the row counters must be 4-byte aligned");
+  if (ready == nullptr) return fail("the row counters must not be NULL");
+  plan->fused = 1;
+  plan->fused_a_int8 = a_int8;
+  plan->a_scale = a_scale;
+  plan->fused_a_out = a_out;
+  plan->fused_ready = static_cast<uint32_t*>(ready);
+  return 0;
+}
+}  // namespace
+
+int plan_o0_fused(GemmPlan* plan, const void* a_int8, const void* a_scale, void* a_fp16, const void* w_fp16, float* y,
+                  void* ready, int M, int N, int K, int ldy) {
+  if (int rc = plan_o0(plan, a_fp16, w_fp16, y, M, N, K, ldy)) return rc;
+  return finish_fused(plan, a_int8, a_scale, a_fp16, ready);
+}
+
+int plan_o2_fused(GemmPlan* plan, const void* a_int8, const void* a_scale, void* a_mxfp4, void* sfa_tiled, void* sf_natural,
+                  const void* w_mxfp4, const void* sfb_tiled, float* y, void* ready, int M, int N, int K, int ldy) {
+  if (int rc = plan_o2(plan, a_mxfp4, sfa_tiled, w_mxfp4, sfb_tiled, y, M, N, K, ldy)) return rc;
+  plan->fused_sf_natural = sf_natural;
+  return finish_fused(plan, a_int8, a_scale, a_mxfp4, ready);
+}
+
+// The planner's choice for a shape, without buffers: the same rules as plan_o0 / plan_o1 / plan_o2 above.
+int plan_info(int variant, int flags, int M, int N, int K, PlanInfo* info) {
+  if (info == nullptr) return fail("info must not be NULL");
+  if (variant < 0 || variant > 3) return fail("unknown variant");
+  if (int rc = check_shape(M, N, K, N)) return rc;
+  // the pair rule depends on the SM count: that of the current device, or a B200's 148 without one
+  int sm_count = 148;
+  DeviceCtx* ctx = nullptr;
+  if (device_ctx(&ctx) == 0) sm_count = ctx->sm_count;
+  else set_error("");
+  *info = PlanInfo{};
+  const bool fused = (flags & kPlanFusedActivation) != 0 && M > 64 && (variant == 0 || variant == 2);
+  const int block_n = N > 128 ? 256 : 128;
+  if (variant == 1) {
+    if (M <= 64 && !(flags & kPlanPartialDump)) describe_gemm_o1_skinny(info);
+    else if ((flags & kPlanO1Bf16) && !(flags & kPlanPartialDump)) describe_gemm_o1_bf16(info);
+    else describe_gemm_o1(info);
+    return 0;
+  }
+  if (variant == 3) {
+    describe_gemm_acc(3, block_n, false, info);
+    return 0;
+  }
+  if (variant == 2 && M <= 64) {
+    describe_gemm_o2_skinny(M, info);
+    return 0;
+  }
+  if (pair_enabled(variant, M, N, K, sm_count)) describe_gemm_pair(variant, fused, info);
+  else describe_gemm_acc(variant, block_n, fused, info);
+  return 0;
+}
+
 int run_plan(const GemmPlan& plan, cudaStream_t stream) {
   if (plan.variant == 1 && plan.o1_bf16) return run_gemm_o1_bf16(plan, stream);
   if (plan.variant == 1) return plan.skinny ? run_gemm_o1_skinny(plan, stream) : run_gemm_o1(plan, stream);
   if (plan.skinny) return run_gemm_o2_skinny(plan, stream);
+  if (plan.variant == 3) return run_gemm_acc(plan, stream);
   if (plan.pair) return run_gemm_pair(plan, stream);
   return run_gemm_acc(plan, stream);
 }

@@ -188,15 +188,39 @@ def _output(out, m, n, device):
 
     if out is None:
         out = torch.empty((m, n), dtype=torch.float32, device=device)
+    _require(out.is_cuda and out.device == device, "the output must live on the operands' device")
     _require(out.dtype == torch.float32 and tuple(out.shape) == (m, n) and out.stride(1) == 1, "invalid output tensor")
     return out, int(out.stride(0))
 
 
+def _operand(t, name, dtype, shape=None, device=None):
+    """dtype / device / contiguity / shape check of one GEMM operand (the library sees only pointers)."""
+    _require(t.is_cuda, f"{name} must be a CUDA tensor")
+    _require(t.dtype == dtype, f"{name} must be {dtype}")
+    _require(t.is_contiguous(), f"{name} must be contiguous")
+    if shape is not None:
+        _require(tuple(t.shape) == tuple(shape), f"{name} must have shape {tuple(shape)}, found {tuple(t.shape)}")
+    if device is not None:
+        _require(t.device == device, f"{name} must be on {device}")
+    return t
+
+
+def _tiled(t, name, rows, k, device):
+    import torch
+
+    _operand(t, name, torch.uint8, device=device)
+    _require(t.numel() >= tiled_scale_bytes(rows, k), f"{name} is shorter than the tiled scale layout of {rows} rows x K = {k}")
+    return t
+
+
 def gemm_o0(a_fp16, w_fp16, out=None):
+    import torch
+
     m, k = a_fp16.shape
     n = w_fp16.shape[0]
+    _operand(a_fp16, "A_fp16", torch.float16)
+    _operand(w_fp16, "W_fp16", torch.float16, (n, k), a_fp16.device)
     out, ldy = _output(out, m, n, a_fp16.device)
-    import torch
 
     with torch.cuda.device(a_fp16.device):
         _sm100._check(_lib().adg_gemm_o0(a_fp16.data_ptr(), w_fp16.data_ptr(), out.data_ptr(), m, n, k, ldy, _stream(out)))
@@ -208,6 +232,11 @@ def gemm_o1(a_int8, a_scale, w_int8, w_scale, out=None, dump_partials=False):
 
     m, k = a_int8.shape
     n = w_int8.shape[0]
+    dev = a_int8.device
+    _operand(a_int8, "A_int8", torch.int8)
+    _operand(a_scale, "A_scale", torch.float32, (m,), dev)
+    _operand(w_int8, "W_int8", torch.int8, (n, k), dev)
+    _operand(w_scale, "W_scale", torch.uint8, (n, k // 32), dev)
     out, ldy = _output(out, m, n, a_int8.device)
     partials = torch.empty((m, n, k // 32), dtype=torch.int32, device=a_int8.device) if dump_partials else None
     with torch.cuda.device(a_int8.device):
@@ -220,8 +249,15 @@ def gemm_o1(a_int8, a_scale, w_int8, w_scale, out=None, dump_partials=False):
 def gemm_o1_bf16(a_bf16, a_scale, w_bf16, range_flag, out=None):
     """O1 on BF16 operands (same bits as :func:`gemm_o1` while ``range_flag`` stays zero; otherwise the
     kernel refuses and the next status check raises)."""
+    import torch
+
     m, k = a_bf16.shape
     n = w_bf16.shape[0]
+    dev = a_bf16.device
+    _operand(a_bf16, "A_bf16", torch.bfloat16)
+    _operand(a_scale, "A_scale", torch.float32, (m,), dev)
+    _operand(w_bf16, "W_bf16", torch.bfloat16, (n, k), dev)
+    _operand(range_flag, "range_flag", torch.int32, device=dev)
     out, ldy = _output(out, m, n, a_bf16.device)
     with torch_device(a_bf16.device):
         _sm100._check(_lib().adg_gemm_o1_bf16(
@@ -254,8 +290,14 @@ class O1Weights:
 def o1_linear(a_int8, a_scale, weights: O1Weights, out=None):
     """O1 for every input without a host synchronisation: the BF16-operand kernel, and behind it the
     INT8-operand kernel, which runs only if the first one refused (``adg_o1_linear``)."""
+    import torch
+
     m, k = a_int8.shape
     n = weights.w_int8.shape[0]
+    dev = a_int8.device
+    _operand(a_int8, "A_int8", torch.int8)
+    _operand(a_scale, "A_scale", torch.float32, (m,), dev)
+    _require(tuple(weights.w_int8.shape) == (n, k) and weights.w_int8.device == dev, "weights do not match A")
     out, ldy = _output(out, m, n, a_int8.device)
     ws = weights.workspace(m, k)
     with torch_device(a_int8.device):
@@ -270,6 +312,11 @@ def gemm_o2(a_mxfp4, a_sf_tiled, w_mxfp4, w_sf_tiled, out=None):
 
     m, kh = a_mxfp4.shape
     n = w_mxfp4.shape[0]
+    dev = a_mxfp4.device
+    _operand(a_mxfp4, "A_mxfp4", torch.uint8)
+    _operand(w_mxfp4, "W_mxfp4", torch.uint8, (n, kh), dev)
+    _tiled(a_sf_tiled, "a_sf_tiled", m, kh * 2, dev)
+    _tiled(w_sf_tiled, "w_sf_tiled", n, kh * 2, dev)
     out, ldy = _output(out, m, n, a_mxfp4.device)
     with torch.cuda.device(a_mxfp4.device):
         _sm100._check(_lib().adg_gemm_o2(
@@ -287,12 +334,137 @@ def o2_linear_noalloc(a_int8, a_scale, w_mxfp4, w_sf_tiled, out, synchronize=Tru
 
     m, k = a_int8.shape
     n = w_mxfp4.shape[0]
-    _require(out is not None and out.dtype == torch.float32 and tuple(out.shape) == (m, n) and out.stride(1) == 1,
-             "invalid output tensor")
+    dev = a_int8.device
+    _operand(a_int8, "A_int8", torch.int8)
+    _operand(a_scale, "A_scale", torch.float32, (m,), dev)
+    _operand(w_mxfp4, "W_mxfp4", torch.uint8, (n, k // 2), dev)
+    _tiled(w_sf_tiled, "w_sf_tiled", n, k, dev)
+    _require(out is not None and out.is_cuda and out.device == dev and out.dtype == torch.float32
+             and tuple(out.shape) == (m, n) and out.stride(1) == 1, "invalid output tensor")
     with torch.cuda.device(a_int8.device):
         _sm100._check(_lib().adg_o2_linear_noalloc(
             a_int8.data_ptr(), a_scale.data_ptr(), w_mxfp4.data_ptr(), w_sf_tiled.data_ptr(), out.data_ptr(),
             m, n, k, int(out.stride(0)), _stream(out), 1 if synchronize else 0))
+    return out
+
+
+def o2_linear_noalloc_status(device=None):
+    """Status of earlier ``o2_linear_noalloc(..., synchronize=False)`` calls; allocates nothing."""
+    import torch
+
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    with torch.cuda.device(dev):
+        _sm100._check(_lib().adg_o2_linear_noalloc_status(torch.cuda.current_stream(dev).cuda_stream))
+
+
+class FusedWorkspace:
+    """Buffers of the one-kernel steady-state passes :func:`o0_linear` / :func:`o2_linear` for up to
+    ``max_m`` rows of K elements: the converted operand, O2's tiled scales and the row counters (zeroed
+    once here; the kernels leave them zero)."""
+
+    def __init__(self, variant: str, max_m: int, k: int, device, want_natural_scales: bool = False):
+        import torch
+
+        _require(variant in ("o0", "o2"), "fused passes exist for o0 and o2")
+        self.variant, self.max_m, self.k = variant, max_m, k
+        self.counters = torch.zeros((int(_lib().adg_fused_workspace_bytes(max_m)) // 4,), dtype=torch.int32, device=device)
+        if variant == "o0":
+            self.operand = torch.empty((max_m, k), dtype=torch.float16, device=device)
+            self.sf_tiled = self.sf_natural = None
+        else:
+            self.operand = torch.empty((max_m, k // 2), dtype=torch.uint8, device=device)
+            self.sf_tiled = torch.zeros((tiled_scale_bytes(max_m, k),), dtype=torch.uint8, device=device)
+            self.sf_natural = torch.empty((max_m, k // 32), dtype=torch.uint8, device=device) if want_natural_scales else None
+
+
+def o0_linear(a_int8, a_scale, w_fp16, workspace: FusedWorkspace, out=None):
+    """O0 steady-state pass (INT8 -> FP16 conversion inside the GEMM kernel for M > 64): ``adg_o0_linear``."""
+    import torch
+
+    m, k = a_int8.shape
+    n = w_fp16.shape[0]
+    dev = a_int8.device
+    _operand(a_int8, "A_int8", torch.int8)
+    _operand(a_scale, "A_scale", torch.float32, (m,), dev)
+    _operand(w_fp16, "W_fp16", torch.float16, (n, k), dev)
+    _require(workspace.variant == "o0" and workspace.k == k and m <= workspace.max_m, "workspace does not fit this call")
+    out, ldy = _output(out, m, n, dev)
+    with torch.cuda.device(dev):
+        _sm100._check(_lib().adg_o0_linear(a_int8.data_ptr(), a_scale.data_ptr(), w_fp16.data_ptr(), workspace.operand.data_ptr(),
+                                           workspace.counters.data_ptr(), out.data_ptr(), m, n, k, ldy, _stream(out)))
+    return out
+
+
+def o2_linear(a_int8, a_scale, w_mxfp4, w_sf_tiled, workspace: FusedWorkspace, out=None):
+    """O2 steady-state pass (re-quantization inside the GEMM kernel for M > 64): ``adg_o2_linear``."""
+    import torch
+
+    m, k = a_int8.shape
+    n = w_mxfp4.shape[0]
+    dev = a_int8.device
+    _operand(a_int8, "A_int8", torch.int8)
+    _operand(a_scale, "A_scale", torch.float32, (m,), dev)
+    _operand(w_mxfp4, "W_mxfp4", torch.uint8, (n, k // 2), dev)
+    _tiled(w_sf_tiled, "w_sf_tiled", n, k, dev)
+    _require(workspace.variant == "o2" and workspace.k == k and m <= workspace.max_m, "workspace does not fit this call")
+    out, ldy = _output(out, m, n, dev)
+    nat = workspace.sf_natural
+    with torch.cuda.device(dev):
+        _sm100._check(_lib().adg_o2_linear(
+            a_int8.data_ptr(), a_scale.data_ptr(), w_mxfp4.data_ptr(), w_sf_tiled.data_ptr(), workspace.operand.data_ptr(),
+            workspace.sf_tiled.data_ptr(), nat.data_ptr() if nat is not None else None, workspace.counters.data_ptr(),
+            out.data_ptr(), m, n, k, ldy, _stream(out)))
+    return out
+
+
+class O1xWeights:
+    """W prepared for the exact-integer O1 variant: the row-shifted INT8 image, one factor per W row, the
+    list of column blocks that must take the literal path, and the literal path's own INT8 image."""
+
+    def __init__(self, w_mxfp4, w_scale):
+        import torch
+
+        n, kh = w_mxfp4.shape
+        k = kh * 2
+        dev = w_mxfp4.device
+        _operand(w_mxfp4, "W_mxfp4", torch.uint8)
+        _operand(w_scale, "W_scale", torch.uint8, (n, k // 32), dev)
+        self.n, self.k = n, k
+        self.w_scale = w_scale
+        self.w_int8 = mxfp4_to_int8(w_mxfp4)
+        self.w_int8x = torch.empty((n, k), dtype=torch.int8, device=dev)
+        self.col_factor = torch.empty((n,), dtype=torch.float32, device=dev)
+        self.workspace = torch.zeros(((int(_lib().adg_o1x_workspace_bytes(n)) + 15) // 16 * 4,), dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            _sm100._check(_lib().adg_o1x_prepare_weight(
+                w_mxfp4.data_ptr(), w_scale.data_ptr(), self.w_int8x.data_ptr(), self.col_factor.data_ptr(),
+                self.workspace.data_ptr(), n, k, _stream(w_mxfp4)))
+
+    def ineligible_rows(self) -> int:
+        """Number of W rows (output columns) whose scale-code spread exceeds 3 (synchronises)."""
+        import torch
+
+        rows = ctypes.c_int64(0)
+        with torch.cuda.device(self.w_int8.device):
+            _sm100._check(_lib().adg_o1x_ineligible_rows(self.workspace.data_ptr(), _stream(self.w_int8), ctypes.byref(rows)))
+        return int(rows.value)
+
+
+def gemm_o1x(a_int8, a_scale, weights: O1xWeights, out=None):
+    """The exact-integer O1 variant (``adg_gemm_o1x``): NOT the O1 recurrence; see the header."""
+    import torch
+
+    m, k = a_int8.shape
+    dev = a_int8.device
+    _operand(a_int8, "A_int8", torch.int8)
+    _operand(a_scale, "A_scale", torch.float32, (m,), dev)
+    _require(k == weights.k and weights.w_int8.device == dev, "weights do not match A")
+    out, ldy = _output(out, m, weights.n, dev)
+    with torch.cuda.device(dev):
+        _sm100._check(_lib().adg_gemm_o1x(
+            a_int8.data_ptr(), a_scale.data_ptr(), weights.w_int8x.data_ptr(), weights.col_factor.data_ptr(),
+            weights.workspace.data_ptr(), weights.w_int8.data_ptr(), weights.w_scale.data_ptr(), out.data_ptr(),
+            m, weights.n, k, ldy, _stream(out)))
     return out
 
 

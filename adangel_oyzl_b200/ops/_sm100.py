@@ -13,14 +13,15 @@ import os
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_uint32, c_void_p
 from pathlib import Path
 
-# ADANGEL_B200_LIB points the package at an instrumented build of the library (see build.py --define)
-_LIB_PATH = Path(os.environ["ADANGEL_B200_LIB"]).resolve() if os.environ.get("ADANGEL_B200_LIB") else (
-    Path(__file__).resolve().parents[1] / "lib" / "libadangel_b200.so")
+_LIB_PATH = Path(__file__).resolve().parents[1] / "lib" / "libadangel_b200.so"
 _lib = None
 
 DEFAULT_CONVERSION_INNER_REPEATS = 100  # include/adangel/kernel_api.h:9 of the reference
 _MODES = {"conversion_only": 0, "compute_only": 1, "cold": 2, "steady_state": 3}
-_VARIANTS = {"o0": 0, "o1": 1, "o2": 2}
+_VARIANTS = {"o0": 0, "o1": 1, "o2": 2, "o1x": 3}  # o1x: the exact-integer O1 variant, only ever by name
+BENCH_FUSE_ACTIVATION = 1
+BENCH_O1_SPLIT_ACTIVATION = 2
+PLAN_O1_BF16, PLAN_FUSED_ACTIVATION, PLAN_PARTIAL_DUMP = 1, 2, 4
 _STAGE_BITS = (("weight_conversion", 1), ("activation_conversion", 2), ("gemm", 4), ("total", 8))
 
 
@@ -38,6 +39,19 @@ class BenchArgs(ctypes.Structure):
         ("t_gemm", POINTER(c_float)), ("t_total", POINTER(c_float)),
         ("stages_out", c_uint32), ("stream", c_void_p),
         ("conv_weight_bf16", c_void_p), ("conv_act_bf16", c_void_p), ("range_flag", c_void_p),
+        ("flags", c_uint32), ("row_counters", c_void_p),
+        ("o1x_col_factor", c_void_p), ("o1x_workspace", c_void_p), ("o1x_w_int8", c_void_p),
+    ]
+
+
+class PlanDesc(ctypes.Structure):
+    """``adg_plan_desc`` of include/adangel_b200.h."""
+
+    _fields_ = [
+        ("tile_m", c_int32), ("tile_n", c_int32), ("stages", c_int32), ("accumulator_stages", c_int32),
+        ("threads", c_int32), ("cluster", c_int32), ("mma_m", c_int32), ("mma_n", c_int32), ("mma_k", c_int32),
+        ("persistent", c_int32), ("fused_activation", c_int32),
+        ("kernel_symbol", ctypes.c_char * 64), ("mma_family", ctypes.c_char * 96),
     ]
 
 
@@ -47,6 +61,16 @@ _SIGNATURES = {
     "adg_capabilities": (c_uint32, []),
     "adg_device_info": (c_int, [c_char_p, c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
     "adg_check_status": (c_int, [c_void_p]),
+    "adg_plan_info": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(PlanDesc)]),
+    "adg_fused_workspace_bytes": (c_int64, [c_int64]),
+    "adg_o0_linear": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_void_p]),
+    "adg_o2_linear": (c_int, [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_void_p]),
+    "adg_o1x_workspace_bytes": (c_int64, [c_int64]),
+    "adg_o1x_prepare_weight": (c_int, [c_void_p] * 5 + [c_int64, c_int64, c_void_p]),
+    "adg_o1x_ineligible_rows": (c_int, [c_void_p, c_void_p, POINTER(c_int64)]),
+    "adg_gemm_o1x": (c_int, [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_void_p]),
+    "adg_o2_linear_noalloc_status": (c_int, [c_void_p]),
+    "adg_o2_linear_noalloc_status_words": (c_int, [POINTER(c_void_p), POINTER(c_int)]),
     "adg_mxfp4_to_fp16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "adg_int8_to_fp16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "adg_mxfp4_to_int8": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
@@ -164,9 +188,30 @@ def _timing_metadata(mode: str, inner: int) -> dict:
     }
 
 
-def kernel_metadata(variant: str, m: int, n: int, k: int, o1_bf16: bool = False) -> dict:
-    block_n = 128 if variant == "o1" or n <= 128 else 256
-    common = {
+def plan_info(variant: str, m: int, n: int, k: int, o1_bf16: bool = False, fused: bool = False,
+              partial_dump: bool = False) -> dict:
+    """The planner's choice for a shape, asked of the library (``adg_plan_info``); needs a device."""
+    desc = PlanDesc()
+    flags = (PLAN_O1_BF16 if o1_bf16 else 0) | (PLAN_FUSED_ACTIVATION if fused else 0) | (PLAN_PARTIAL_DUMP if partial_dump else 0)
+    _check(library().adg_plan_info(_VARIANTS[variant], flags, m, n, k, ctypes.byref(desc)))
+    return {
+        "kernel_symbol": desc.kernel_symbol.decode(),
+        "mma_family": desc.mma_family.decode(),
+        "tile": [desc.tile_m, desc.tile_n],
+        "stages": desc.stages,
+        "accumulator_stages": desc.accumulator_stages,
+        "threads": desc.threads,
+        "cluster": [desc.cluster, 1, 1],
+        "mma_shape": [desc.mma_m, desc.mma_n, desc.mma_k],
+        "persistent": bool(desc.persistent),
+        "fused_activation_conversion": bool(desc.fused_activation),
+    }
+
+
+def kernel_metadata(variant: str, m: int, n: int, k: int, o1_bf16: bool = False, fused: bool = False) -> dict:
+    """The ``kernel`` dictionary of a result (the reference builds its own by hand per variant,
+    csrc/sm120/o0_gemm.cu:300-328): constant facts plus the planner's choice from :func:`plan_info`."""
+    meta = {
         "library": "hand-written sm_100a (no CUTLASS, no cuBLAS)",
         "tensor_core": True,
         "data_movement": "TMA",
@@ -174,70 +219,33 @@ def kernel_metadata(variant: str, m: int, n: int, k: int, o1_bf16: bool = False)
         "global_partial_buffer": False,
         "output_stores_per_element": 1,
         "group_size": 32,
-        "tile": [128, block_n],
-        "persistent": True,
     }
-    # the planner's rule for CTA pairs (csrc/runtime.cu, pair_enabled; 148 SMs = 74 clusters)
-    row_blocks = (m + 127) // 128
-    pair_tiles = ((m + 255) // 256) * ((n + 255) // 256)
-    switch = os.environ.get("ADG_TWO_CTA", "")[:1]
-    if m < 256 or n < 256 or switch == "0":
-        pair = False
-    elif switch == "1":
-        pair = True
-    elif row_blocks % 2 != 0 and row_blocks < 33:
-        pair = False
-    elif variant == "o0":
-        pair = pair_tiles >= 2 * 74 and k >= 2048
-    else:
-        pair = pair_tiles >= 7 * 74 and k >= 4096
-    if variant == "o0" and pair:
-        common.update(mma_family="tcgen05.mma.cta_group::2.kind::f16", kernel_symbol="gemm_pair_kernel<0>",
-                      stages=6, accumulator_stages=2, threads=384, tile=[256, 256], cluster=[2, 1, 1],
-                      mma_shape=[256, 256, 16])
-    elif variant == "o0":
-        common.update(mma_family="tcgen05.mma.cta_group::1.kind::f16", kernel_symbol="gemm_acc_kernel<0>",
-                      stages=4 if block_n == 256 else 6, accumulator_stages=2, threads=384,
-                      mma_shape=[128, block_n, 16])
-    elif variant == "o1" and m <= 64:
-        # decode shapes: operands swapped, one CTA per 128 W rows x 16 A rows, K walked in order
-        common.update(mma_family="tcgen05.mma.cta_group::1.kind::i8", kernel_symbol="gemm_o1_skinny_kernel",
-                      stages=8, threads=384, tile=[16, 128], persistent=False, mma_shape=[128, 16, 32],
-                      partial_rescale="per-K32, FP32 registers",
-                      accumulator="INT32 partial in tensor memory, FP32 accumulate in registers")
-    elif variant == "o1" and o1_bf16:
-        # weight scale folded into a BF16 operand: the partial leaves the tensor core as float(P) * 2^(s-128)
-        common.update(mma_family="tcgen05.mma.cta_group::1.kind::f16 (bf16 operands; exact integer partials)",
-                      kernel_symbol="gemm_o1_bf16_kernel", stages=6, threads=640, mma_shape=[128, 128, 16],
-                      partial_rescale="per-K32, FP32 registers",
-                      accumulator="FP32 partial in tensor memory (four 128-column buffers), FP32 accumulate in registers")
-    elif variant == "o1":
-        common.update(mma_family="tcgen05.mma.cta_group::1.kind::i8", kernel_symbol="gemm_o1_kernel",
-                      stages=6, scale_stages=8, threads=640, mma_shape=[128, 128, 32],
-                      partial_rescale="per-K32, FP32 registers",
-                      accumulator="INT32 partial in tensor memory, FP32 accumulate in registers")
-    elif m <= 64:
-        # decode shapes: operands swapped, W rows are the MMA M dimension
-        m_pad = (m + 15) // 16 * 16
-        common.update(mma_family="tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32",
-                      kernel_symbol="gemm_o2_skinny_kernel", stages=4, threads=192, tile=[m_pad, 128],
-                      persistent=False, mma_shape=[128, m_pad, 64], scale_format="UE8M0", weight_copy=False)
-    elif pair:
-        common.update(mma_family="tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32",
-                      kernel_symbol="gemm_pair_kernel<2>", stages=5, accumulator_stages=1, threads=384,
-                      tile=[256, 256], cluster=[2, 1, 1], mma_shape=[256, 256, 64], scale_format="UE8M0",
-                      weight_copy=False)
-    else:
-        common.update(mma_family="tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32",
-                      kernel_symbol="gemm_acc_kernel<2>", stages=4 if block_n == 256 else 6,
-                      accumulator_stages=1 if block_n == 256 else 2, threads=384,
-                      mma_shape=[128, block_n, 64], scale_format="UE8M0", weight_copy=False)
-    return common
+    meta.update(plan_info(variant, m, n, k, o1_bf16=o1_bf16, fused=fused))
+    if variant == "o1":
+        meta["partial_rescale"] = "per-K32, FP32 registers"
+        meta["accumulator"] = ("FP32 partial in tensor memory, FP32 accumulate in registers" if o1_bf16 and m > 64
+                               else "INT32 partial in tensor memory, FP32 accumulate in registers")
+    elif variant == "o1x":
+        meta["partial_rescale"] = "none: INT32 accumulation over all of K, one scaling per output element"
+        meta["accumulator"] = "INT32 in tensor memory"
+    elif variant == "o2":
+        meta["scale_format"] = "UE8M0"
+        meta["weight_copy"] = False
+    return meta
 
 
 def benchmark(variant, mode, a_int8, a_scale, w_mxfp4, w_scale, warmup, repeats,
-              conversion_inner_repeats=DEFAULT_CONVERSION_INNER_REPEATS):
-    """One variant/mode under the reference's timing protocol (``adangel_benchmark_o{0,1,2}``)."""
+              conversion_inner_repeats=DEFAULT_CONVERSION_INNER_REPEATS, *, fuse_activation=True,
+              o1_split_activation_stage=False):
+    """One variant/mode under the reference's timing protocol (``adangel_benchmark_o{0,1,2}``).
+
+    The positional signature is the reference's.  Keyword-only additions: ``fuse_activation`` (O0/O2, cold and
+    steady-state modes, M > 64: the activation conversion runs inside the GEMM kernel, so the ``gemm`` stage is
+    that one kernel and ``activation_conversion`` is reported from its isolated batches only);
+    ``o1_split_activation_stage`` (O1 on BF16 operands: report the INT8 -> BF16 conversion as an
+    ``activation_conversion`` stage instead of inside ``gemm``; off by default because the reference's O1 has
+    no such stage).  ``variant="o1x"`` runs the exact-integer O1 variant; its result carries
+    ``o1x_ineligible_rows``."""
     import torch
 
     lib = library()
@@ -268,7 +276,16 @@ def benchmark(variant, mode, a_int8, a_scale, w_mxfp4, w_scale, warmup, repeats,
     output = empty((m, n), torch.float32)
     conv_weight = conv_act = conv_act_sf = conv_act_sf_tiled = None
     conv_weight_bf16 = conv_act_bf16 = range_flag = None
-    if variant == "o0":
+    row_counters = o1x_col_factor = o1x_workspace = o1x_w_int8 = None
+    fused = bool(fuse_activation) and variant in ("o0", "o2") and m > 64 and mode in ("cold", "steady_state")
+    if fused:
+        row_counters = torch.zeros((lib.adg_fused_workspace_bytes(m) // 4,), dtype=torch.int32, device=device)
+    if variant == "o1x":
+        conv_weight = empty((n, k), torch.int8)
+        o1x_w_int8 = empty((n, k), torch.int8)
+        o1x_col_factor = empty((n,), torch.float32)
+        o1x_workspace = torch.zeros(((lib.adg_o1x_workspace_bytes(n) + 15) // 16 * 4,), dtype=torch.int32, device=device)
+    elif variant == "o0":
         conv_weight = empty((n, k), torch.float16)
         conv_act = empty((m, k), torch.float16)
     elif variant == "o1":
@@ -299,6 +316,11 @@ def benchmark(variant, mode, a_int8, a_scale, w_mxfp4, w_scale, warmup, repeats,
     args.conv_weight_bf16 = conv_weight_bf16.data_ptr() if conv_weight_bf16 is not None else None
     args.conv_act_bf16 = conv_act_bf16.data_ptr() if conv_act_bf16 is not None else None
     args.range_flag = range_flag.data_ptr() if range_flag is not None else None
+    args.flags = (BENCH_FUSE_ACTIVATION if fused else 0) | (BENCH_O1_SPLIT_ACTIVATION if o1_split_activation_stage else 0)
+    args.row_counters = row_counters.data_ptr() if row_counters is not None else None
+    args.o1x_col_factor = o1x_col_factor.data_ptr() if o1x_col_factor is not None else None
+    args.o1x_workspace = o1x_workspace.data_ptr() if o1x_workspace is not None else None
+    args.o1x_w_int8 = o1x_w_int8.data_ptr() if o1x_w_int8 is not None else None
     args.t_weight = ctypes.cast(times["weight_conversion"], POINTER(c_float))
     args.t_activation = ctypes.cast(times["activation_conversion"], POINTER(c_float))
     args.t_gemm = ctypes.cast(times["gemm"], POINTER(c_float))
@@ -310,17 +332,25 @@ def benchmark(variant, mode, a_int8, a_scale, w_mxfp4, w_scale, warmup, repeats,
     timings = {name: list(times[name]) for name, bit in _STAGE_BITS if args.stages_out & bit}
     if variant == "o0":
         converted_weight, converted_activation = conv_weight, conv_act
-    elif variant == "o1":
+    elif variant in ("o1", "o1x"):
         converted_weight, converted_activation = conv_weight, None
     else:
         converted_weight, converted_activation = None, (conv_act, conv_act_sf)
+    extra = {}
+    if variant == "o1x":
+        rows = c_int64(0)
+        with torch.cuda.device(device):
+            _check(lib.adg_o1x_ineligible_rows(o1x_workspace.data_ptr(), args.stream, ctypes.byref(rows)))
+        extra = {"o1x_ineligible_rows": int(rows.value), "o1x_column_factor": o1x_col_factor}
     return {
+        **extra,
         "output": output,
         "converted_weight": converted_weight,
         "converted_activation": converted_activation,
         "timings_ms": timings,
         "timing_method": _timing_metadata(mode, conversion_inner_repeats),
-        "kernel": kernel_metadata(variant, m, n, k, o1_bf16=range_flag is not None and int(range_flag.item()) == 0),
+        "kernel": kernel_metadata(variant, m, n, k, o1_bf16=range_flag is not None and int(range_flag.item()) == 0,
+                                  fused=fused),
     }
 
 
@@ -345,6 +375,11 @@ def run_o1(a_int8, a_scale, w_mxfp4, w_scale, mode):
 
 def run_o2(a_int8, a_scale, w_mxfp4, w_scale, mode):
     return _run("o2", a_int8, a_scale, w_mxfp4, w_scale, mode)
+
+
+def run_o1x(a_int8, a_scale, w_mxfp4, w_scale, mode):
+    """The exact-integer O1 variant (no reference counterpart; see ``adg_gemm_o1x``)."""
+    return _run("o1x", a_int8, a_scale, w_mxfp4, w_scale, mode)
 
 
 def verify_layout() -> dict:

@@ -97,6 +97,7 @@ def require_variant(variant: str):
         "o0": ("o0_fp16_tc",),
         "o1": ("o1_int8_tc",),
         "o2": ("o2_mxf4_block_scale", "o2_cutlass_tiled"),
+        "o1x": ("o1_int8_tc",),  # the exact-integer O1 variant of this build; only ever requested by name
     }
     if variant not in required:
         raise ValueError(f"unknown variant: {variant}")

@@ -50,8 +50,24 @@ uint32_t adg_capabilities(void);
 int adg_device_info(char* name, int name_len, int* cc_major, int* cc_minor, int* sm_count);
 
 /* Waits for the work enqueued on `stream`, then reads and clears the device status words written
- * by kernels whose bounded waits gave up; fails with a description if one did. */
+ * by kernels whose bounded waits gave up; fails with a description if one did.  Also covers the status
+ * words of asynchronous adg_o2_linear_noalloc calls (see there). */
 int adg_check_status(void* stream);
+
+/* What the planner runs for a shape: kernel, tile, pipeline depth.  Replaces the `kernel` metadata
+ * dictionary the reference's benchmark functions build by hand (csrc/sm120/o0_gemm.cu:300-328,
+ * o1_gemm.cu:395-429, o2_cutlass.cu:320-362).  variant: 0 = O0, 1 = O1, 2 = O2, 3 = o1x.  The rules depend on
+ * the SM count: the current device's, or a B200's 148 when no device is usable. */
+#define ADG_PLAN_O1_BF16 1u          /* O1 on BF16 operands (adg_gemm_o1_bf16 / adg_o1_linear) */
+#define ADG_PLAN_FUSED_ACTIVATION 2u /* O0 / O2 through adg_o0_linear / adg_o2_linear */
+#define ADG_PLAN_PARTIAL_DUMP 4u     /* O1 with the INT32 partial dump */
+typedef struct adg_plan_desc {
+  int32_t tile_m, tile_n, stages, accumulator_stages, threads, cluster;
+  int32_t mma_m, mma_n, mma_k, persistent, fused_activation;
+  char kernel_symbol[64];
+  char mma_family[96];
+} adg_plan_desc;
+int adg_plan_info(int variant, int flags, int M, int N, int K, adg_plan_desc* out);
 
 /* ---- conversion kernels (device pointers) -------------------------------------------------- */
 
@@ -156,6 +172,46 @@ int adg_o1_linear(const void* a_int8, const void* a_scale, const void* w_int8, c
 int adg_gemm_o2(const void* a_mxfp4, const void* a_sf_tiled, const void* w_mxfp4, const void* w_sf_tiled, float* y,
                 int M, int N, int K, int ldy, void* stream);
 
+/* O0 / O2 steady-state pass in one call: activation conversion + GEMM.  For M > 64 the conversion runs
+ * INSIDE the GEMM kernel: a fourth warp group of every CTA converts rows of A_int8 into the operand buffer
+ * (FP16, or MXFP4 codes + tiled scales) while the tensor cores work, and the kernel's TMA producer waits on
+ * per-row-block counters before it loads a row block -- the conversion kernel that the reference launches in
+ * front of every GEMM (csrc/sm120/o0_gemm.cu:432-470, o2_cutlass.cu:451-472) leaves the critical path and
+ * the results are bit-identical to the two-kernel sequence.  For M <= 64, with row_counters == NULL, or with
+ * ADG_FUSE_A=0 in the environment, the two kernels run one after the other.
+ *   - a_fp16_workspace [M,K] FP16 / a_mxfp4_workspace [M,K/2] + a_sf_tiled_workspace
+ *     (adg_o2_tiled_scale_bytes(M,K), zero-filled once by the caller) receive the converted operand;
+ *     a_sf_natural ([M,K/32], may be NULL) the natural-layout scales.
+ *   - row_counters: adg_fused_workspace_bytes(M) bytes, zero-filled once by the caller; the kernel leaves
+ *     them zero again.  After a call that reported a device-side error, zero them before the next call.
+ *     Calls that share counters or workspaces must not overlap on the GPU. */
+int64_t adg_fused_workspace_bytes(int64_t M);
+int adg_o0_linear(const void* a_int8, const void* a_scale, const void* w_fp16, void* a_fp16_workspace, void* row_counters,
+                  float* y, int M, int N, int K, int ldy, void* stream);
+int adg_o2_linear(const void* a_int8, const void* a_scale, const void* w_mxfp4, const void* w_sf_tiled, void* a_mxfp4_workspace,
+                  void* a_sf_tiled_workspace, void* a_sf_natural, void* row_counters, float* y, int M, int N, int K, int ldy,
+                  void* stream);
+
+/* ---- o1x: the exact-integer variant of O1 (no reference counterpart; never selected on a caller's behalf) ----
+ * The literal O1 (adg_gemm_o1, reference csrc/sm120/o1_gemm.cu:298-316) rounds twice per K32 group, which
+ * keeps every INT32 partial on the FP32 pipe.  Where the scale codes of a W row differ by at most 3, the row
+ * is rewritten as INT8 with one exponent, W'[n,k] = 2*e2m1 << (code[n,g] - min_g code[n,.]) (|W'| <= 96), and
+ *     y[m,n] = RN(float_rn(sum_k A_int8[m,k] * W'[n,k]) * RN(A_scale[m] * 2^(mincode[n]-128)))
+ * with the INT32 sum exact over all of K (tcgen05 kind::i8, accumulator in tensor memory): two roundings in
+ * total.  128-column blocks of Y that contain a row with a larger spread (blocks of all-zero nibbles do not
+ * count) are computed by the literal kernel instead, on a device-side list, without a host round trip.
+ *   adg_o1x_prepare_weight: once per weight; writes w_int8x [N,K] INT8, col_factor [N] FP32 and `workspace`
+ *     (adg_o1x_workspace_bytes(N): ineligible-row count, block flags, block list).
+ *   adg_o1x_ineligible_rows: synchronises and returns the number of W rows that take the literal path.
+ *   adg_gemm_o1x: the GEMM; w_int8 (adg_mxfp4_to_int8) and w_scale serve the literal path and may be NULL
+ *     only if no row is ineligible. */
+int64_t adg_o1x_workspace_bytes(int64_t N);
+int adg_o1x_prepare_weight(const void* w_mxfp4, const void* w_scale, void* w_int8x, void* col_factor, void* workspace,
+                           int64_t N, int64_t K, void* stream);
+int adg_o1x_ineligible_rows(const void* workspace, void* stream, int64_t* rows);
+int adg_gemm_o1x(const void* a_int8, const void* a_scale, const void* w_int8x, const void* col_factor, const void* workspace,
+                 const void* w_int8, const void* w_scale, float* y, int M, int N, int K, int ldy, void* stream);
+
 /* O2 without device allocations: Y = requantize(A) @ W^T in one call, for callers that cannot
  * allocate (a server whose memory pool already owns all of the GPU's memory, or a latency-critical
  * loop that must avoid the device-wide synchronisation of cudaMalloc/cudaFree).  The packed codes
@@ -166,14 +222,28 @@ int adg_gemm_o2(const void* a_mxfp4, const void* a_sf_tiled, const void* w_mxfp4
  *     1024 x 8192 or 512 x 16384); larger activations are rejected with an error.
  *   - w_sf_tiled is W's scales in tiled form (adg_o2_tile_scales, done once per weight).
  *   - The first call on a device performs one-time set-up (address look-up of the array, kernel
- *     attributes); make that first call before starting any stream capture.
+ *     attributes); make that first call before starting any stream capture -- and before the caller's
+ *     pool takes the rest of the device's memory: the array itself comes into being when the CUDA runtime
+ *     loads this library's kernels onto the device, which happens no later than that first call.
  *   - All calls share the one array: two calls that overlap on the GPU (different streams, or
  *     different host threads) race on it.  Issue them on one stream or order them yourself.
  *   - synchronize != 0: wait for the result and report a kernel wait timeout as an error;
- *     synchronize == 0: return after enqueueing.
+ *     synchronize == 0: return after enqueueing; a timeout is then reported by the next
+ *     adg_o2_linear_noalloc_status (or adg_check_status) call.
  * It calls no cudaMalloc/cudaFree and no allocating library routine. */
 int adg_o2_linear_noalloc(const void* a_int8, const void* a_scale, const void* w_mxfp4, const void* w_sf_tiled,
                           float* y, int M, int N, int K, int ldy, void* stream, int synchronize);
+
+/* Status of earlier asynchronous adg_o2_linear_noalloc calls: waits for `stream`, reads the status words
+ * that those calls' kernels keep inside the built-in array, clears them if set and fails with a
+ * description.  Allocates nothing (unlike adg_check_status, whose first use on a device allocates the
+ * regular path's status words).  Returns 0 when adg_o2_linear_noalloc has not been used on this device.
+ * No counterpart in the reference. */
+int adg_o2_linear_noalloc_status(void* stream);
+
+/* For tests and tools: device address and size in bytes of the status words read by
+ * adg_o2_linear_noalloc_status (performs the one-time set-up if needed). */
+int adg_o2_linear_noalloc_status_words(void** device_address, int* bytes);
 
 /* ---- timing harness -------------------------------------------------------------------------- */
 
@@ -218,7 +288,22 @@ typedef struct adg_bench_args {
   void* conv_weight_bf16;
   void* conv_act_bf16;
   void* range_flag;
+  /* ABI 102 */
+  uint32_t flags;      /* ADG_BENCH_* */
+  void* row_counters;  /* O0 / O2 with ADG_BENCH_FUSE_ACTIVATION: adg_fused_workspace_bytes(M), zero-filled */
+  /* variant 3 (o1x): conv_weight is the shifted INT8 image [N,K]; plus */
+  void* o1x_col_factor; /* float [N] */
+  void* o1x_workspace;  /* adg_o1x_workspace_bytes(N) */
+  void* o1x_w_int8;     /* int8 [N,K]: the literal path's weights */
 } adg_bench_args;
+
+/* cold / steady_state of O0 and O2 run adg_o0_linear / adg_o2_linear's fused kernel: the `gemm` stage is
+ * that kernel (conversion inside), `activation_conversion` is still reported from the isolated batches of the
+ * stand-alone conversion kernel, and `total` is the directly timed path. */
+#define ADG_BENCH_FUSE_ACTIVATION 1u
+/* O1 on BF16 operands: report the INT8 -> BF16 activation conversion as a stage of its own instead of
+ * inside `gemm` (the reference's O1 has no activation stage, tests/integration/test_sm120_o1.py:86-94). */
+#define ADG_BENCH_O1_SPLIT_ACTIVATION 2u
 
 /* Runs the reference's timing protocol for one variant and mode (warm-up, `repeats` directly timed
  * iterations with CUDA events, conversions additionally timed as isolated batches of

@@ -328,3 +328,49 @@ def canonical_inputs(m: int, n: int, k: int, seed: int = 20250805):
     a_int8, a_scale = quantize_int8_per_row(a.numpy())
     w_mxfp4, w_scale = quantize_mxfp4(w.numpy())
     return a_int8, a_scale, w_mxfp4, w_scale
+
+
+# --------------------------------------------------------------------------------------------
+# o1x: the exact-integer variant of O1 (an addition of the B200 build; the reference has no such
+# variant -- its O1 is run_o1 above, python/adangel/reference/o1.py:8-29)
+# --------------------------------------------------------------------------------------------
+
+O1X_MAX_SPREAD = 3
+O1X_BLOCK = 128  # output columns are handed to the literal recurrence in blocks of this many
+
+
+def o1x_prepare(w_mxfp4, w_scale):
+    """Per W row: the smallest scale code over the blocks that hold a non-zero nibble, whether the row's
+    code spread allows one exponent (<= 3, so that 12 * 2**3 = 96 still fits INT8), and the INT8 image
+    ``2*e2m1 << (code - min code)`` (zero for an ineligible row)."""
+    n, kh = w_mxfp4.shape
+    groups = kh * 2 // GROUP_SIZE
+    base = mxfp4_to_int8_base(w_mxfp4).astype(np.int32).reshape(n, groups, GROUP_SIZE)
+    nonzero = (base != 0).any(axis=2)
+    codes = w_scale.astype(np.int32)
+    emin = np.where(nonzero, codes, 255).min(axis=1)
+    emax = np.where(nonzero, codes, 0).max(axis=1)
+    empty = emax < emin
+    emin = np.where(empty, 127, emin)
+    eligible = empty | (emax - emin <= O1X_MAX_SPREAD)
+    shift = np.clip(codes - emin[:, None], 0, O1X_MAX_SPREAD)
+    shifted = np.where(eligible[:, None, None], base << shift[:, :, None], 0).reshape(n, kh * 2)
+    factor = np.where(eligible, np.ldexp(np.float64(1.0), emin - 128), 0.0).astype(np.float32)
+    return shifted.astype(np.int8), factor, eligible
+
+
+def run_o1x(a_int8, a_scale, w_mxfp4, w_scale):
+    """``y = RN(float32_rn(S) * RN(A_scale[m] * 2**(emin[n]-128)))`` with ``S`` the exact integer sum over
+    all of K; 128-column blocks that contain an ineligible W row take run_o1's recurrence instead."""
+    w_shift, factor, eligible = o1x_prepare(w_mxfp4, w_scale)
+    sums = a_int8.astype(np.int64) @ w_shift.astype(np.int64).T  # exact
+    assert np.abs(sums).max(initial=0) < 2**31
+    scale = a_scale.astype(np.float32)[:, None] * factor[None, :]
+    y = sums.astype(np.float32) * scale
+    n = w_mxfp4.shape[0]
+    bad_blocks = sorted({int(i) // O1X_BLOCK for i in np.nonzero(~eligible)[0]})
+    if bad_blocks:
+        literal = run_o1(a_int8, a_scale, w_mxfp4, w_scale)["output"]
+        for b in bad_blocks:
+            y[:, b * O1X_BLOCK:min(n, (b + 1) * O1X_BLOCK)] = literal[:, b * O1X_BLOCK:min(n, (b + 1) * O1X_BLOCK)]
+    return {"output": y, "converted_weight": w_shift, "column_factor": factor, "ineligible_rows": int((~eligible).sum())}

@@ -78,9 +78,9 @@ def test_timing_mode_contract(golden_dir, variant, mode):
     _, _, cuda = _prepared(golden_dir)
     native = require_variant(variant)
     result = native.benchmark(variant, mode, cuda.A_int8, cuda.A_scale, cuda.W_mxfp4, cuda.W_scale, 2, 3)
-    # O1 has an activation conversion stage only when it runs on BF16 operands (M > 64, scales inside that
-    # kernel's exact range); on the reference's INT8 operands it has none
-    has_act = variant != "o1" or result["kernel"]["kernel_symbol"] == "gemm_o1_bf16_kernel"
+    # the reference's stage sets (tests/integration/test_sm120_o{0,1,2}.py): O1 never has an activation stage --
+    # on BF16 operands its INT8 -> BF16 conversion is part of this build's gemm stage unless asked otherwise
+    has_act = variant != "o1"
     expected = {
         "conversion_only": {"weight_conversion", "total"} | ({"activation_conversion"} if has_act else set()),
         "compute_only": {"gemm", "total"},
@@ -97,6 +97,29 @@ def test_timing_mode_contract(golden_dir, variant, mode):
     want = {"o0": orc.run_o0, "o1": orc.run_o1, "o2": orc.run_o2}[variant]
     args = tuple(t.cpu().numpy() for t in (cuda.A_int8, cuda.A_scale, cuda.W_mxfp4, cuda.W_scale))
     np.testing.assert_allclose(result["output"].cpu().numpy(), want(*args)["output"], rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("variant", ["o0", "o2"])
+@pytest.mark.parametrize("mode", ["cold", "steady_state"])
+def test_harness_fused_and_separate_activation_paths_agree(variant, mode):
+    # cold / steady_state of O0 and O2 run the GEMM kernel that converts A itself (the default) or, with
+    # fuse_activation=False, the reference's sequence of conversion kernel and GEMM: same stages, same bits
+    import torch
+
+    from adangel_oyzl_b200.ops import _sm100
+
+    args = orc.canonical_inputs(320, 384, 512, seed=71)
+    dev = [torch.from_numpy(np.ascontiguousarray(x)).cuda() for x in args]
+    fused = _sm100.benchmark(variant, mode, *dev, 1, 2, 2)
+    plain = _sm100.benchmark(variant, mode, *dev, 1, 2, 2, fuse_activation=False)
+    assert fused["kernel"]["fused_activation_conversion"] and not plain["kernel"]["fused_activation_conversion"]
+    assert set(fused["timings_ms"]) == set(plain["timings_ms"])
+    assert torch.equal(fused["output"], plain["output"])
+    if variant == "o2":
+        for got, want in zip(fused["converted_activation"], plain["converted_activation"]):
+            assert torch.equal(got, want)
+    else:
+        assert torch.equal(fused["converted_activation"].view(torch.int16), plain["converted_activation"].view(torch.int16))
 
 
 def test_rejections(golden_dir):
@@ -217,6 +240,9 @@ def test_harness_o1_operand_paths():
         result = _sm100.benchmark("o1", "steady_state", *dev, 1, 2)
         want = orc.run_o1(a_int8, a_scale, w_mx, sc)
         assert result["kernel"]["kernel_symbol"] == ("gemm_o1_kernel" if odd else "gemm_o1_bf16_kernel")
-        assert ("activation_conversion" in result["timings_ms"]) == (not odd)
+        assert "activation_conversion" not in result["timings_ms"]
+        split = _sm100.benchmark("o1", "steady_state", *dev, 1, 2, o1_split_activation_stage=True)
+        assert ("activation_conversion" in split["timings_ms"]) == (not odd)
+        np.testing.assert_array_equal(split["output"].cpu().numpy(), want["output"])
         np.testing.assert_array_equal(result["output"].cpu().numpy(), want["output"])
         np.testing.assert_array_equal(result["converted_weight"].cpu().numpy(), orc.mxfp4_to_int8_base(w_mx))

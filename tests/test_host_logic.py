@@ -23,7 +23,7 @@ def test_library_exports_declared_symbols():
     for name in sorted(declared):
         assert hasattr(lib, name), f"{name} is declared but not exported"
     assert declared == set(_sm100.EXPORTED_SYMBOLS)
-    assert lib.adg_abi_version() == 101
+    assert lib.adg_abi_version() == 102
     caps = _sm100.capabilities()
     for key in ("compiled_sm100a", "o0_fp16_tc", "o1_int8_tc", "o2_mxf4_block_scale", "o2_cutlass_tiled"):
         assert caps[key] is True
@@ -122,6 +122,28 @@ def test_kernel_and_timing_metadata():
     assert "kind::f16" in _sm100.kernel_metadata("o0", 4096, 4096, 4096)["mma_family"]
     assert "kind::i8" in _sm100.kernel_metadata("o1", 4096, 4096, 4096)["mma_family"]
     assert "kind::mxf4.block_scale" in _sm100.kernel_metadata("o2", 4096, 4096, 4096)["mma_family"]
+    assert "kind::i8" in _sm100.kernel_metadata("o1x", 4096, 4096, 4096)["mma_family"]
+
+
+def test_plan_info_follows_the_planner():
+    # the library's own account of what it would launch (adg_plan_info; 148 SMs assumed without a device)
+    from adangel_oyzl_b200.ops import _sm100
+
+    big = _sm100.plan_info("o2", 16384, 3584, 8192)
+    assert big["kernel_symbol"] == "gemm_pair_kernel<2>" and big["tile"] == [256, 256] and big["cluster"] == [2, 1, 1]
+    assert _sm100.plan_info("o2", 16384, 3584, 8192, fused=True)["kernel_symbol"] == "gemm_pair_kernel<2,fused>"
+    assert _sm100.plan_info("o2", 4096, 4096, 4096)["kernel_symbol"] == "gemm_acc_kernel<2>"
+    assert _sm100.plan_info("o0", 4096, 4096, 4096)["kernel_symbol"] == "gemm_pair_kernel<0>"
+    fused = _sm100.plan_info("o0", 4096, 4096, 4096, fused=True)
+    assert fused["fused_activation_conversion"] and fused["threads"] == 512
+    assert _sm100.plan_info("o0", 2048, 128, 4096)["tile"] == [128, 128]
+    assert _sm100.plan_info("o1", 4096, 4096, 4096)["kernel_symbol"] == "gemm_o1_kernel"
+    assert _sm100.plan_info("o1", 4096, 4096, 4096, o1_bf16=True)["kernel_symbol"] == "gemm_o1_bf16_kernel"
+    assert _sm100.plan_info("o1", 16, 4096, 4096, o1_bf16=True)["kernel_symbol"] == "gemm_o1_skinny_kernel"
+    assert _sm100.plan_info("o2", 64, 4096, 4096, fused=True)["kernel_symbol"] == "gemm_o2_skinny_kernel"
+    assert _sm100.plan_info("o1x", 4096, 4096, 4096)["mma_shape"] == [128, 256, 32]
+    with pytest.raises(RuntimeError, match="K must be divisible by 64"):
+        _sm100.plan_info("o0", 128, 128, 96)
 
 
 def test_sources_issue_blackwell_instructions():
@@ -170,3 +192,33 @@ def test_instruction_audit_passes(tmp_path):
     assert result["status"] == "PASS", result["lines"]
     assert (tmp_path / "summary.txt").read_text().startswith("status=PASS")
     assert result["kernels"] >= 12
+
+
+def test_c_abi_rejects_misaligned_and_null_pointers():
+    # the conversion kernels use 16-byte vector accesses (4-byte for scale arrays and flag words): a pointer
+    # that would fault on the device is refused on the host, before any CUDA call
+    from adangel_oyzl_b200.ops import _sm100
+
+    lib = _sm100.library()
+    base = 0x7F0000000000  # never dereferenced: every call below must fail in its argument checks
+    cases = [
+        (lib.adg_int8_to_fp16, (base + 1, base, base, 64, 64, None), "A_int8 must be 16-byte aligned"),
+        (lib.adg_int8_to_fp16, (base, base + 2, base, 64, 64, None), "A_scale must be 4-byte aligned"),
+        (lib.adg_int8_to_fp16, (base, base, base + 8, 64, 64, None), "out_fp16 must be 16-byte aligned"),
+        (lib.adg_mxfp4_to_fp16, (base + 4, base, base, 64, 64, None), "W_mxfp4 must be 16-byte aligned"),
+        (lib.adg_mxfp4_to_fp16, (base, None, base, 64, 64, None), "W_scale must not be NULL"),
+        (lib.adg_mxfp4_to_int8, (base, base + 3, 64, 64, None), "out_int8 must be 16-byte aligned"),
+        (lib.adg_mxfp4_to_bf16_scaled, (base, base, base, base + 2, 64, 64, None), "range_flag must be 4-byte aligned"),
+        (lib.adg_int8_to_bf16, (base, base, base + 1, base, 64, 64, None), "out_bf16 must be 16-byte aligned"),
+        (lib.adg_o2_quantize_activation, (base, base, base + 8, None, base, 64, 64, None), "A_mxfp4 must be 16-byte aligned"),
+        (lib.adg_o2_quantize_activation, (base, base, base, base + 1, base, 64, 64, None), "sf_natural must be 4-byte aligned"),
+        (lib.adg_o2_quantize_activation, (base, base, base, None, None, 64, 64, None), "sf_tiled must not be NULL"),
+        (lib.adg_o2_tile_scales, (base, base + 4, 64, 64, None), "sf_tiled must be 16-byte aligned"),
+        (lib.adg_quantize_int8_per_row, (base + 4, 0, base, base, 64, 64, None), "x must be 16-byte aligned"),
+        (lib.adg_quantize_mxfp4, (base, 0, base + 1, base, 64, 64, None), "packed must be 16-byte aligned"),
+        (lib.adg_o1x_prepare_weight, (base, base, base + 1, base, base, 64, 64, None), "must be 16-byte aligned"),
+        (lib.adg_int8_to_fp16, (base, base, base, 64, 96, None), "K must be divisible by 64"),
+    ]
+    for fn, args, message in cases:
+        assert fn(*args) != 0, message
+        assert message in lib.adg_last_error().decode(), (message, lib.adg_last_error())

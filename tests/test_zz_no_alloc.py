@@ -52,3 +52,37 @@ def test_no_alloc_rejects_oversized_activation():
     out = torch.empty((m, n), device="cuda")
     with pytest.raises(RuntimeError, match="too large for the built-in scratch"):
         K.o2_linear_noalloc(da, ds, dw, w_tiled, out)
+
+
+def test_no_alloc_async_status_is_reported_and_cleared():
+    """An asynchronous call (synchronize=0) leaves its kernels' status words inside the built-in array; the
+    status query and adg_check_status must both find, report and clear a non-zero word there.  The word is
+    planted from the host with a copy -- no kernel is made to give up."""
+    import ctypes
+
+    import torch
+
+    from adangel_oyzl_b200 import kernels as K
+
+    m, n, k = 128, 256, 256
+    a_int8, a_scale, w_mx, w_sc = orc.canonical_inputs(m, n, k, seed=103)
+    da, ds, dw, dws = (torch.from_numpy(x).cuda() for x in (a_int8, a_scale, w_mx, w_sc))
+    w_tiled = K.o2_tile_scales(dws)
+    out = torch.empty((m, n), device="cuda")
+    K.o2_linear_noalloc(da, ds, dw, w_tiled, out, synchronize=False)
+    K.o2_linear_noalloc_status()  # healthy: nothing to report
+    np.testing.assert_allclose(out.cpu().numpy(), orc.run_o2(a_int8, a_scale, w_mx, w_sc)["output"], rtol=RTOL, atol=ATOL)
+
+    lib = K._lib()
+    addr, size = ctypes.c_void_p(), ctypes.c_int()
+    assert lib.adg_o2_linear_noalloc_status_words(ctypes.byref(addr), ctypes.byref(size)) == 0
+    assert size.value >= 16
+    from cuda.bindings import runtime as cudart  # cuda-python: the same primary context as the library's runtime
+
+    words = torch.tensor([1, 0x123, 7, 0], dtype=torch.int32)  # code 1 = a wait that gave up, tag, block
+    for check in (K.o2_linear_noalloc_status, K.check_status):
+        (err,) = cudart.cudaMemcpy(addr.value, words.data_ptr(), 16, cudart.cudaMemcpyKind.cudaMemcpyHostToDevice)
+        assert int(err) == 0
+        with pytest.raises(RuntimeError, match="adg_o2_linear_noalloc: kernel wait timeout: code=1"):
+            check()
+        check()  # reported once, then clear
