@@ -44,14 +44,26 @@ def broadcast_activations(a_int8, a_scale, src: int = 0, group=None):
 
 
 def gather_columns(y_local, n: int, group=None, align: int = TILE_ALIGN):
-    """All-gather the ranks' column blocks ``[M, n_r]`` into the contiguous ``[M, N]`` matrix."""
+    """All-gather the ranks' column blocks ``[M, n_r]`` into the contiguous ``[M, N]`` matrix.
+
+    Equal blocks (the usual case: N a multiple of ``align * world``) travel in ONE collective into a
+    ``[world, M, N/world]`` buffer, followed by one local permute into ``[M, N]``; ragged partitions fall
+    back to padded pieces."""
     import torch
     import torch.distributed as dist
 
     world = dist.get_world_size(group)
     ranges = all_ranges(n, world, align)
     m = y_local.shape[0]
-    widest = max(n1 - n0 for n0, n1 in ranges)
+    widths = {n1 - n0 for n0, n1 in ranges}
+    if len(widths) == 1:
+        width = widths.pop()
+        stacked = torch.empty((world * m, width), dtype=y_local.dtype, device=y_local.device)
+        dist.all_gather_into_tensor(stacked, y_local.contiguous(), group=group)
+        full = torch.empty((m, n), dtype=y_local.dtype, device=y_local.device)
+        full.view(m, world, width).copy_(stacked.view(world, m, width).permute(1, 0, 2))
+        return full
+    widest = max(widths)
     # collectives want equal-sized pieces: ragged blocks travel padded to the widest one
     mine = y_local
     if y_local.shape[1] != widest:
@@ -74,6 +86,7 @@ class ShardedWeights:
     w_int8: object = None    # O1 (INT8 operands: every input)
     o1: object = None        # O1: kernels.O1Weights (both operand forms + flag words) for kernels.o1_linear
     w_sf_tiled: object = None  # O2
+    workspaces: object = None  # kernels.FusedWorkspace per variant, made on first use
 
     @property
     def rows(self) -> int:
@@ -103,19 +116,37 @@ def shard_weights(w_mxfp4, w_scale, world_size: int, rank: int, variants=("o0", 
     return shard
 
 
-def sharded_gemm(variant: str, a_int8, a_scale, shard: ShardedWeights, out=None):
-    """This rank's column block of Y for ``variant`` (activation conversion included)."""
+def _workspace(shard: ShardedWeights, variant: str, m: int, k: int, device):
+    from . import kernels
+
+    if shard.workspaces is None:
+        shard.workspaces = {}
+    ws = shard.workspaces.get(variant)
+    if ws is None or ws.max_m < m or ws.k != k:
+        ws = shard.workspaces[variant] = kernels.FusedWorkspace(variant, m, k, device)
+    return ws
+
+
+def sharded_gemm(variant: str, a_int8, a_scale, shard: ShardedWeights, out=None, fused: bool = True):
+    """This rank's column block of Y for ``variant`` (activation conversion included).  O0 and O2 convert the
+    replicated A inside the GEMM kernel (``fused=False``: the conversion kernel first, then the GEMM)."""
     from . import kernels
 
     if shard.rows == 0:
         return out
+    m, k = a_int8.shape
     if variant == "o0":
+        if fused:
+            return kernels.o0_linear(a_int8, a_scale, shard.w_fp16, _workspace(shard, "o0", m, k, a_int8.device), out=out)
         return kernels.gemm_o0(kernels.int8_to_fp16(a_int8, a_scale), shard.w_fp16, out=out)
     if variant == "o1":
         if getattr(shard, "o1", None) is not None:
             return kernels.o1_linear(a_int8, a_scale, shard.o1, out=out)
         return kernels.gemm_o1(a_int8, a_scale, shard.w_int8, shard.w_scale, out=out)
     if variant == "o2":
+        if fused:
+            return kernels.o2_linear(a_int8, a_scale, shard.w_mxfp4, shard.w_sf_tiled, _workspace(shard, "o2", m, k, a_int8.device),
+                                     out=out)
         codes, _, sfa = kernels.o2_quantize_activation(a_int8, a_scale, want_natural=False)
         return kernels.gemm_o2(codes, sfa, shard.w_mxfp4, shard.w_sf_tiled, out=out)
     raise ValueError(f"unknown variant: {variant}")
