@@ -26,6 +26,8 @@ LIB = PKG / "lib" / "libadangel_b200.so"
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
+# gemm_o1_bf16.cu: the O1 recurrence rounds after the multiply AND after the add; no contraction into fma
+PER_FILE = {"gemm_o1_bf16.cu": ["-fmad=false"]}
 
 
 def _nvcc() -> str:
@@ -45,7 +47,7 @@ def _compile(src: Path, force: bool, verbose: bool) -> Path:
     obj = build_dir / (src.stem + ".o")
     if not force and obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, _newest_header()):
         return obj
-    cmd = [_nvcc(), *ARCH_FLAGS, *COMMON, "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *ARCH_FLAGS, *COMMON, *PER_FILE.get(src.name, []), "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     log = build_dir / (src.stem + ".ptxas.log")
     log.write_text(proc.stderr)

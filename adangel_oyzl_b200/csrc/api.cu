@@ -270,7 +270,7 @@ int64_t adg_fused_workspace_bytes(int64_t M) { return 4 * ((M + 127) / 128 + 1);
 int adg_o0_linear(const void* a_int8, const void* a_scale, const void* w_fp16, void* a_fp16_workspace, void* row_counters,
                   float* y, int M, int N, int K, int ldy, void* stream) {
   GemmPlan plan;
-  if (M > 64 && row_counters != nullptr && fusion_enabled()) {
+  if (M > 64 && row_counters != nullptr) {
     if (int rc = plan_o0_fused(&plan, a_int8, a_scale, a_fp16_workspace, w_fp16, y, row_counters, M, N, K, ldy)) return rc;
     return run_plan(plan, as_stream(stream));
   }
@@ -283,7 +283,7 @@ int adg_o2_linear(const void* a_int8, const void* a_scale, const void* w_mxfp4, 
                   void* a_sf_tiled_workspace, void* a_sf_natural, void* row_counters, float* y, int M, int N, int K, int ldy,
                   void* stream) {
   GemmPlan plan;
-  if (M > 64 && row_counters != nullptr && fusion_enabled()) {
+  if (M > 64 && row_counters != nullptr) {
     if (a_sf_natural != nullptr && check_ptr(a_sf_natural, 4, "a_sf_natural")) return 1;
     if (int rc = plan_o2_fused(&plan, a_int8, a_scale, a_mxfp4_workspace, a_sf_tiled_workspace, a_sf_natural, w_mxfp4,
                                w_sf_tiled, y, row_counters, M, N, K, ldy))

@@ -50,6 +50,23 @@ __device__ __forceinline__ uint32_t float2_to_e2m1x2(float first, float second) 
   return out;
 }
 
+// Eight FP32 values -> one 32-bit word of packed E2M1 (x[0] in the lowest nibble), round-to-nearest-even,
+// saturating to +-6: four conversions and one byte merge.
+__device__ __forceinline__ uint32_t float8_to_e2m1x8(const float (&x)[8]) {
+  uint32_t out;
+  asm("{\n"
+      ".reg .b8 t0, t1, t2, t3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n"
+      "mov.b32 %0, {t0, t1, t2, t3};\n"
+      "}\n"
+      : "=r"(out)
+      : "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]), "f"(x[4]), "f"(x[5]), "f"(x[6]), "f"(x[7]));
+  return out;
+}
+
 // prmt.b32 in its default mode: selector nibble bits [2:0] pick one of the eight source bytes
 // {b:a}; bit 3 replaces the picked byte by eight copies of its most significant bit.
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {

@@ -38,7 +38,8 @@ namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kEpiWarps = 8;
-constexpr int kSfWarp = 2;        // copies scale factors into tensor memory (O2 only)
+constexpr int kSfWarp = 2;
+constexpr int kPublishWarp = 3;   // FUSED kernels: publishes the converter warps' finished rows        // copies scale factors into tensor memory (O2 only)
 constexpr int kFirstEpiWarp = 4;  // the epilogue is warp groups 1 and 2
 constexpr int kFirstConvWarp = kFirstEpiWarp + kEpiWarps;  // warp group 3 (FUSED kernels)
 constexpr int kAccThreads = kFirstConvWarp * 32;
@@ -60,6 +61,18 @@ enum : uint32_t {  // wait tags reported on timeout
   kTagRowsReady = 0x600,
 };
 
+// Waits of the roles that have nothing else to do.  In a FUSED kernel the waiting warps share their
+// schedulers with the converter warps: they wait suspended by the hardware (mbarrier.try_wait with a time
+// hint) instead of probing in a loop, so that their probes do not take the converters' issue slots.
+template <bool FUSED>
+__device__ __forceinline__ bool role_wait(uint64_t* bar, uint32_t parity, const WaitEnv& env, uint32_t tag) {
+  if constexpr (FUSED) {
+    return mbar_wait_suspended_a(smem_u32(bar), parity, env.status, smem_u32(const_cast<uint32_t*>(env.abort)), tag);
+  } else {
+    return mbar_wait(bar, parity, env, tag);
+  }
+}
+
 // Bounded wait until `*counter` has reached `need` (rows of a row block converted by the converter
 // warps of all CTAs).  Returns false when the CTA is aborting.
 __device__ __forceinline__ bool wait_rows_ready(const uint32_t* counter, uint32_t need, const WaitEnv& env, uint32_t tag) {
@@ -67,6 +80,7 @@ __device__ __forceinline__ bool wait_rows_ready(const uint32_t* counter, uint32_
   const unsigned long long t0 = global_timer_ns();
   uint32_t spins = 0;
   while (ld_acquire_gpu(counter) < need) {
+    __nanosleep(200);
     if ((++spins & 0xFFu) == 0) {
       if (*env.abort) return false;
       if (global_timer_ns() - t0 > kWaitTimeoutNs) {
@@ -139,6 +153,7 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
   uint64_t* sf_full_bar = tmem_empty_bar + Cfg::kAccStages;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sf_full_bar + Cfg::kStages);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
+  uint32_t* conv_done_slot = tmem_base_slot + 2;  // FUSED: rows finished by this CTA's converter warps
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -161,6 +176,7 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       mbar_init(&tmem_empty_bar[a], kEpiWarps);
     }
     *abort_flag = 0;
+    *conv_done_slot = 0;
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
@@ -188,17 +204,23 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      uint32_t seen_rows = 0;  // FUSED: the counter of this tile's row block as read one tile earlier
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         const TileCoord tc = tile_coord(tile, num_m, num_n);
         if constexpr (FUSED) {
-          // the row block's operand is being written by the converter warps of all CTAs
+          // the row block's operand is being written by the converter warps of all CTAs; its counter was
+          // requested while the previous tile's loads were issued, so a finished block costs no round trip
           const uint32_t need = static_cast<uint32_t>(min(kBlockM, M - tc.m_blk * kBlockM));
-          ok = wait_rows_ready(conv.ready + tc.m_blk, need, env, kTagRowsReady);
-          if (!ok) break;
+          if (seen_rows < need) {
+            ok = wait_rows_ready(conv.ready + tc.m_blk, need, env, kTagRowsReady);
+            if (!ok) break;
+          }
           fence_proxy_async_all();
+          const int next_tile = tile + static_cast<int>(gridDim.x);
+          if (next_tile < num_tiles) seen_rows = ld_acquire_gpu(conv.ready + tile_coord(next_tile, num_m, num_n).m_blk);
         }
         for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage);
+          ok = role_wait<FUSED>(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage);
           if (!ok) break;
           uint8_t* st = smem + stage * Cfg::kStageBytes;
           mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
@@ -291,7 +313,7 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
           for (int kb = 0; kb < num_kb; ++kb) {
             // the stage's data has landed; its tensor-memory scale columns were last read by MMAs
             // that completed before the stage was handed back to the producer
-            ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | 0x80 | stage);
+            ok = role_wait<FUSED>(&full_bar[stage], phase, env, kTagFull | 0x80 | stage);
             if (!ok) break;
             tc_fence_after();
             const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
@@ -316,6 +338,18 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         }
       }
     }
+  } else if (warp == kPublishWarp) {
+    // ------------------------------- row publisher (FUSED) -------------------------------------
+    if constexpr (FUSED) {
+      if (lane == 0 && !publish_rows_role(conv, M, blockIdx.x, gridDim.x, smem_u32(conv_done_slot), abort_flag, kWaitTimeoutNs)) {
+        *abort_flag = 1;
+        if (atomicCAS(status, 0u, static_cast<uint32_t>(kStatusWaitTimeout)) == 0u) {
+          status[1] = kTagRowsReady | 0x80u;
+          status[2] = blockIdx.x;
+          status[3] = 0;
+        }
+      }
+    }
   } else if (warp >= kFirstEpiWarp && warp < kFirstConvWarp) {
     if constexpr (FUSED) reg_alloc<kFusedRegsEpi>();
     // ------------------------------- epilogue ---------------------------------------------------
@@ -332,7 +366,7 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       const TileCoord tc = tile_coord(tile, num_m, num_n);
       const int acc = local_tile % Cfg::kAccStages;
       const uint32_t acc_phase = static_cast<uint32_t>(local_tile / Cfg::kAccStages) & 1u;
-      ok = mbar_wait(&tmem_full_bar[acc], acc_phase, env, kTagTmemFull | acc);
+      ok = role_wait<FUSED>(&tmem_full_bar[acc], acc_phase, env, kTagTmemFull | acc);
       if (!ok) break;
       tc_fence_after();
       const int row0 = tc.m_blk * kBlockM + q * 32;
@@ -399,7 +433,8 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     // ------------------------------- activation converters (FUSED) ------------------------------
     if constexpr (FUSED) {
       reg_dealloc<kFusedRegsConv>();
-      convert_rows_role<KIND>(conv, M, K, static_cast<int>(threadIdx.x) - kAccThreads, blockIdx.x, gridDim.x, kConvBarrier);
+      convert_rows_role<KIND>(conv, M, K, static_cast<int>(threadIdx.x) - kAccThreads, blockIdx.x, gridDim.x, kConvBarrier,
+                              smem_u32(conv_done_slot));
     }
   }
 

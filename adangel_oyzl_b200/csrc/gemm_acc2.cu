@@ -39,6 +39,7 @@ constexpr int kTileA = kBlockM * 128;
 constexpr int kTileB = kHalfN * 128;
 constexpr int kEpiWarps = 8;
 constexpr int kSfWarp = 2;
+constexpr int kPublishWarp = 3;   // FUSED kernels: publishes the converter warps' finished rows
 constexpr int kFirstEpiWarp = 4;  // the epilogue is warp groups 1 and 2
 constexpr int kFirstConvWarp = kFirstEpiWarp + kEpiWarps;  // warp group 3 (FUSED kernels)
 constexpr int kThreads = kFirstConvWarp * 32;
@@ -70,12 +71,25 @@ struct PairCfg {
 enum : uint32_t { kTagEmpty = 0x4100, kTagFull = 0x4200, kTagTmemEmpty = 0x4300, kTagTmemFull = 0x4400, kTagSfFull = 0x4500,
                   kTagRowsReady = 0x4600 };
 
+// Waits of the roles that have nothing else to do.  In a FUSED kernel the waiting warps share their
+// schedulers with the converter warps: they wait suspended by the hardware (mbarrier.try_wait with a time
+// hint) instead of probing in a loop, so that their probes do not take the converters' issue slots.
+template <bool FUSED>
+__device__ __forceinline__ bool role_wait(uint64_t* bar, uint32_t parity, const WaitEnv& env, uint32_t tag) {
+  if constexpr (FUSED) {
+    return mbar_wait_suspended_a(smem_u32(bar), parity, env.status, smem_u32(const_cast<uint32_t*>(env.abort)), tag);
+  } else {
+    return mbar_wait(bar, parity, env, tag);
+  }
+}
+
 // Bounded wait until `*counter` has reached `need` (see gemm_acc.cu).
 __device__ __forceinline__ bool wait_rows_ready(const uint32_t* counter, uint32_t need, const WaitEnv& env, uint32_t tag) {
   if (ld_acquire_gpu(counter) >= need) return true;
   const unsigned long long t0 = global_timer_ns();
   uint32_t spins = 0;
   while (ld_acquire_gpu(counter) < need) {
+    __nanosleep(200);
     if ((++spins & 0xFFu) == 0) {
       if (*env.abort) return false;
       if (global_timer_ns() - t0 > kWaitTimeoutNs) {
@@ -190,6 +204,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   uint64_t* tmem_empty_bar = tmem_full_bar + Cfg::kAccStages;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + Cfg::kAccStages);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
+  uint32_t* conv_done_slot = tmem_base_slot + 2;  // FUSED: rows finished by this CTA's converter warps
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -215,6 +230,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       mbar_init(&tmem_empty_bar[a], 2 * kEpiWarps);
     }
     *abort_flag = 0;
+    *conv_done_slot = 0;
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
@@ -248,6 +264,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       const uint32_t full_leader = map_to_cta(smem_u32(full_bar), 0);
+      uint32_t seen_rows = 0;  // FUSED: the counter of this tile's row block as read one tile earlier
       for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
         const TileCoord tc = tile_coord(tile, num_mp, num_n);
         const int m_blk = tc.m_pair * 2 + static_cast<int>(rank);
@@ -257,14 +274,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           // this CTA's 128 rows of the operand are being written by the converter warps of all CTAs
           // (a pair's second row block may lie wholly beyond M: nothing to wait for, the loads read zeros)
           const int rows_left = M - row0;
-          if (rows_left > 0) {
+          if (rows_left > 0 && seen_rows < static_cast<uint32_t>(min(kBlockM, rows_left))) {
             ok = wait_rows_ready(conv.ready + m_blk, static_cast<uint32_t>(min(kBlockM, rows_left)), env, kTagRowsReady);
             if (!ok) break;
           }
           fence_proxy_async_all();
+          // request the next tile's counter now: it arrives while this tile's loads are issued
+          const int next_tile = tile + num_clusters;
+          seen_rows = 0;
+          if (next_tile < num_tiles) {
+            const int next_blk = tile_coord(next_tile, num_mp, num_n).m_pair * 2 + static_cast<int>(rank);
+            if (next_blk * kBlockM < M) seen_rows = ld_acquire_gpu(conv.ready + next_blk);
+          }
         }
         for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage);
+          ok = role_wait<FUSED>(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage);
           if (!ok) break;
           uint8_t* st = smem + stage * Cfg::kStageBytes;
           if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
@@ -352,7 +376,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           for (int kb = 0; kb < num_kb; ++kb) {
             // both CTAs' scale factors of the stage have landed; the stage's tensor-memory scale
             // columns were last read by MMAs that completed before the stage was handed back
-            ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | 0x80 | stage);
+            ok = role_wait<FUSED>(&full_bar[stage], phase, env, kTagFull | 0x80 | stage);
             if (!ok) break;
             tc_fence_after();
             const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
@@ -377,6 +401,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
       }
     }
+  } else if (warp == kPublishWarp) {
+    // ------------------------------- row publisher (FUSED) -------------------------------------
+    if constexpr (FUSED) {
+      if (lane == 0 && !publish_rows_role(conv, M, blockIdx.x, gridDim.x, smem_u32(conv_done_slot), abort_flag, kWaitTimeoutNs)) {
+        *abort_flag = 1;
+        if (atomicCAS(status, 0u, static_cast<uint32_t>(kStatusWaitTimeout)) == 0u) {
+          status[1] = kTagRowsReady | 0x80u;
+          status[2] = blockIdx.x;
+          status[3] = 0;
+        }
+      }
+    }
   } else if (warp >= kFirstEpiWarp && warp < kFirstConvWarp) {
     if constexpr (FUSED) reg_alloc<kFusedRegsEpi>();
     // ------------------------------- epilogue (both CTAs) -------------------------------------
@@ -394,7 +430,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const TileCoord tc = tile_coord(tile, num_mp, num_n);
       const int acc = local_tile % Cfg::kAccStages;
       const uint32_t acc_phase = static_cast<uint32_t>(local_tile / Cfg::kAccStages) & 1u;
-      ok = mbar_wait(&tmem_full_bar[acc], acc_phase, env, kTagTmemFull | acc);
+      ok = role_wait<FUSED>(&tmem_full_bar[acc], acc_phase, env, kTagTmemFull | acc);
       if (!ok) break;
       tc_fence_after();
       const int row0 = (tc.m_pair * 2 + static_cast<int>(rank)) * kBlockM + q * 32;
@@ -444,7 +480,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     // ------------------------------- activation converters (FUSED, both CTAs) ------------------
     if constexpr (FUSED) {
       reg_dealloc<kFusedRegsConv>();
-      convert_rows_role<KIND>(conv, M, K, static_cast<int>(threadIdx.x) - kThreads, blockIdx.x, gridDim.x, kConvBarrier);
+      convert_rows_role<KIND>(conv, M, K, static_cast<int>(threadIdx.x) - kThreads, blockIdx.x, gridDim.x, kConvBarrier,
+                              smem_u32(conv_done_slot));
     }
   }
 

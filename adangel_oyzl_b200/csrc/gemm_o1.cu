@@ -58,6 +58,7 @@ struct TileCoord {
 };
 // `n_list`, if given, restricts the launch to some column blocks: n_list[0] of them, listed from n_list[1]
 // (the exact-integer O1 variant sends only the column blocks that hold an ineligible W row through here).
+template <bool kListed>
 __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, const int32_t* __restrict__ n_list) {
   const int per_group = kGroupM * num_n;
   const int group = tile / per_group;
@@ -67,13 +68,14 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
   TileCoord t;
   t.m_blk = first_m + in_group % gsize;
   t.n_blk = in_group / gsize;
-  if (n_list != nullptr) t.n_blk = __ldg(n_list + 1 + t.n_blk);
+  if constexpr (kListed) t.n_blk = __ldg(n_list + 1 + t.n_blk);
   return t;
 }
 
-// kDump = true adds the debug store of every INT32 partial (a separate instantiation so that the
-// production kernel carries none of its register pressure).
-template <bool kDump>
+// kDump = true adds the debug store of every INT32 partial, kListed = true the restriction to listed column
+// blocks (separate instantiations so that the production kernel carries none of their register pressure:
+// its epilogue has no register to spare).
+template <bool kDump, bool kListed>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const float* __restrict__ a_scale, const uint8_t* __restrict__ w_scale, float* __restrict__ y,
@@ -81,7 +83,9 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                const uint32_t* __restrict__ only_if_flag, const int32_t* __restrict__ n_list) {
   // second half of a sync-free fallback: run only when the BF16-operand kernel in front refused
   if (only_if_flag != nullptr && *only_if_flag == 0u) return;
-  if (n_list != nullptr && __ldg(n_list) <= 0) return;
+  if constexpr (kListed) {
+    if (__ldg(n_list) <= 0) return;
+  }
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* sc_ring = reinterpret_cast<float*>(smem + kStages * kStageBytes);
@@ -103,7 +107,7 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   const uint32_t full_a = smem_u32(full_bar), empty_a = smem_u32(empty_bar);
 
   const int num_m = (M + kBlockM - 1) / kBlockM;
-  const int num_n = n_list != nullptr ? __ldg(n_list) : (N + kBlockN - 1) / kBlockN;
+  const int num_n = kListed ? __ldg(n_list) : (N + kBlockN - 1) / kBlockN;
   const int num_tiles = num_m * num_n;
   const int groups = K / 32;
   const int num_kb = (groups + 3) / 4;
@@ -146,7 +150,7 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const TileCoord tc = tile_coord(tile, num_m, num_n, n_list);
+        const TileCoord tc = tile_coord<kListed>(tile, num_m, num_n, n_list);
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait_a(empty_a + stage * 8, phase ^ 1u, status, abort_a, kTagEmpty | stage);
           if (!ok) break;
@@ -227,9 +231,9 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     };
     uint32_t next_codes[kRowsPerLane];
     int tile = blockIdx.x;
-    if (tile < num_tiles) load_codes(tile_coord(tile, num_m, num_n, n_list).n_blk, 0, next_codes);
+    if (tile < num_tiles) load_codes(tile_coord<kListed>(tile, num_m, num_n, n_list).n_blk, 0, next_codes);
     for (; ok && tile < num_tiles; tile += gridDim.x) {
-      const int n_blk = tile_coord(tile, num_m, num_n, n_list).n_blk;
+      const int n_blk = tile_coord<kListed>(tile, num_m, num_n, n_list).n_blk;
       for (int kb = 0; kb < num_kb; ++kb) {
         uint32_t codes[kRowsPerLane];
 #pragma unroll
@@ -237,7 +241,7 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (kb + 1 < num_kb) {
           load_codes(n_blk, kb + 1, next_codes);
         } else if (tile + static_cast<int>(gridDim.x) < num_tiles) {
-          load_codes(tile_coord(tile + gridDim.x, num_m, num_n, n_list).n_blk, 0, next_codes);
+          load_codes(tile_coord<kListed>(tile + gridDim.x, num_m, num_n, n_list).n_blk, 0, next_codes);
         }
         ok = mbar_wait_a(sc_empty_a + scs * 8, sc_phase ^ 1u, status, abort_a, kTagScEmpty | scs);
         if (!ok) break;
@@ -294,7 +298,7 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     };
 
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      const TileCoord tc = tile_coord(tile, num_m, num_n, n_list);
+      const TileCoord tc = tile_coord<kListed>(tile, num_m, num_n, n_list);
       const int row = tc.m_blk * kBlockM + q * 32 + lane;
       const int col0 = tc.n_blk * kBlockN + cs * 32;
       const float a_m = row < M ? __ldg(a_scale + row) : 0.0f;
@@ -386,30 +390,34 @@ gemm_o1_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
 }  // namespace
 
+int init_gemm_o1_attributes() {
+  if (int rc = check_cuda(cudaFuncSetAttribute(gemm_o1_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+                          "cudaFuncSetAttribute(gemm_o1_kernel)"))
+    return rc;
+  if (int rc = check_cuda(cudaFuncSetAttribute(gemm_o1_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+                          "cudaFuncSetAttribute(gemm_o1_kernel<listed>)"))
+    return rc;
+  return check_cuda(cudaFuncSetAttribute(gemm_o1_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+                    "cudaFuncSetAttribute(gemm_o1_kernel<dump>)");
+}
+
 int o1_block_n() { return kBlockN; }
 int o1_ctas_per_sm() { return kCtasPerSm; }
 
-int init_gemm_o1_attributes() {
-  if (int rc = check_cuda(
-          cudaFuncSetAttribute(gemm_o1_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
-          "cudaFuncSetAttribute(gemm_o1_kernel)"))
-    return rc;
-  return check_cuda(
-      cudaFuncSetAttribute(gemm_o1_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
-      "cudaFuncSetAttribute(gemm_o1_kernel<dump>)");
-}
-
 int run_gemm_o1(const GemmPlan& p, cudaStream_t stream) {
   if (p.variant != 1) return fail("run_gemm_o1: plan is not an O1 plan");
+  const float* a_scale = static_cast<const float*>(p.a_scale);
+  const uint8_t* w_scale = static_cast<const uint8_t*>(p.w_scale);
   if (p.partial_dump != nullptr) {
-    gemm_o1_kernel<true><<<p.grid, kThreads, kSmemBytes, stream>>>(
-        p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y,
-        p.partial_dump, p.M, p.N, p.K, p.ldy, p.status, p.only_if_flag, p.n_list);
+    if (p.n_list != nullptr) return fail("run_gemm_o1: the partial dump and a column-block list exclude one another");
+    gemm_o1_kernel<true, false><<<p.grid, kThreads, kSmemBytes, stream>>>(p.tm_a, p.tm_b, a_scale, w_scale, p.y, p.partial_dump, p.M,
+                                                                         p.N, p.K, p.ldy, p.status, p.only_if_flag, nullptr);
+  } else if (p.n_list != nullptr) {
+    gemm_o1_kernel<false, true><<<p.grid, kThreads, kSmemBytes, stream>>>(p.tm_a, p.tm_b, a_scale, w_scale, p.y, nullptr, p.M, p.N,
+                                                                         p.K, p.ldy, p.status, p.only_if_flag, p.n_list);
   } else {
-    gemm_o1_kernel<false><<<p.grid, kThreads, kSmemBytes, stream>>>(
-        p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y,
-        nullptr,
-        p.M, p.N, p.K, p.ldy, p.status, p.only_if_flag, p.n_list);
+    gemm_o1_kernel<false, false><<<p.grid, kThreads, kSmemBytes, stream>>>(p.tm_a, p.tm_b, a_scale, w_scale, p.y, nullptr, p.M, p.N,
+                                                                          p.K, p.ldy, p.status, p.only_if_flag, nullptr);
   }
   return check_cuda(cudaGetLastError(), "gemm_o1_kernel launch");
 }

@@ -29,10 +29,11 @@
 // buffers 1 and 3 with the odd groups (the two MMAs of a group must come from one thread, in order;
 // different groups are independent), and an epilogue warp gives a buffer back as soon as its 32
 // columns are in registers -- in the middle of the previous partial's arithmetic -- and asks for the
-// next partial before its arithmetic if that partial is already there.  Measured at 4096^3: 375 us with two-group buffers and
+// next partial before its arithmetic if that partial is already there.  The epilogue arithmetic is packed (two
+// elements per instruction), which frees issue slots for the hand-over instructions.  Measured at 4096^3: 375 us with two-group buffers and
 // one issuer, 365 us with per-group buffers, 342 us with the second issuer, 335 us with the early
 // request, 326 us with the next buffer released in the middle of the arithmetic, 323 us with the
-// one-thread roles waiting suspended; the kernel
+// one-thread roles waiting suspended, 283 us with packed arithmetic; the kernel (before packing)
 // without the arithmetic takes 199 us, so the hand-over chain
 // (MMA -> commit -> load -> release, about a thousand cycles, over four buffers) and the arithmetic
 // (137 us, near the FP32 pipe's rate) add up instead of overlapping.
@@ -47,13 +48,25 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
 constexpr int kStages = 6;      // A 128 x 128 B + W 128 x 128 B each: two K32 groups
 constexpr int kBufs = 4;         // 128-column tensor-memory buffers, one K32 partial each
-constexpr int kEpiWarps = 4 * (kBlockN / 32);
 constexpr int kFirstEpiWarp = 4;
-constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
+// Geometry of the epilogue by the number of tensor-memory columns one epilogue warp owns (CW): 32 -> 16 warps
+// (four per scheduler), 64 -> 8 warps (two per scheduler, twice as much arithmetic between two hand-overs;
+// measured 293 us against 283 us at 4096^3, same bits, so 32 is what is built).
+// Registers: the first warp group keeps kRoleRegs per thread and hands the rest to the epilogue warps.
+constexpr int kColsPerEpiWarp = 32;
+template <int CW>
+struct EpiCfg {
+  static constexpr int kEpiWarps = 4 * (kBlockN / CW);
+  static constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
+  static constexpr int kLaunchRegs = (65536 / kThreads) / 8 * 8;  // registers per thread at launch
+  static constexpr int kRoleRegs = 32;
+  static constexpr int kEpiRegs = kLaunchRegs + (kLaunchRegs - kRoleRegs) * 4 / kEpiWarps / 8 * 8;
+  static_assert(128 * kRoleRegs + kEpiWarps * 32 * kEpiRegs <= 65536, "register budget");
+  static_assert(kEpiRegs <= 248, "register budget");
+};
 constexpr int kTile = kBlockM * 128;
 constexpr int kStageBytes = kTile + kBlockN * 128;
 constexpr int kTmemCols = kBufs * kBlockN;
-constexpr int kEpiRegs = 112;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
 constexpr int kGroupM = 8;
 constexpr uint32_t kFmtBF16 = 1;  // kind::f16 operand format: bfloat16
@@ -86,7 +99,8 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) 
   return t;
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <int CW>
+__global__ void __launch_bounds__(EpiCfg<CW>::kThreads, 1)
 gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const float* __restrict__ a_scale, float* __restrict__ y, const uint32_t* __restrict__ range_flag,
                     int quiet_refusal, int M, int N, int K, int ldy, uint32_t* status) {
@@ -103,6 +117,7 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       return;
     }
   }
+  constexpr int kEpiWarps = EpiCfg<CW>::kEpiWarps;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -150,7 +165,7 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const uint32_t tmem_base = *tmem_base_slot;
 
   if (warp < kFirstEpiWarp) {
-    reg_dealloc<32>();  // 128 threads x 64 registers returned = 512 threads x 16 registers gained below
+    reg_dealloc<EpiCfg<CW>::kRoleRegs>();  // what this warp group returns is what the epilogue warps gain below
     if (warp == 0) {
       // ------------------------------- TMA producer -------------------------------------------
       if (lane == 0) {
@@ -208,35 +223,53 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
     }
   } else {
-    reg_alloc<kEpiRegs>();
+    reg_alloc<EpiCfg<CW>::kEpiRegs>();
     // ------------------------------- epilogue ---------------------------------------------------
     // Each warp owns 32 columns of one lane quarter and alternates between two register buffers:
     // while one partial is scaled and accumulated, the load of the next is in flight.
     const int q = warp & 3;                     // tensor-memory lane quarter
-    const int cs = (warp - kFirstEpiWarp) >> 2;  // 32-column slice of the 128-column partial
-    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(cs * 32);
+    const int cs = (warp - kFirstEpiWarp) >> 2;  // CW-column slice of the 128-column partial
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(cs * CW);
     int pair = 0;  // tensor-memory buffer of the next partial
     uint32_t pair_phase = 0;
     bool ok = true;
 
     // The arithmetic (accumulate_part below) is two passes, each a run of independent instructions:
-    // u = RN(partial * A_scale), acc = RN(acc + u).
-    // Scalar on purpose: the packed forms (mul.rn.f32x2 followed by add.rn.f32x2, or by an fma with a
-    // multiplier of one) were measured to come out contracted into one fused multiply-add -- a
-    // single rounding where the recurrence has two, which changes 30 % of the results by an ulp.
+    // u = RN(partial * A_scale), acc = RN(acc + u), two elements per instruction (mul.rn.f32x2, add.rn.f32x2).
+    // The FP32 pipe needs two cycles for a packed instruction, which leaves every other issue slot of the
+    // scheduler to the other warps' hand-over instructions: 283 us against 326 us with scalar arithmetic at
+    // 4096^3, same bits.  This translation unit is compiled with -fmad=false: left to itself the assembler
+    // contracts the packed multiply and add into one fused multiply-add -- a single rounding where the
+    // recurrence has two, which changes 30 % of the results by an ulp.
 
     // elements of a partial handled before the next buffer is released (8, 16 and 24 measure alike)
-    constexpr int kSplit = 16;
+    constexpr int kSplit = CW / 2;
     // elements [lo, hi) of a partial (both even)
-    auto accumulate_part = [&](uint32_t (&p)[32], float2 (&acc)[16], const float a, const int lo, const int hi) {
+    auto accumulate_part = [&](uint32_t (&p)[CW], float2 (&acc)[CW / 2], const float a, const int lo, const int hi) {
+      // two elements per instruction: the FP32 pipe needs two cycles for each, which leaves every other
+      // issue slot of the scheduler to the other warps' hand-over instructions.  This translation unit is
+      // compiled with -fmad=false so that the multiply and the add stay two roundings.
+      uint64_t a2;
+      asm("mov.b64 %0, {%1, %1};" : "=l"(a2) : "r"(__float_as_uint(a)));
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j >= lo && j < hi) p[j] = __float_as_uint(__fmul_rn(__uint_as_float(p[j]), a));
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
+      for (int j = 0; j < CW / 2; ++j) {
         if (2 * j >= lo && 2 * j < hi) {
-          acc[j].x = __fadd_rn(acc[j].x, __uint_as_float(p[2 * j]));
-          acc[j].y = __fadd_rn(acc[j].y, __uint_as_float(p[2 * j + 1]));
+          uint64_t v;
+          asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(p[2 * j]), "r"(p[2 * j + 1]));
+          asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(v) : "l"(v), "l"(a2));
+          asm("mov.b64 {%0, %1}, %2;" : "=r"(p[2 * j]), "=r"(p[2 * j + 1]) : "l"(v));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < CW / 2; ++j) {
+        if (2 * j >= lo && 2 * j < hi) {
+          uint64_t v, c;
+          asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(p[2 * j]), "r"(p[2 * j + 1]));
+          asm("mov.b64 %0, {%1, %2};" : "=l"(c) : "r"(__float_as_uint(acc[j].x)), "r"(__float_as_uint(acc[j].y)));
+          asm("add.rn.f32x2 %0, %1, %2;" : "=l"(c) : "l"(c), "l"(v));
+          uint32_t x, y2;
+          asm("mov.b64 {%0, %1}, %2;" : "=r"(x), "=r"(y2) : "l"(c));
+          acc[j] = make_float2(__uint_as_float(x), __uint_as_float(y2));
         }
       }
     };
@@ -244,12 +277,26 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       const TileCoord tc = tile_coord(tile, num_m, num_n);
       const int row = tc.m_blk * kBlockM + q * 32 + lane;
-      const int col0 = tc.n_blk * kBlockN + cs * 32;
+      const int col0 = tc.n_blk * kBlockN + cs * CW;
       const float a_m = row < M ? __ldg(a_scale + row) : 0.0f;
-      float2 acc[16];
+      float2 acc[CW / 2];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) acc[j] = make_float2(0.0f, 0.0f);
-      uint32_t pa[32], pb[32];
+      for (int j = 0; j < CW / 2; ++j) acc[j] = make_float2(0.0f, 0.0f);
+      uint32_t pa[CW], pb[CW];
+      // CW columns of this warp's lane quarter -> registers (one or two 32-column loads)
+      auto load_partial = [&](uint32_t taddr, uint32_t (&dst)[CW]) {
+#pragma unroll
+        for (int i = 0; i < CW / 32; ++i) tmem_ld_32x32(taddr + i * 32, *reinterpret_cast<uint32_t(*)[32]>(&dst[i * 32]));
+      };
+      auto wait_partial = [&](uint32_t (&dst)[CW]) {
+        if constexpr (CW == 32) {
+          tmem_wait_ld_for(dst);
+        } else {
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < CW; ++i) asm volatile("" : "+r"(dst[i]));  // no use of the registers ahead of the wait
+        }
+      };
       // Per-partial hand-over: a buffer goes back to the MMA thread as soon as its 32 columns are in
       // registers; the load of partial i+1 is in flight while partial i is scaled and accumulated.
       auto next_buf = [&]() {
@@ -269,29 +316,29 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       ok = mbar_wait_a(tmem_full_a + pair * 8, pair_phase, status, abort_a, kTagTmemFull | pair);
       if (!ok) break;
       tc_fence_after();
-      tmem_ld_32x32(t_lane + pair * kBlockN, pa);
-      tmem_wait_ld_for(pa);
+      load_partial(t_lane + pair * kBlockN, pa);
+      wait_partial(pa);
       release_buf();
 #define ADG_STEP(cur, nxt, more)                                                                              \
   {                                                                                                           \
     bool issued = false;                                                                                      \
     if ((more) && mbar_test_wait_a(tmem_full_a + pair * 8, pair_phase)) {                                     \
       tc_fence_after();                                                                                       \
-      tmem_ld_32x32(t_lane + pair * kBlockN, nxt);                                                            \
+      load_partial(t_lane + pair * kBlockN, nxt);                                                             \
       issued = true;                                                                                          \
     }                                                                                                         \
     accumulate_part(cur, acc, a_m, 0, kSplit);                                                                \
     if (issued) {                                                                                             \
-      tmem_wait_ld_for(nxt);                                                                                  \
+      wait_partial(nxt);                                                                                      \
       release_buf();                                                                                          \
     }                                                                                                         \
-    accumulate_part(cur, acc, a_m, kSplit, 32);                                                               \
+    accumulate_part(cur, acc, a_m, kSplit, CW);                                                               \
     if ((more) && !issued) {                                                                                  \
       ok = mbar_wait_a(tmem_full_a + pair * 8, pair_phase, status, abort_a, kTagTmemFull | pair);             \
       if (!ok) break;                                                                                         \
       tc_fence_after();                                                                                       \
-      tmem_ld_32x32(t_lane + pair * kBlockN, nxt);                                                            \
-      tmem_wait_ld_for(nxt);                                                                                  \
+      load_partial(t_lane + pair * kBlockN, nxt);                                                             \
+      wait_partial(nxt);                                                                                      \
       release_buf();                                                                                          \
     }                                                                                                         \
   }
@@ -302,14 +349,14 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #undef ADG_STEP
       if (ok && row < M) {
         float* dst = y + static_cast<long>(row) * ldy + col0;
-        if (col0 + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        if (col0 + CW <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
+          for (int j4 = 0; j4 < CW / 4; ++j4) {
             reinterpret_cast<float4*>(dst)[j4] = make_float4(acc[2 * j4].x, acc[2 * j4].y, acc[2 * j4 + 1].x, acc[2 * j4 + 1].y);
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
+          for (int j = 0; j < CW / 2; ++j) {
             if (col0 + 2 * j < N) dst[2 * j] = acc[j].x;
             if (col0 + 2 * j + 1 < N) dst[2 * j + 1] = acc[j].y;
           }
@@ -327,17 +374,16 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 }  // namespace
 
 int init_gemm_o1_bf16_attributes() {
-  return check_cuda(
-      cudaFuncSetAttribute(gemm_o1_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
-      "cudaFuncSetAttribute(gemm_o1_bf16_kernel)");
+  return check_cuda(cudaFuncSetAttribute(gemm_o1_bf16_kernel<kColsPerEpiWarp>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+                    "cudaFuncSetAttribute(gemm_o1_bf16_kernel)");
 }
 
 int o1_bf16_block_n() { return kBlockN; }
 
 int run_gemm_o1_bf16(const GemmPlan& p, cudaStream_t stream) {
   if (p.variant != 1 || !p.o1_bf16) return fail("run_gemm_o1_bf16: plan is not an O1 BF16-operand plan");
-  gemm_o1_bf16_kernel<<<p.grid, kThreads, kSmemBytes, stream>>>(p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), p.y,
-                                                                p.range_flag, p.quiet_refusal, p.M, p.N, p.K, p.ldy, p.status);
+  gemm_o1_bf16_kernel<kColsPerEpiWarp><<<p.grid, EpiCfg<kColsPerEpiWarp>::kThreads, kSmemBytes, stream>>>(
+      p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), p.y, p.range_flag, p.quiet_refusal, p.M, p.N, p.K, p.ldy, p.status);
   return check_cuda(cudaGetLastError(), "gemm_o1_bf16_kernel launch");
 }
 
@@ -345,7 +391,7 @@ void describe_gemm_o1_bf16(PlanInfo* info) {
   info->symbol = "gemm_o1_bf16_kernel";
   info->mma_family = "tcgen05.mma.cta_group::1.kind::f16 (bf16 operands; exact integer partials)";
   info->tile_m = kBlockM, info->tile_n = kBlockN, info->stages = kStages, info->acc_stages = kBufs;
-  info->threads = kThreads, info->cluster = 1, info->mma_m = kBlockM, info->mma_n = kBlockN, info->mma_k = 16;
+  info->threads = EpiCfg<kColsPerEpiWarp>::kThreads, info->cluster = 1, info->mma_m = kBlockM, info->mma_n = kBlockN, info->mma_k = 16;
   info->persistent = 1;
 }
 

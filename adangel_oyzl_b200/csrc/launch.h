@@ -137,7 +137,6 @@ int plan_o0_fused(GemmPlan* plan, const void* a_int8, const void* a_scale, void*
                   void* ready, int M, int N, int K, int ldy);
 int plan_o2_fused(GemmPlan* plan, const void* a_int8, const void* a_scale, void* a_mxfp4, void* sfa_tiled, void* sf_natural,
                   const void* w_mxfp4, const void* sfb_tiled, float* y, void* ready, int M, int N, int K, int ldy);
-bool fusion_enabled();  // ADG_FUSE_A in the environment: 0 = callers of the *_linear entries get separate kernels
 int plan_o1_bf16(GemmPlan* plan, const void* a_bf16, const void* a_scale, const void* w_bf16, float* y,
                  const void* range_flag, int M, int N, int K, int ldy);
 int run_plan(const GemmPlan& plan, cudaStream_t stream);

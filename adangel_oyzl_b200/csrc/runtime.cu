@@ -332,11 +332,6 @@ int plan_o1x(GemmPlan* plan, const void* a_int8, const void* a_scale, const void
   return finish_plan(plan, block_n);
 }
 
-bool fusion_enabled() {
-  const char* e = getenv("ADG_FUSE_A");
-  return !(e != nullptr && e[0] == '0');
-}
-
 namespace {
 int finish_fused(GemmPlan* plan, const void* a_int8, const void* a_scale, void* a_out, void* ready) {
   if (plan->skinny) return fail("the decode-shape kernels do not convert their activations themselves");

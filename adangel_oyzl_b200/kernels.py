@@ -358,16 +358,17 @@ def o2_linear_noalloc_status(device=None):
 
 
 class FusedWorkspace:
-    """Buffers of the one-kernel steady-state passes :func:`o0_linear` / :func:`o2_linear` for up to
-    ``max_m`` rows of K elements: the converted operand, O2's tiled scales and the row counters (zeroed
-    once here; the kernels leave them zero)."""
+    """Buffers of the steady-state passes :func:`o0_linear` / :func:`o2_linear` for up to ``max_m`` rows of K
+    elements: the converted operand, O2's tiled scales and -- with ``fuse=True``, which selects the GEMM kernels
+    that convert A themselves -- the row counters (zeroed once here; the kernels leave them zero)."""
 
-    def __init__(self, variant: str, max_m: int, k: int, device, want_natural_scales: bool = False):
+    def __init__(self, variant: str, max_m: int, k: int, device, want_natural_scales: bool = False, fuse: bool = False):
         import torch
 
-        _require(variant in ("o0", "o2"), "fused passes exist for o0 and o2")
+        _require(variant in ("o0", "o2"), "steady-state passes exist for o0 and o2")
         self.variant, self.max_m, self.k = variant, max_m, k
-        self.counters = torch.zeros((int(_lib().adg_fused_workspace_bytes(max_m)) // 4,), dtype=torch.int32, device=device)
+        self.counters = (torch.zeros((int(_lib().adg_fused_workspace_bytes(max_m)) // 4,), dtype=torch.int32, device=device)
+                         if fuse else None)
         if variant == "o0":
             self.operand = torch.empty((max_m, k), dtype=torch.float16, device=device)
             self.sf_tiled = self.sf_natural = None
@@ -378,7 +379,8 @@ class FusedWorkspace:
 
 
 def o0_linear(a_int8, a_scale, w_fp16, workspace: FusedWorkspace, out=None):
-    """O0 steady-state pass (INT8 -> FP16 conversion inside the GEMM kernel for M > 64): ``adg_o0_linear``."""
+    """O0 steady-state pass, ``adg_o0_linear``: INT8 -> FP16 conversion and GEMM (inside one kernel when the
+    workspace was made with ``fuse=True`` and M > 64)."""
     import torch
 
     m, k = a_int8.shape
@@ -391,12 +393,14 @@ def o0_linear(a_int8, a_scale, w_fp16, workspace: FusedWorkspace, out=None):
     out, ldy = _output(out, m, n, dev)
     with torch.cuda.device(dev):
         _sm100._check(_lib().adg_o0_linear(a_int8.data_ptr(), a_scale.data_ptr(), w_fp16.data_ptr(), workspace.operand.data_ptr(),
-                                           workspace.counters.data_ptr(), out.data_ptr(), m, n, k, ldy, _stream(out)))
+                                           workspace.counters.data_ptr() if workspace.counters is not None else None,
+                                           out.data_ptr(), m, n, k, ldy, _stream(out)))
     return out
 
 
 def o2_linear(a_int8, a_scale, w_mxfp4, w_sf_tiled, workspace: FusedWorkspace, out=None):
-    """O2 steady-state pass (re-quantization inside the GEMM kernel for M > 64): ``adg_o2_linear``."""
+    """O2 steady-state pass, ``adg_o2_linear``: re-quantization and GEMM (inside one kernel when the workspace
+    was made with ``fuse=True`` and M > 64)."""
     import torch
 
     m, k = a_int8.shape
@@ -412,8 +416,8 @@ def o2_linear(a_int8, a_scale, w_mxfp4, w_sf_tiled, workspace: FusedWorkspace, o
     with torch.cuda.device(dev):
         _sm100._check(_lib().adg_o2_linear(
             a_int8.data_ptr(), a_scale.data_ptr(), w_mxfp4.data_ptr(), w_sf_tiled.data_ptr(), workspace.operand.data_ptr(),
-            workspace.sf_tiled.data_ptr(), nat.data_ptr() if nat is not None else None, workspace.counters.data_ptr(),
-            out.data_ptr(), m, n, k, ldy, _stream(out)))
+            workspace.sf_tiled.data_ptr(), nat.data_ptr() if nat is not None else None,
+            workspace.counters.data_ptr() if workspace.counters is not None else None, out.data_ptr(), m, n, k, ldy, _stream(out)))
     return out
 
 

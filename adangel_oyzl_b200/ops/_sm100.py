@@ -235,13 +235,14 @@ def kernel_metadata(variant: str, m: int, n: int, k: int, o1_bf16: bool = False,
 
 
 def benchmark(variant, mode, a_int8, a_scale, w_mxfp4, w_scale, warmup, repeats,
-              conversion_inner_repeats=DEFAULT_CONVERSION_INNER_REPEATS, *, fuse_activation=True,
+              conversion_inner_repeats=DEFAULT_CONVERSION_INNER_REPEATS, *, fuse_activation=False,
               o1_split_activation_stage=False):
     """One variant/mode under the reference's timing protocol (``adangel_benchmark_o{0,1,2}``).
 
     The positional signature is the reference's.  Keyword-only additions: ``fuse_activation`` (O0/O2, cold and
     steady-state modes, M > 64: the activation conversion runs inside the GEMM kernel, so the ``gemm`` stage is
-    that one kernel and ``activation_conversion`` is reported from its isolated batches only);
+    that one kernel and ``activation_conversion`` is reported from its isolated batches only; off by default:
+    the two-kernel sequence is faster at every measured shape);
     ``o1_split_activation_stage`` (O1 on BF16 operands: report the INT8 -> BF16 conversion as an
     ``activation_conversion`` stage instead of inside ``gemm``; off by default because the reference's O1 has
     no such stage).  ``variant="o1x"`` runs the exact-integer O1 variant; its result carries

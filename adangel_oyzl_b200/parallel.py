@@ -116,37 +116,32 @@ def shard_weights(w_mxfp4, w_scale, world_size: int, rank: int, variants=("o0", 
     return shard
 
 
-def _workspace(shard: ShardedWeights, variant: str, m: int, k: int, device):
+def _workspace(shard: ShardedWeights, variant: str, m: int, k: int, device, fuse: bool):
     from . import kernels
 
     if shard.workspaces is None:
         shard.workspaces = {}
-    ws = shard.workspaces.get(variant)
+    ws = shard.workspaces.get((variant, fuse))
     if ws is None or ws.max_m < m or ws.k != k:
-        ws = shard.workspaces[variant] = kernels.FusedWorkspace(variant, m, k, device)
+        ws = shard.workspaces[(variant, fuse)] = kernels.FusedWorkspace(variant, m, k, device, fuse=fuse)
     return ws
 
 
-def sharded_gemm(variant: str, a_int8, a_scale, shard: ShardedWeights, out=None, fused: bool = True):
-    """This rank's column block of Y for ``variant`` (activation conversion included).  O0 and O2 convert the
-    replicated A inside the GEMM kernel (``fused=False``: the conversion kernel first, then the GEMM)."""
+def sharded_gemm(variant: str, a_int8, a_scale, shard: ShardedWeights, out=None, fused: bool = False):
+    """This rank's column block of Y for ``variant`` (activation conversion included): the conversion of the
+    replicated A, then the GEMM (``fused=True``: O0 and O2 convert A inside the GEMM kernel)."""
     from . import kernels
 
     if shard.rows == 0:
         return out
     m, k = a_int8.shape
     if variant == "o0":
-        if fused:
-            return kernels.o0_linear(a_int8, a_scale, shard.w_fp16, _workspace(shard, "o0", m, k, a_int8.device), out=out)
-        return kernels.gemm_o0(kernels.int8_to_fp16(a_int8, a_scale), shard.w_fp16, out=out)
+        return kernels.o0_linear(a_int8, a_scale, shard.w_fp16, _workspace(shard, "o0", m, k, a_int8.device, fused), out=out)
     if variant == "o1":
         if getattr(shard, "o1", None) is not None:
             return kernels.o1_linear(a_int8, a_scale, shard.o1, out=out)
         return kernels.gemm_o1(a_int8, a_scale, shard.w_int8, shard.w_scale, out=out)
     if variant == "o2":
-        if fused:
-            return kernels.o2_linear(a_int8, a_scale, shard.w_mxfp4, shard.w_sf_tiled, _workspace(shard, "o2", m, k, a_int8.device),
-                                     out=out)
-        codes, _, sfa = kernels.o2_quantize_activation(a_int8, a_scale, want_natural=False)
-        return kernels.gemm_o2(codes, sfa, shard.w_mxfp4, shard.w_sf_tiled, out=out)
+        return kernels.o2_linear(a_int8, a_scale, shard.w_mxfp4, shard.w_sf_tiled, _workspace(shard, "o2", m, k, a_int8.device, fused),
+                                 out=out)
     raise ValueError(f"unknown variant: {variant}")

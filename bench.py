@@ -5,9 +5,9 @@
 
 Workload (N = 1): the canonical experiment M = N = K = 4096 with seeded synthetic inputs of the canonical
 distributions.  One *pass* is the steady state of all three variants on one batch of activations: O0 (INT8 ->
-FP16 conversion inside the FP16 GEMM kernel), O1 (INT8 -> BF16 conversion + the per-K32 recurrence on BF16
-operands, bit-identical to the INT8-operand kernel) and O2 (MXFP4 re-quantization inside the block-scaled GEMM
-kernel); the weight-side conversions are cached, as in the reference's ``steady_state`` mode.  One *step* is
+FP16 conversion + FP16 GEMM), O1 (INT8 -> BF16 conversion + the per-K32 recurrence on BF16 operands,
+bit-identical to the INT8-operand kernel) and O2 (MXFP4 re-quantization + block-scaled GEMM): six kernels; the
+weight-side conversions are cached, as in the reference's ``steady_state`` mode.  One *step* is
 ``passes_per_step`` passes, sized so that the K timed steps last at least two seconds: the sampled SM clocks
 and power then belong to the kernels, and ``value`` is a sustained figure.  The metric is equivalent TFLOP/s,
 ``2*M*N*K`` per variant and pass.  A short burst of K passes is timed as well (``config.burst``).  With N GPUs,
@@ -298,15 +298,16 @@ def sharded_block(dist, world: int, rank: int, dev) -> dict:
     flop = 2.0 * m * n * k
     o1_ms = timed(lambda: parallel.sharded_gemm("o1", a_int8, a_scale, shard, out=y), 1, 3)
     o2_ms = timed(lambda: parallel.sharded_gemm("o2", a_int8, a_scale, shard, out=y), 2, 10)
-    o2_two_kernel_ms = timed(lambda: parallel.sharded_gemm("o2", a_int8, a_scale, shard, out=y, fused=False), 2, 10)
+    o2_one_kernel_ms = timed(lambda: parallel.sharded_gemm("o2", a_int8, a_scale, shard, out=y, fused=True), 2, 10)
     o2_quantize_ms = timed(lambda: kernels.o2_quantize_activation(a_int8, a_scale, want_natural=False), 2, 10)
     out = {
         "shape": [m, n, k], "scaling": "strong", "n_gpus": world, "rows_of_w_per_rank": n1 - n0,
         "o1_ms": o1_ms, "o1_aggregate_tflops": flop / o1_ms / 1e9,
         "o2_ms": o2_ms, "aggregate_tflops": flop / o2_ms / 1e9,
-        "o2_two_kernel_ms": o2_two_kernel_ms, "o2_quantize_ms": o2_quantize_ms,
+        "o2_one_kernel_ms": o2_one_kernel_ms, "o2_quantize_ms": o2_quantize_ms,
         "o1_path": "adg_o1_linear (INT8 -> BF16 conversion + BF16-operand kernel, INT8-operand kernel behind it)",
-        "o2_path": "adg_o2_linear (re-quantization of the replicated A inside the GEMM kernel)",
+        "o2_path": "adg_o2_linear (re-quantization of the replicated A, then the GEMM; o2_one_kernel_ms: the GEMM kernel that "
+                   "re-quantizes A itself)",
         "timing": "CUDA events around back-to-back calls, barrier + synchronize on both sides, max over ranks",
         "gather_ms": None,
     }
@@ -375,8 +376,11 @@ def run_native_arm(args) -> None:
     a_bf16 = kernels.int8_to_bf16(a_int8, a_scale, o1_flag)
     o1_on_bf16 = int(o1_flag.item()) == 0
     w_sf_tiled = kernels.o2_tile_scales(w_scale)
-    ws0 = kernels.FusedWorkspace("o0", M, K, dev)
-    ws2 = kernels.FusedWorkspace("o2", M, K, dev)
+    ws0 = kernels.FusedWorkspace("o0", M, K, dev, fuse=True)  # the one-kernel passes, timed outside the step
+    ws2 = kernels.FusedWorkspace("o2", M, K, dev, fuse=True)
+    a16 = torch.empty((M, K), dtype=torch.float16, device=dev)
+    codes = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    sfa = torch.zeros((kernels.tiled_scale_bytes(M, K),), dtype=torch.uint8, device=dev)
 
     # per-variant outputs (distinct buffers so a pass's working set exceeds L2)
     y = {v: torch.empty((M, N_PER_GPU), dtype=torch.float32, device=dev) for v in VARIANTS}
@@ -385,8 +389,21 @@ def run_native_arm(args) -> None:
     sp = stream.cuda_stream
     check = _sm100._check
     o1_gemm_name = "o1_gemm_bf16" if o1_on_bf16 else "o1_gemm_i8"
-    o0_symbol = _sm100.plan_info("o0", M, N_PER_GPU, K, fused=True)["kernel_symbol"]
-    o2_symbol = _sm100.plan_info("o2", M, N_PER_GPU, K, fused=True)["kernel_symbol"]
+    o0_symbol = _sm100.plan_info("o0", M, N_PER_GPU, K)["kernel_symbol"]
+    o2_symbol = _sm100.plan_info("o2", M, N_PER_GPU, K)["kernel_symbol"]
+
+    def o0_conv():
+        check(lib.adg_int8_to_fp16(a_int8.data_ptr(), a_scale.data_ptr(), a16.data_ptr(), M, K, sp))
+
+    def o0_gemm():
+        check(lib.adg_gemm_o0(a16.data_ptr(), w_fp16.data_ptr(), y["o0"].data_ptr(), M, N_PER_GPU, K, N_PER_GPU, sp))
+
+    def o2_conv():
+        check(lib.adg_o2_quantize_activation(a_int8.data_ptr(), a_scale.data_ptr(), codes.data_ptr(), None, sfa.data_ptr(), M, K, sp))
+
+    def o2_gemm():
+        check(lib.adg_gemm_o2(codes.data_ptr(), sfa.data_ptr(), w_mxfp4.data_ptr(), w_sf_tiled.data_ptr(), y["o2"].data_ptr(),
+                              M, N_PER_GPU, K, N_PER_GPU, sp))
 
     def o0_pass():
         check(lib.adg_o0_linear(a_int8.data_ptr(), a_scale.data_ptr(), w_fp16.data_ptr(), ws0.operand.data_ptr(),
@@ -411,8 +428,8 @@ def run_native_arm(args) -> None:
                                 ws2.operand.data_ptr(), ws2.sf_tiled.data_ptr(), None, ws2.counters.data_ptr(),
                                 y["o2"].data_ptr(), M, N_PER_GPU, K, N_PER_GPU, sp))
 
-    launches = [("o0_linear", o0_pass)] + ([("o1_int8_to_bf16", o1_conv)] if o1_on_bf16 else []) + \
-               [(o1_gemm_name, o1_gemm), ("o2_linear", o2_pass)]
+    launches = [("o0_int8_to_fp16", o0_conv), ("o0_gemm_f16", o0_gemm)] + ([("o1_int8_to_bf16", o1_conv)] if o1_on_bf16 else []) + \
+               [(o1_gemm_name, o1_gemm), ("o2_quantize", o2_conv), ("o2_gemm_mxf4", o2_gemm)]
 
     def one_pass(events=None):
         for i, (_, fn) in enumerate(launches):
@@ -448,6 +465,12 @@ def run_native_arm(args) -> None:
     for _ in range(warmup):
         one_pass()
     kernels.check_status(dev)
+    if args.profile_pass:
+        # a small target for a profiler: the six kernels of one more pass, nothing else
+        one_pass()
+        kernels.check_status(dev)
+        print(json.dumps({"profile_pass": [name for name, _ in launches]}))
+        return
 
     # burst: K passes from a cool start (about 10 ms)
     burst_ms = timed_passes(args.steps) / args.steps
@@ -495,19 +518,12 @@ def run_native_arm(args) -> None:
         torch.cuda.synchronize(dev)
         return e0.elapsed_time(e1) / reps
 
-    a16 = torch.empty((M, K), dtype=torch.float16, device=dev)
-    codes = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
-    sfa = torch.zeros((kernels.tiled_scale_bytes(M, K),), dtype=torch.uint8, device=dev)
-    check(lib.adg_int8_to_fp16(a_int8.data_ptr(), a_scale.data_ptr(), a16.data_ptr(), M, K, sp))
-    check(lib.adg_o2_quantize_activation(a_int8.data_ptr(), a_scale.data_ptr(), codes.data_ptr(), None, sfa.data_ptr(), M, K, sp))
     burst_kernel_ms = {
-        "o0_linear": batched(lambda i: o0_pass()),
+        "o0_gemm_f16": batched(lambda i: o0_gemm()),
         o1_gemm_name: batched(lambda i: o1_gemm(), reps=10),
-        "o2_linear": batched(lambda i: o2_pass()),
-        "o0_gemm_f16": batched(lambda i: check(lib.adg_gemm_o0(a16.data_ptr(), w_fp16.data_ptr(), y["o0"].data_ptr(),
-                                                               M, N_PER_GPU, K, N_PER_GPU, sp))),
-        "o2_gemm_mxf4": batched(lambda i: check(lib.adg_gemm_o2(codes.data_ptr(), sfa.data_ptr(), w_mxfp4.data_ptr(),
-                                                                w_sf_tiled.data_ptr(), y["o2"].data_ptr(), M, N_PER_GPU, K, N_PER_GPU, sp))),
+        "o2_gemm_mxf4": batched(lambda i: o2_gemm()),
+        "o0_one_kernel": batched(lambda i: o0_pass()),
+        "o2_one_kernel": batched(lambda i: o2_pass()),
     }
     if o1_on_bf16:
         y1 = y["o1"].clone()
@@ -539,7 +555,7 @@ def run_native_arm(args) -> None:
         "mxfp4_to_int8": batched(lambda i: check(lib.adg_mxfp4_to_int8(
             w_rot[i % n_rot].data_ptr(), out_rot[i % n_rot].data_ptr(), N_PER_GPU, K, sp)), reps=50),
     }
-    del a_rot, out_rot, w_rot, a16, codes
+    del a_rot, out_rot, w_rot
     kernels.check_status(dev)
     torch.cuda.empty_cache()
 
@@ -556,14 +572,16 @@ def run_native_arm(args) -> None:
                   "mxfp4_to_fp16": N_PER_GPU * K // 2 + N_PER_GPU * K // 32 + 2 * N_PER_GPU * K,
                   "mxfp4_to_int8": N_PER_GPU * K // 2 + N_PER_GPU * K}
     # tensor peak per kernel: the measured BF16 cuBLAS figure times the MMA kind's nominal ratio to BF16
-    peak_mult = {"o0_linear": 1.0, "o0_gemm_f16": 1.0, "o1_gemm_bf16": 1.0, "o1_gemm_i8": 2.0, "o1x_gemm_i8": 2.0,
-                 "o2_linear": 4.0, "o2_gemm_mxf4": 4.0}
-    nominal = {"o0_linear": 2250.0, "o0_gemm_f16": 2250.0, "o1_gemm_bf16": 2250.0, "o1_gemm_i8": 4500.0, "o1x_gemm_i8": 4500.0,
-               "o2_linear": 9000.0, "o2_gemm_mxf4": 9000.0}
-    symbols = {"o0_linear": o0_symbol, "o2_linear": o2_symbol, "o1_gemm_bf16": "gemm_o1_bf16_kernel", "o1_gemm_i8": "gemm_o1_kernel",
-               "o0_gemm_f16": _sm100.plan_info("o0", M, N_PER_GPU, K)["kernel_symbol"],
-               "o2_gemm_mxf4": _sm100.plan_info("o2", M, N_PER_GPU, K)["kernel_symbol"], "o1x_gemm_i8": "gemm_acc_kernel<1>",
-               "o1_int8_to_bf16": "int8_to_bf16_kernel"}
+    peak_mult = {"o0_one_kernel": 1.0, "o0_gemm_f16": 1.0, "o1_gemm_bf16": 1.0, "o1_gemm_i8": 2.0, "o1x_gemm_i8": 2.0,
+                 "o2_one_kernel": 4.0, "o2_gemm_mxf4": 4.0}
+    nominal = {"o0_one_kernel": 2250.0, "o0_gemm_f16": 2250.0, "o1_gemm_bf16": 2250.0, "o1_gemm_i8": 4500.0, "o1x_gemm_i8": 4500.0,
+               "o2_one_kernel": 9000.0, "o2_gemm_mxf4": 9000.0}
+    symbols = {"o0_gemm_f16": o0_symbol, "o2_gemm_mxf4": o2_symbol, "o1_gemm_bf16": "gemm_o1_bf16_kernel", "o1_gemm_i8": "gemm_o1_kernel",
+               "o0_one_kernel": _sm100.plan_info("o0", M, N_PER_GPU, K, fused=True)["kernel_symbol"],
+               "o2_one_kernel": _sm100.plan_info("o2", M, N_PER_GPU, K, fused=True)["kernel_symbol"], "o1x_gemm_i8": "gemm_acc_kernel<1>",
+               "o0_int8_to_fp16": "int8_to_fp16_kernel", "o1_int8_to_bf16": "int8_to_bf16_kernel", "o2_quantize": "o2_quantize_kernel"}
+    step_conv_bytes = {"o0_int8_to_fp16": conv_bytes["int8_to_fp16"], "o1_int8_to_bf16": conv_bytes["int8_to_bf16"],
+                       "o2_quantize": conv_bytes["o2_quantize"]}
     kernels_out = {}
     for name in sorted(set(sustained_kernel_ms) | set(burst_kernel_ms)):
         entry = {"kernel_symbol": symbols.get(name)}
@@ -576,18 +594,21 @@ def run_native_arm(args) -> None:
                                   "frac_of_nominal": ach / nominal[name]}
         else:
             ms = sustained_kernel_ms.get(name)
-            nbytes = conv_bytes["int8_to_bf16"]
-            entry["sustained"] = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_measured": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+            nbytes = step_conv_bytes[name]
+            entry["sustained"] = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_measured": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                  "note": "inside the step, launch ramp and tail included; conversions_batched has the isolated figure"}
         kernels_out[name] = entry
     if o1_on_bf16:
         kernels_out["o1_gemm_i8"]["note"] = f"INT8-operand O1 kernel, timed outside the step; bit-identical output: {o1_same_bits}"
+    for name in ("o0_one_kernel", "o2_one_kernel"):
+        kernels_out[name]["note"] = "activation conversion inside the GEMM kernel (adg_o0_linear / adg_o2_linear with row counters): timed outside the step"
     kernels_out["o1x_gemm_i8"]["note"] = (f"exact-integer O1 variant, timed outside the step, never part of `value`; ineligible W rows: "
                                           f"{o1x_rows} of {N_PER_GPU}; max relative difference from literal O1: {o1x_max_rel:.2e}")
     conversions_out = {name: {"batched_ms": ms, "gbs": conv_bytes[name] / (ms * 1e-3) / 1e9,
                               "frac_of_measured_hbm": conv_bytes[name] / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                               "algorithmic_bytes": conv_bytes[name]} for name, ms in conv_ms.items()}
 
-    dominant = max(sustained_kernel_ms, key=sustained_kernel_ms.get)
+    dominant = max((k_ for k_ in sustained_kernel_ms if k_ in peak_mult), key=sustained_kernel_ms.get)
     d_ms = sustained_kernel_ms[dominant]
     d_peak = peaks["bf16_tflops_sustained"] * peak_mult.get(dominant, 1.0)
     d_ach = FLOP_PER_VARIANT / (d_ms * 1e-3) / 1e12
@@ -688,6 +709,8 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("native", "reference"), default="native")
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU timing in the native arm")
+    parser.add_argument("--profile-pass", action="store_true",
+                        help="run the warm-up passes and ONE more pass, then exit: the target of the ncu captures under profiles/")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

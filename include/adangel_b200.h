@@ -172,17 +172,19 @@ int adg_o1_linear(const void* a_int8, const void* a_scale, const void* w_int8, c
 int adg_gemm_o2(const void* a_mxfp4, const void* a_sf_tiled, const void* w_mxfp4, const void* w_sf_tiled, float* y,
                 int M, int N, int K, int ldy, void* stream);
 
-/* O0 / O2 steady-state pass in one call: activation conversion + GEMM.  For M > 64 the conversion runs
- * INSIDE the GEMM kernel: a fourth warp group of every CTA converts rows of A_int8 into the operand buffer
- * (FP16, or MXFP4 codes + tiled scales) while the tensor cores work, and the kernel's TMA producer waits on
- * per-row-block counters before it loads a row block -- the conversion kernel that the reference launches in
- * front of every GEMM (csrc/sm120/o0_gemm.cu:432-470, o2_cutlass.cu:451-472) leaves the critical path and
- * the results are bit-identical to the two-kernel sequence.  For M <= 64, with row_counters == NULL, or with
- * ADG_FUSE_A=0 in the environment, the two kernels run one after the other.
+/* O0 / O2 steady-state pass in one call: activation conversion + GEMM, the sequence the reference runs for every
+ * steady-state pass (csrc/sm120/o0_gemm.cu:432-470, o2_cutlass.cu:451-472).  With row_counters == NULL (the
+ * default, and the faster path at every measured shape) the conversion kernel runs first and the GEMM behind
+ * it.  With row_counters given and M > 64 the conversion runs INSIDE the GEMM kernel: a fourth warp group of
+ * every CTA converts rows of A_int8 into the operand buffer (FP16, or MXFP4 codes + tiled scales) while the
+ * tensor cores work, and the kernel's TMA producer waits on per-row-block counters before it loads a row
+ * block; the results are bit-identical to the two-kernel sequence.  Measured on B200 the four converter
+ * warps a GEMM CTA can host are not enough to stream A (O2 at 4096^3: 67 us against 50 us for the two
+ * kernels; O0: 117 against 109), so the one-kernel form is kept as an option, not as the default.
  *   - a_fp16_workspace [M,K] FP16 / a_mxfp4_workspace [M,K/2] + a_sf_tiled_workspace
  *     (adg_o2_tiled_scale_bytes(M,K), zero-filled once by the caller) receive the converted operand;
  *     a_sf_natural ([M,K/32], may be NULL) the natural-layout scales.
- *   - row_counters: adg_fused_workspace_bytes(M) bytes, zero-filled once by the caller; the kernel leaves
+ *   - row_counters (optional): adg_fused_workspace_bytes(M) bytes, zero-filled once by the caller; the kernel leaves
  *     them zero again.  After a call that reported a device-side error, zero them before the next call.
  *     Calls that share counters or workspaces must not overlap on the GPU. */
 int64_t adg_fused_workspace_bytes(int64_t M);
