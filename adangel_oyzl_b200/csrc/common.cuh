@@ -47,6 +47,15 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// Every kernel of the steady-state pass is launched with programmatic stream serialization (launch.h,
+// launch_overlapped): its CTAs may become resident while the kernel in front of it in the stream is still
+// draining.  pdl_wait() blocks until that kernel has completed and its writes are visible; a kernel calls it
+// before it touches global memory.  pdl_launch_dependents() lets the kernel behind this one start to become
+// resident.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier -------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

@@ -13,6 +13,7 @@
 //   o2_tile_scales     O2 weight-scale re-layout (reference csrc/sm120/o2_cutlass.cu:261-274)
 #include <cuda_bf16.h>
 
+#include "common.cuh"
 #include "convert_device.cuh"
 #include "launch.h"
 
@@ -39,6 +40,8 @@ constexpr int kQuantCtasPerSm = 4;  // the re-quantizer needs up to 64 registers
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) mxfp4_to_fp16_kernel(const uint32_t* __restrict__ packed,
                                                                  const uint8_t* __restrict__ scales,
                                                                  uint4* __restrict__ out, uint32_t words) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (uint32_t base = blockIdx.x * kChunk + threadIdx.x; base - threadIdx.x < words; base += gridDim.x * kChunk) {
     uint32_t w[kUnroll];
     uint32_t sc[kUnroll];
@@ -89,6 +92,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) int8_to_fp16_kernel(cons
                                                                 const float* __restrict__ row_scale,
                                                                 uint4* __restrict__ out, uint32_t octs,
                                                                 uint32_t octs_per_row, uint32_t magic) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (uint32_t base = blockIdx.x * kChunk + threadIdx.x; base - threadIdx.x < octs; base += gridDim.x * kChunk) {
     uint2 v[kUnroll];
     float s[kUnroll];
@@ -115,6 +120,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) mxfp4_to_bf16_scaled_ker
                                                                         const uint8_t* __restrict__ scales,
                                                                         uint4* __restrict__ out, uint32_t words,
                                                                         uint32_t* __restrict__ range_flag) {
+  pdl_launch_dependents();
+  pdl_wait();
   bool bad = false;
   for (uint32_t base = blockIdx.x * kChunk + threadIdx.x; base - threadIdx.x < words; base += gridDim.x * kChunk) {
     uint32_t w[kUnroll];
@@ -154,6 +161,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) int8_to_bf16_kernel(cons
                                                                 const float* __restrict__ row_scale,
                                                                 uint4* __restrict__ out, uint32_t octs, uint32_t rows,
                                                                 uint32_t* __restrict__ range_flag) {
+  pdl_launch_dependents();
+  pdl_wait();
   bool bad = false;
   for (uint32_t r = blockIdx.x * kThreads + threadIdx.x; r < rows; r += gridDim.x * kThreads) {
     const float s = __ldg(row_scale + r);
@@ -188,6 +197,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) int8_to_bf16_kernel(cons
 // Sixteen elements (64-bit load, 128-bit store) per item; `pairs` = rows*K/16.
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) mxfp4_to_int8_kernel(const uint2* __restrict__ packed,
                                                                  uint4* __restrict__ out, uint32_t pairs) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (uint32_t base = blockIdx.x * kChunk + threadIdx.x; base - threadIdx.x < pairs; base += gridDim.x * kChunk) {
     uint2 v[kUnroll];
 #pragma unroll
@@ -218,6 +229,8 @@ __global__ void __launch_bounds__(kThreads, kQuantCtasPerSm) o2_quantize_kernel(
                                                                uint2* __restrict__ codes, uint8_t* __restrict__ sf_natural,
                                                                uint8_t* __restrict__ sf_tiled, uint32_t halves,
                                                                uint32_t halves_per_row, uint32_t magic, int katoms) {
+  pdl_launch_dependents();
+  pdl_wait();
   const bool words_ok = (halves_per_row & 7u) == 0;  // K/32 a multiple of 4: whole scale words per row
   for (uint32_t base = blockIdx.x * kChunk + threadIdx.x; base - threadIdx.x < halves; base += gridDim.x * kChunk) {
     uint4 v[kUnroll];
@@ -260,6 +273,8 @@ __global__ void __launch_bounds__(kThreads, kQuantCtasPerSm) o2_quantize_kernel(
 __global__ void __launch_bounds__(kThreads) o2_tile_scales_kernel(const uint8_t* __restrict__ natural,
                                                                   uint32_t* __restrict__ tiled, int rows, int groups,
                                                                   int padded_rows, int katoms) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long idx = static_cast<long>(blockIdx.x) * kThreads + threadIdx.x;
   if (idx >= static_cast<long>(padded_rows) * katoms) return;
   const int row = static_cast<int>(idx / katoms);
@@ -288,10 +303,10 @@ int launch_mxfp4_to_fp16(const void* packed, const void* scales, void* out, long
   const long words = rows * k / 8;
   if (words == 0) return 0;
   if (words > kMaxItems) return too_large();
-  mxfp4_to_fp16_kernel<<<grid_for(words, kChunk), kThreads, 0, stream>>>(
+  const cudaError_t err = launch_overlapped(mxfp4_to_fp16_kernel, dim3(grid_for(words, kChunk)), dim3(kThreads), 0, stream, 1,
       static_cast<const uint32_t*>(packed), static_cast<const uint8_t*>(scales), static_cast<uint4*>(out),
       static_cast<uint32_t>(words));
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(err);
 }
 
 int launch_int8_to_fp16(const void* in, const void* row_scale, void* out, long rows, long k, cudaStream_t stream) {
@@ -299,10 +314,10 @@ int launch_int8_to_fp16(const void* in, const void* row_scale, void* out, long r
   if (octs == 0) return 0;
   if (octs > kMaxItems) return too_large();
   const uint32_t per_row = static_cast<uint32_t>(k / 8);
-  int8_to_fp16_kernel<<<grid_for(octs, kChunk), kThreads, 0, stream>>>(
+  const cudaError_t err = launch_overlapped(int8_to_fp16_kernel, dim3(grid_for(octs, kChunk)), dim3(kThreads), 0, stream, 1,
       static_cast<const uint2*>(in), static_cast<const float*>(row_scale), static_cast<uint4*>(out),
       static_cast<uint32_t>(octs), per_row, fast_div_magic(per_row));
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(err);
 }
 
 int launch_mxfp4_to_bf16_scaled(const void* packed, const void* scales, void* out, void* range_flag, long rows, long k,
@@ -310,10 +325,10 @@ int launch_mxfp4_to_bf16_scaled(const void* packed, const void* scales, void* ou
   const long words = rows * k / 8;
   if (words == 0) return 0;
   if (words > kMaxItems) return too_large();
-  mxfp4_to_bf16_scaled_kernel<<<grid_for(words, kChunk), kThreads, 0, stream>>>(
+  const cudaError_t err = launch_overlapped(mxfp4_to_bf16_scaled_kernel, dim3(grid_for(words, kChunk)), dim3(kThreads), 0, stream, 1,
       static_cast<const uint32_t*>(packed), static_cast<const uint8_t*>(scales), static_cast<uint4*>(out),
       static_cast<uint32_t>(words), static_cast<uint32_t*>(range_flag));
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(err);
 }
 
 int launch_int8_to_bf16(const void* in, const void* row_scale, void* out, void* range_flag, long rows, long k,
@@ -321,19 +336,19 @@ int launch_int8_to_bf16(const void* in, const void* row_scale, void* out, void* 
   const long octs = rows * k / 8;
   if (octs == 0) return 0;
   if (octs > kMaxItems) return too_large();
-  int8_to_bf16_kernel<<<grid_for(octs, kChunk), kThreads, 0, stream>>>(
+  const cudaError_t err = launch_overlapped(int8_to_bf16_kernel, dim3(grid_for(octs, kChunk)), dim3(kThreads), 0, stream, 1,
       static_cast<const uint2*>(in), static_cast<const float*>(row_scale), static_cast<uint4*>(out),
       static_cast<uint32_t>(octs), static_cast<uint32_t>(rows), static_cast<uint32_t*>(range_flag));
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(err);
 }
 
 int launch_mxfp4_to_int8(const void* packed, void* out, long rows, long k, cudaStream_t stream) {
   const long pairs = rows * k / 16;
   if (pairs == 0) return 0;
   if (pairs > kMaxItems) return too_large();
-  mxfp4_to_int8_kernel<<<grid_for(pairs, kChunk), kThreads, 0, stream>>>(
+  const cudaError_t err = launch_overlapped(mxfp4_to_int8_kernel, dim3(grid_for(pairs, kChunk)), dim3(kThreads), 0, stream, 1,
       static_cast<const uint2*>(packed), static_cast<uint4*>(out), static_cast<uint32_t>(pairs));
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(err);
 }
 
 int launch_o2_quantize(const void* a_int8, const void* row_scale, void* codes, void* sf_natural, void* sf_tiled,
@@ -342,11 +357,11 @@ int launch_o2_quantize(const void* a_int8, const void* row_scale, void* codes, v
   if (halves == 0) return 0;
   if (halves > kMaxItems) return too_large();
   const uint32_t per_row = static_cast<uint32_t>(k / 16);
-  o2_quantize_kernel<<<grid_for(halves, kChunk), kThreads, 0, stream>>>(
+  const cudaError_t err = launch_overlapped(o2_quantize_kernel, dim3(grid_for(halves, kChunk)), dim3(kThreads), 0, stream, 1,
       static_cast<const uint4*>(a_int8), static_cast<const float*>(row_scale), static_cast<uint2*>(codes),
       static_cast<uint8_t*>(sf_natural), static_cast<uint8_t*>(sf_tiled), static_cast<uint32_t>(halves), per_row,
       fast_div_magic(per_row), static_cast<int>(tiled_scale_katoms(k)));
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(err);
 }
 
 int launch_o2_tile_scales(const void* natural, void* tiled, long rows, long k, cudaStream_t stream) {

@@ -188,10 +188,12 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     tmem_alloc(tmem_base_slot, Cfg::kTmemCols);
     tmem_relinquish();
   }
+  pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
+  pdl_wait();  // barriers, tensor memory and descriptors are set up: now wait for the kernel in front of this one
 
   // Warp group 0: the one-thread roles.  (FUSED: each warp group starts its branch with the register
   // re-balancing, all four warps of the group at the same instruction.)
@@ -475,11 +477,11 @@ int launch(const GemmPlan& p, cudaStream_t stream) {
     conv.sf_tiled = static_cast<uint8_t*>(const_cast<void*>(p.sfa));
     conv.ready = p.fused_ready;
   }
-  gemm_acc_kernel<KIND, BLOCK_N, FUSED><<<p.grid, FUSED ? kFusedThreads : kAccThreads, Cfg::kSmemBytes, stream>>>(
-      p.tm_a, p.tm_b, p.tm_y, static_cast<const uint8_t*>(p.sfa), static_cast<const uint8_t*>(p.sfb), p.y, p.M, p.N,
-      p.K, p.ldy, p.use_tma_store, p.status, conv, static_cast<const float*>(p.a_scale),
-      static_cast<const float*>(p.col_factor));
-  return check_cuda(cudaGetLastError(), "gemm_acc_kernel launch");
+  return check_cuda(launch_overlapped(gemm_acc_kernel<KIND, BLOCK_N, FUSED>, dim3(p.grid), dim3(FUSED ? kFusedThreads : kAccThreads),
+                                      Cfg::kSmemBytes, stream, 1, p.tm_a, p.tm_b, p.tm_y, static_cast<const uint8_t*>(p.sfa),
+                                      static_cast<const uint8_t*>(p.sfb), p.y, p.M, p.N, p.K, p.ldy, p.use_tma_store, p.status, conv,
+                                      static_cast<const float*>(p.a_scale), static_cast<const float*>(p.col_factor)),
+                    "gemm_acc_kernel launch");
 }
 
 template <int KIND, bool FUSED>

@@ -246,11 +246,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     tmem_alloc_pair(tmem_base_slot, 512);
     tmem_relinquish_pair();
   }
+  pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();  // the peer's barriers are initialised before anything of ours reaches them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
+  pdl_wait();  // set-up done: now wait for the kernel in front of this one in the stream
 
   // Warp group 0: the one-thread roles.  (FUSED: each warp group starts its branch with the register
   // re-balancing, all four warps of the group at the same instruction.)
@@ -507,18 +509,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
 template <int KIND, bool FUSED>
 int launch_pair(const GemmPlan& p, cudaStream_t stream) {
-  cudaLaunchConfig_t config{};
-  config.gridDim = dim3(static_cast<unsigned>(p.grid));
-  config.blockDim = dim3(FUSED ? kFusedThreads : kThreads);
-  config.dynamicSmemBytes = PairCfg<KIND>::kSmemBytes;
-  config.stream = stream;
-  cudaLaunchAttribute attr{};
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  config.attrs = &attr;
-  config.numAttrs = 1;
   FusedConvert conv{};
   if constexpr (FUSED) {
     conv.a_int8 = static_cast<const uint4*>(p.fused_a_int8);
@@ -528,8 +518,9 @@ int launch_pair(const GemmPlan& p, cudaStream_t stream) {
     conv.sf_tiled = static_cast<uint8_t*>(const_cast<void*>(p.sfa));
     conv.ready = p.fused_ready;
   }
-  return check_cuda(cudaLaunchKernelEx(&config, gemm_pair_kernel<KIND, FUSED>, p.tm_a, p.tm_b, p.tm_y, p.tm_sfa, p.tm_sfb,
-                                       p.y, p.M, p.N, p.K, p.ldy, p.use_tma_store, p.status, conv),
+  return check_cuda(launch_overlapped(gemm_pair_kernel<KIND, FUSED>, dim3(static_cast<unsigned>(p.grid)),
+                                      dim3(FUSED ? kFusedThreads : kThreads), PairCfg<KIND>::kSmemBytes, stream, 2, p.tm_a, p.tm_b,
+                                      p.tm_y, p.tm_sfa, p.tm_sfb, p.y, p.M, p.N, p.K, p.ldy, p.use_tma_store, p.status, conv),
                     "gemm_pair_kernel launch");
 }
 

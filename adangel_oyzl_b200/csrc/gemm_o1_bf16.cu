@@ -104,6 +104,8 @@ __global__ void __launch_bounds__(EpiCfg<CW>::kThreads, 1)
 gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const float* __restrict__ a_scale, float* __restrict__ y, const uint32_t* __restrict__ range_flag,
                     int quiet_refusal, int M, int N, int K, int ldy, uint32_t* status) {
+  pdl_launch_dependents();
+  pdl_wait();  // the range flag below is written by the conversion kernel in front of this one
   // operands outside the exact range: refuse, before any barrier or tensor memory exists -- loudly (an
   // error status for the next check) unless the caller watches the flag itself and falls back
   if (range_flag != nullptr) {
@@ -382,9 +384,10 @@ int o1_bf16_block_n() { return kBlockN; }
 
 int run_gemm_o1_bf16(const GemmPlan& p, cudaStream_t stream) {
   if (p.variant != 1 || !p.o1_bf16) return fail("run_gemm_o1_bf16: plan is not an O1 BF16-operand plan");
-  gemm_o1_bf16_kernel<kColsPerEpiWarp><<<p.grid, EpiCfg<kColsPerEpiWarp>::kThreads, kSmemBytes, stream>>>(
-      p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), p.y, p.range_flag, p.quiet_refusal, p.M, p.N, p.K, p.ldy, p.status);
-  return check_cuda(cudaGetLastError(), "gemm_o1_bf16_kernel launch");
+  return check_cuda(launch_overlapped(gemm_o1_bf16_kernel<kColsPerEpiWarp>, dim3(p.grid), dim3(EpiCfg<kColsPerEpiWarp>::kThreads),
+                                      kSmemBytes, stream, 1, p.tm_a, p.tm_b, static_cast<const float*>(p.a_scale), p.y, p.range_flag,
+                                      p.quiet_refusal, p.M, p.N, p.K, p.ldy, p.status),
+                    "gemm_o1_bf16_kernel launch");
 }
 
 void describe_gemm_o1_bf16(PlanInfo* info) {

@@ -17,6 +17,38 @@ int fail(const std::string& message);
 int check_cuda(cudaError_t err, const char* what);
 const char* last_error_cstr();
 
+// ---- launches ------------------------------------------------------------------------------------
+// Launch with programmatic stream serialization (and, optionally, clusters of `cluster_x` CTAs): the kernel may
+// become resident while its predecessor in the stream drains; it calls pdl_wait() (common.cuh) before it
+// touches global memory.  ADG_PDL=0 in the environment launches the ordinary way.
+bool overlapped_launches_enabled();
+template <typename... KArgs, typename... Args>
+cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_x,
+                              Args&&... args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  unsigned n = 0;
+  if (overlapped_launches_enabled()) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_x > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = static_cast<unsigned>(cluster_x);
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  config.attrs = attrs;
+  config.numAttrs = n;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- per-device context -------------------------------------------------------------------------
 struct DeviceCtx {
   int device = -1;

@@ -24,6 +24,14 @@ PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 
 const char* last_error_cstr() { return g_last_error.c_str(); }
 
+bool overlapped_launches_enabled() {
+  static const bool enabled = [] {
+    const char* e = getenv("ADG_PDL");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return enabled;
+}
+
 void set_error(const std::string& message) { g_last_error = message; }
 
 int fail(const std::string& message) {
