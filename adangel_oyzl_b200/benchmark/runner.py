@@ -172,6 +172,7 @@ def run_experiment(config_path, output_dir, *, sample_limit=None, warmup_overrid
     write_environment(output_dir / "environment.json")
 
     max_cv = float(timing["max_cv_percent"])
+    flush_l2 = bool(timing.get("flush_l2", False))  # decode shapes: operands from HBM, not from a warm L2
     modes = list(config["modes"])
     variants = list(config["variants"])
     formal = bool(config["experiment"].get("formal", False))
@@ -184,7 +185,7 @@ def run_experiment(config_path, output_dir, *, sample_limit=None, warmup_overrid
                 for variant in variants:
                     payload = benchmark_variant(inputs, variant, mode, warmup, repeats, backend="native",
                                                 conversion_inner_repeats=conversion_inner_repeats,
-                                                formal=formal and shape == (4096, 4096, 4096))
+                                                formal=formal and shape == (4096, 4096, 4096), flush_l2=flush_l2)
                     _validate_benchmark_payload(payload, repeats, mode, conversion_inner_repeats)
                     summaries, stable = _summarize_timings(payload["timings_ms"], max_cv)
                     for stage, stats in summaries.items():
@@ -206,6 +207,7 @@ def run_experiment(config_path, output_dir, *, sample_limit=None, warmup_overrid
                         "mse_vs_o0": None,
                         "kernel": payload.get("kernel"),
                         "timing_method": payload.get("timing_method"),
+                        "l2_flushed": flush_l2,
                         "stable_cv": stable,
                         "valid": stable,
                         "roofline": _roofline(variant, summaries, m, n, k,

@@ -427,8 +427,12 @@ int adg_benchmark(adg_bench_args* a) {
   const size_t per_iter = seq.size() + 1;
   EventList events;
   if (int rc = events.grow(per_iter * static_cast<size_t>(a->repeats))) return rc;
+  const bool flush = (a->flags & ADG_BENCH_FLUSH_L2) != 0 && a->l2_flush != nullptr && a->l2_flush_bytes > 0;
   for (int it = 0; it < a->repeats; ++it) {
     cudaEvent_t* e = &events.ev[per_iter * it];
+    if (flush)
+      if (int rc = check_cuda(cudaMemsetAsync(a->l2_flush, it & 0xff, static_cast<size_t>(a->l2_flush_bytes), stream), "L2 flush"))
+        return rc;
     if (int rc = check_cuda(cudaEventRecord(e[0], stream), "cudaEventRecord")) return rc;
     for (size_t s = 0; s < seq.size(); ++s) {
       if ((*seq[s].second)()) return fail(std::string("timed launch failed: ") + last_error_cstr());

@@ -3,11 +3,14 @@
 // With so few activation rows the 128-row tile of the regular kernel would be almost empty and only
 // N/256 CTAs would stream W, so the operands are swapped: the tensor core computes
 // Y^T[n, m] = W[n, :] . A[m, :]^T with the 128 MMA rows taken from W and the MMA N extent equal to M
-// rounded up to 16.  One CTA per 128-row block of W walks all of K, accumulates in tensor memory
-// and writes its block of Y.  (Splitting K over several CTAs with a last-arriver reduction was
-// measured and removed: a launch of this kernel costs about 6.5 us before the first K slab is
-// consumed and 0.3 us per slab after that, and the hand-off of the partials cost more than the
-// slabs it saved.)
+// rounded up to 16.  A 128-row block of W is handled by a cluster of S CTAs (S = 1, 2 or 4, chosen so
+// that the grid covers the GPU once): each walks 1/S of K, accumulates in its tensor memory, and the
+// partial sums meet in the first CTA's shared memory (distributed shared memory: plain remote stores
+// into the stage buffers that its finished MMAs no longer need), which adds them in rank order --
+// deterministic -- and writes the block of Y.  For O2 the accumulation order is free, so the split
+// changes results only within the rounding of the FP32 sums.  (A launch of this kernel costs about
+// 6.5 us before the first K slab is consumed and 0.3 us per slab after that; an earlier split over
+// independent CTAs with a last-arriver reduction through global memory cost more than it saved.)
 //
 // Scale factors: W's tiled scales are the MMA's A-side scales (128-row atoms as stored), A's tiled
 // scales are the B-side scales (row block 0 of A's tiled buffer).
@@ -33,6 +36,28 @@ constexpr int kSfColsPerStage = 16;  // per K-atom: 4 (W side) + 4 (A side); two
 constexpr int kTmemCols = 128;
 
 enum : uint32_t { kTagEmpty = 0x2100, kTagFull = 0x2200, kTagAcc = 0x2300, kTagSfFull = 0x2400 };
+constexpr int kMaxSplit = 4;
+static_assert((kMaxSplit - 1) * kRows * kMaxM * 4 <= kStages * kStageBytes, "the partial sums of the other ranks fit the stage buffers");
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t local_addr, uint32_t rank, const uint32_t (&v)[4]) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
+               : "memory");
+}
 
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
@@ -51,9 +76,12 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const WaitEnv env{status, abort_flag};
-  const int nb = blockIdx.x;      // 128-row block of W
+  const int split = static_cast<int>(cluster_size());
+  const int rank = static_cast<int>(cluster_rank());
+  const int nb = blockIdx.x / split;  // 128-row block of W
   const int num_kb_total = (K + 255) / 256;
-  const int kb0 = 0, kb1 = num_kb_total;
+  const int per_rank = (num_kb_total + split - 1) / split;
+  const int kb0 = min(rank * per_rank, num_kb_total), kb1 = min(kb0 + per_rank, num_kb_total);
   const int katoms = static_cast<int>(((K / 32 + 7) / 8) * 2);
   const uint32_t m_pad = static_cast<uint32_t>((M + 15) / 16 * 16);
 
@@ -155,13 +183,17 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         }
       }
     }
-  } else {
-    // epilogue: lane = one row n of W, registers = the M outputs of that row
-    const int q = warp & 3;
-    const int n = nb * kRows + q * 32 + lane;
-    bool ok = kb1 > kb0 ? mbar_wait(acc_bar, 0, env, kTagAcc) : true;
-    uint32_t r[2][32];
-    if (ok) {
+  }
+
+  // ---- every thread: the cluster meets twice (a cluster of one passes straight through) ----------------
+  // epilogue warps 2-5: lane = one row n of W, registers = the M outputs of that row
+  const bool epi = warp >= 2 && warp < 6;
+  uint32_t r[2][32];
+  bool have = false;
+  const int q = warp & 3;
+  if (epi) {
+    have = kb1 > kb0 ? mbar_wait(acc_bar, 0, env, kTagAcc) : true;
+    if (have) {
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
       if (kb1 > kb0) {
@@ -173,11 +205,52 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[0][j] = r[1][j] = 0u;
       }
-      if (n < N) {
+    }
+  }
+  if (split > 1) {
+    // 1st meeting: every CTA's MMAs are done (its epilogue warps have seen the accumulator complete), so the
+    // first CTA's stage buffers are free to receive the partials.  (__syncthreads first: the one-thread roles'
+    // warps arrive reconverged.)
+    __syncthreads();
+    cluster_barrier();
+    // layout in the first CTA: [rank - 1][m / 4][row 0..127][4 floats]
+    const int row = q * 32 + lane;
+    const uint32_t m_groups = (static_cast<uint32_t>(M) + 3u) / 4u;
+    if (epi && rank != 0) {
+      const uint32_t base = smem_u32(smem) + static_cast<uint32_t>(rank - 1) * (kRows * kMaxM * 4);
 #pragma unroll
-        for (int m = 0; m < kMaxM; ++m)
-          if (m < M) y[static_cast<long>(m) * ldy + n] = __uint_as_float(r[m >> 5][m & 31]);
+      for (int g = 0; g < kMaxM / 4; ++g) {
+        if (static_cast<uint32_t>(g) < m_groups) {
+          const uint32_t v[4] = {r[g >> 3][(g & 7) * 4], r[g >> 3][(g & 7) * 4 + 1], r[g >> 3][(g & 7) * 4 + 2], r[g >> 3][(g & 7) * 4 + 3]};
+          st_cluster_v4(base + (static_cast<uint32_t>(g) * kRows + row) * 16u, 0u, v);
+        }
       }
+    }
+    // 2nd meeting: the partials have landed
+    cluster_barrier();
+    if (epi && rank == 0 && have) {
+      for (int other = 1; other < split; ++other) {
+        const float4* part = reinterpret_cast<const float4*>(smem + static_cast<size_t>(other - 1) * (kRows * kMaxM * 4));
+#pragma unroll
+        for (int g = 0; g < kMaxM / 4; ++g) {
+          if (static_cast<uint32_t>(g) < m_groups) {
+            const float4 p = part[g * kRows + row];
+            uint32_t* dst = &r[g >> 3][(g & 7) * 4];
+            dst[0] = __float_as_uint(__uint_as_float(dst[0]) + p.x);
+            dst[1] = __float_as_uint(__uint_as_float(dst[1]) + p.y);
+            dst[2] = __float_as_uint(__uint_as_float(dst[2]) + p.z);
+            dst[3] = __float_as_uint(__uint_as_float(dst[3]) + p.w);
+          }
+        }
+      }
+    }
+  }
+  if (epi && have && rank == 0) {
+    const int n = nb * kRows + q * 32 + lane;
+    if (n < N) {
+#pragma unroll
+      for (int m = 0; m < kMaxM; ++m)
+        if (m < M) y[static_cast<long>(m) * ldy + n] = __uint_as_float(r[m >> 5][m & 31]);
     }
   }
 
@@ -215,15 +288,33 @@ int plan_o2_skinny(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, c
   if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_mxfp4, M, kbytes, kbytes, kMaxM, 128))
     return rc;
   plan->tm_y = plan->tm_a;
-  plan->grid = (N + kRows - 1) / kRows;
+  // split K over a cluster of 1, 2 or 4 CTAs: as many as keep the grid within what the GPU holds at once (two
+  // CTAs per SM fit) and leave every rank at least two K slabs
+  const int blocks = (N + kRows - 1) / kRows;
+  const int slabs = (K + 255) / 256;
+  int split = 1;
+  while (split < kMaxSplit && blocks * split * 2 <= 2 * ctx->sm_count && slabs / (split * 2) >= 2) split *= 2;
+  plan->grid = blocks * split;
+  plan->grid_y = split;  // cluster size
   return 0;
 }
 
 int run_gemm_o2_skinny(const GemmPlan& p, cudaStream_t stream) {
-  gemm_o2_skinny_kernel<<<p.grid, kThreads, kSmemBytes, stream>>>(
-      p.tm_b, p.tm_a, static_cast<const uint8_t*>(p.sfb), static_cast<const uint8_t*>(p.sfa), p.y, p.M, p.N, p.K, p.ldy,
-      p.status);
-  return check_cuda(cudaGetLastError(), "gemm_o2_skinny_kernel launch");
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(static_cast<unsigned>(p.grid));
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = static_cast<unsigned>(p.grid_y);
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  config.attrs = &attr;
+  config.numAttrs = 1;
+  return check_cuda(cudaLaunchKernelEx(&config, gemm_o2_skinny_kernel, p.tm_b, p.tm_a, static_cast<const uint8_t*>(p.sfb),
+                                       static_cast<const uint8_t*>(p.sfa), p.y, p.M, p.N, p.K, p.ldy, p.status),
+                    "gemm_o2_skinny_kernel launch");
 }
 
 void describe_gemm_o2_skinny(int M, PlanInfo* info) {

@@ -118,7 +118,7 @@ struct GemmPlan {
   float* y = nullptr;
   int32_t* partial_dump = nullptr;  // O1 debug: INT32 partials [M, N, K/32]
   // decode-sized O1/O2 (M <= 64): operand-swapped kernels; tm_a = A map, tm_b = W map; `grid_y`
-  // is the number of 16-row slices of A (O1 only)
+  // is the number of 16-row slices of A (O1) or the number of CTAs that share a W row block's K extent (O2)
   int skinny = 0, grid_y = 1;
   int o1_bf16 = 0;                       // O1 with BF16 operands (weight scale folded into W)
   const uint32_t* range_flag = nullptr;  // O1 BF16: device word set by the operand conversions

@@ -21,6 +21,8 @@ _MODES = {"conversion_only": 0, "compute_only": 1, "cold": 2, "steady_state": 3}
 _VARIANTS = {"o0": 0, "o1": 1, "o2": 2, "o1x": 3}  # o1x: the exact-integer O1 variant, only ever by name
 BENCH_FUSE_ACTIVATION = 1
 BENCH_O1_SPLIT_ACTIVATION = 2
+BENCH_FLUSH_L2 = 4
+L2_FLUSH_BYTES = 256 << 20  # more than the 126 MB L2 of a B200
 PLAN_O1_BF16, PLAN_FUSED_ACTIVATION, PLAN_PARTIAL_DUMP = 1, 2, 4
 _STAGE_BITS = (("weight_conversion", 1), ("activation_conversion", 2), ("gemm", 4), ("total", 8))
 
@@ -41,6 +43,7 @@ class BenchArgs(ctypes.Structure):
         ("conv_weight_bf16", c_void_p), ("conv_act_bf16", c_void_p), ("range_flag", c_void_p),
         ("flags", c_uint32), ("row_counters", c_void_p),
         ("o1x_col_factor", c_void_p), ("o1x_workspace", c_void_p), ("o1x_w_int8", c_void_p),
+        ("l2_flush", c_void_p), ("l2_flush_bytes", c_int64),
     ]
 
 
@@ -236,7 +239,7 @@ def kernel_metadata(variant: str, m: int, n: int, k: int, o1_bf16: bool = False,
 
 def benchmark(variant, mode, a_int8, a_scale, w_mxfp4, w_scale, warmup, repeats,
               conversion_inner_repeats=DEFAULT_CONVERSION_INNER_REPEATS, *, fuse_activation=False,
-              o1_split_activation_stage=False):
+              o1_split_activation_stage=False, flush_l2=False):
     """One variant/mode under the reference's timing protocol (``adangel_benchmark_o{0,1,2}``).
 
     The positional signature is the reference's.  Keyword-only additions: ``fuse_activation`` (O0/O2, cold and
@@ -245,7 +248,9 @@ def benchmark(variant, mode, a_int8, a_scale, w_mxfp4, w_scale, warmup, repeats,
     the two-kernel sequence is faster at every measured shape);
     ``o1_split_activation_stage`` (O1 on BF16 operands: report the INT8 -> BF16 conversion as an
     ``activation_conversion`` stage instead of inside ``gemm``; off by default because the reference's O1 has
-    no such stage).  ``variant="o1x"`` runs the exact-integer O1 variant; its result carries
+    no such stage); ``flush_l2`` (overwrite a 256 MiB buffer before every directly timed iteration, outside its
+    events, so that operands come from HBM: how the weight-streaming decode shapes are measured against the HBM
+    roofline -- the reference's protocol leaves the L2 warm).  ``variant="o1x"`` runs the exact-integer O1 variant; its result carries
     ``o1x_ineligible_rows``."""
     import torch
 
@@ -317,7 +322,11 @@ def benchmark(variant, mode, a_int8, a_scale, w_mxfp4, w_scale, warmup, repeats,
     args.conv_weight_bf16 = conv_weight_bf16.data_ptr() if conv_weight_bf16 is not None else None
     args.conv_act_bf16 = conv_act_bf16.data_ptr() if conv_act_bf16 is not None else None
     args.range_flag = range_flag.data_ptr() if range_flag is not None else None
-    args.flags = (BENCH_FUSE_ACTIVATION if fused else 0) | (BENCH_O1_SPLIT_ACTIVATION if o1_split_activation_stage else 0)
+    l2_flush = torch.empty((L2_FLUSH_BYTES,), dtype=torch.uint8, device=device) if flush_l2 else None
+    args.flags = ((BENCH_FUSE_ACTIVATION if fused else 0) | (BENCH_O1_SPLIT_ACTIVATION if o1_split_activation_stage else 0)
+                  | (BENCH_FLUSH_L2 if flush_l2 else 0))
+    args.l2_flush = l2_flush.data_ptr() if l2_flush is not None else None
+    args.l2_flush_bytes = L2_FLUSH_BYTES if l2_flush is not None else 0
     args.row_counters = row_counters.data_ptr() if row_counters is not None else None
     args.o1x_col_factor = o1x_col_factor.data_ptr() if o1x_col_factor is not None else None
     args.o1x_workspace = o1x_workspace.data_ptr() if o1x_workspace is not None else None
@@ -349,7 +358,8 @@ def benchmark(variant, mode, a_int8, a_scale, w_mxfp4, w_scale, warmup, repeats,
         "converted_weight": converted_weight,
         "converted_activation": converted_activation,
         "timings_ms": timings,
-        "timing_method": _timing_metadata(mode, conversion_inner_repeats),
+        "timing_method": {**_timing_metadata(mode, conversion_inner_repeats),
+                          "l2": "flushed before every directly timed iteration" if flush_l2 else "as the previous iteration left it"},
         "kernel": kernel_metadata(variant, m, n, k, o1_bf16=range_flag is not None and int(range_flag.item()) == 0,
                                   fused=fused),
     }

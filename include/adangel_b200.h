@@ -297,6 +297,10 @@ typedef struct adg_bench_args {
   void* o1x_col_factor; /* float [N] */
   void* o1x_workspace;  /* adg_o1x_workspace_bytes(N) */
   void* o1x_w_int8;     /* int8 [N,K]: the literal path's weights */
+  /* ADG_BENCH_FLUSH_L2: a device buffer larger than the L2 that is overwritten before every directly timed
+   * iteration (outside its events), so that the iteration's operands come from HBM */
+  void* l2_flush;
+  int64_t l2_flush_bytes;
 } adg_bench_args;
 
 /* cold / steady_state of O0 and O2 run adg_o0_linear / adg_o2_linear's fused kernel: the `gemm` stage is
@@ -306,6 +310,11 @@ typedef struct adg_bench_args {
 /* O1 on BF16 operands: report the INT8 -> BF16 activation conversion as a stage of its own instead of
  * inside `gemm` (the reference's O1 has no activation stage, tests/integration/test_sm120_o1.py:86-94). */
 #define ADG_BENCH_O1_SPLIT_ACTIVATION 2u
+/* Cold operands: overwrite l2_flush (more than the L2's size) before every directly timed iteration.  The
+ * reference's protocol leaves the L2 as the previous iteration left it (docs/experiment_protocol.md:25-42),
+ * which for decode-sized problems means W is served from the L2; this flag is how the weight-streaming
+ * decode shapes are measured against the HBM roofline. */
+#define ADG_BENCH_FLUSH_L2 4u
 
 /* Runs the reference's timing protocol for one variant and mode (warm-up, `repeats` directly timed
  * iterations with CUDA events, conversions additionally timed as isolated batches of

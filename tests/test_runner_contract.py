@@ -82,7 +82,7 @@ def test_run_and_analyze_with_stubbed_native(tmp_path, monkeypatch):
 
     from adangel_oyzl_b200.analysis import generate_report
 
-    def fake_benchmark(inputs, variant, mode, warmup, repeats, backend="native", conversion_inner_repeats=100, formal=True):
+    def fake_benchmark(inputs, variant, mode, warmup, repeats, backend="native", conversion_inner_repeats=100, formal=True, flush_l2=False):
         payload = _payload(mode, repeats, conversion_inner_repeats, variant)
         m, n, _ = inputs.shape
         payload["output"] = torch.full((m, n), {"o0": 1.0, "o1": 1.001, "o2": 1.1}[variant])
@@ -134,7 +134,7 @@ def test_run_from_prepared_directory_with_stubbed_native(tmp_path, monkeypatch):
 
     seen = []
 
-    def fake_benchmark(inputs, variant, mode, warmup, repeats, backend="native", conversion_inner_repeats=100, formal=True):
+    def fake_benchmark(inputs, variant, mode, warmup, repeats, backend="native", conversion_inner_repeats=100, formal=True, flush_l2=False):
         seen.append((inputs.sample_id, inputs.shape))
         payload = _payload(mode, repeats, conversion_inner_repeats, variant)
         payload["output"] = torch.ones((inputs.shape[0], inputs.shape[1]))
