@@ -259,6 +259,64 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
+// ---- copy issue by a converged warp ---------------------------------------------------------------
+// A single thread inside a divergent branch needs 100 - 160 cycles per copy instruction and about as
+// much again per mbarrier operation, so a one-thread producer cannot start more than one stage per
+// 500 - 1000 cycles.  The same instructions issued by a converged warp, with one lane elected inside
+// the instruction sequence, cost about half of that (operands stay in uniform registers).  All 32
+// lanes must call these functions together.
+__device__ __forceinline__ void mbar_expect_tx_elect(uint32_t bar, uint32_t bytes) {
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "@P mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n"
+      "}\n" ::"r"(bar), "r"(bytes)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_elect(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "@P cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      "}\n" ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load_elect(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "@P cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+      "}\n" ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+// Bounded wait on one mbarrier phase by a converged warp; the result is the same in every lane.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitEnv& env, uint32_t tag) {
+  if (__any_sync(0xFFFFFFFFu, mbar_test_wait_a(bar, parity))) return true;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!__any_sync(0xFFFFFFFFu, mbar_test_wait_a(bar, parity))) {
+    if ((++spins & 0x3FFu) == 0) {
+      if (__any_sync(0xFFFFFFFFu, *env.abort != 0u)) return false;
+      if (__any_sync(0xFFFFFFFFu, global_timer_ns() - t0 > kWaitTimeoutNs)) {
+        if ((threadIdx.x & 31) == 0) {
+          *env.abort = 1;
+          if (atomicCAS(env.status, 0u, static_cast<uint32_t>(kStatusWaitTimeout)) == 0u) {
+            env.status[1] = tag;
+            env.status[2] = blockIdx.x;
+            env.status[3] = parity;
+          }
+        }
+        __syncwarp();
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_group_read() {
@@ -438,6 +496,65 @@ __device__ __forceinline__ void umma_mxf4(uint32_t d_tmem, uint64_t adesc, uint6
 // lanes 0..31 and replicates it into the other three 32-lane quarters.
 __device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+// ---- tensor-core instructions issued by a converged warp -----------------------------------------
+// Like the copy helpers above: all 32 lanes call, one elected lane issues.  elect.sync chooses the
+// lowest active lane, i.e. the same lane every time, so that a tcgen05.commit follows the MMAs and
+// copies of its own thread.
+__device__ __forceinline__ void umma_f16_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, P;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "@P tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_i8_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, P;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "@P tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_mxf4_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate, uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, P;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "@P tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "@P tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+      "}\n" ::"r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_elect(uint32_t taddr, uint64_t sdesc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "@P tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n"
+      "}\n" ::"r"(taddr), "l"(sdesc)
+      : "memory");
 }
 
 }  // namespace adg

@@ -142,6 +142,9 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 int use_tma_store, uint32_t* status, const FusedConvert conv, const float* __restrict__ row_factor,
                 const float* __restrict__ col_factor) {
   using Cfg = AccCfg<KIND, BLOCK_N>;
+  // Without the in-kernel converters warp 3 is free: it issues the scale-factor copies of the O2 stages,
+  // so that neither producer warp has more than two or three copies to start per stage.
+  constexpr bool kSplitProducer = Cfg::kScaled && !FUSED;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = smem + Cfg::kStages * Cfg::kStageBytes;
@@ -167,7 +170,7 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], kSplitProducer ? 2 : 1);
       mbar_init(&empty_bar[s], 1);
       mbar_init(&sf_full_bar[s], 1);
     }
@@ -202,73 +205,100 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
   }
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------------------
-    if (lane == 0) {
+    if constexpr (!FUSED) {
+      // the whole warp walks the loop converged and one elected lane issues each copy
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      uint32_t seen_rows = 0;  // FUSED: the counter of this tile's row block as read one tile earlier
+      const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         const TileCoord tc = tile_coord(tile, num_m, num_n);
-        if constexpr (FUSED) {
-          // the row block's operand is being written by the converter warps of all CTAs; its counter was
-          // requested while the previous tile's loads were issued, so a finished block costs no round trip
-          const uint32_t need = static_cast<uint32_t>(min(kBlockM, M - tc.m_blk * kBlockM));
-          if (seen_rows < need) {
-            ok = wait_rows_ready(conv.ready + tc.m_blk, need, env, kTagRowsReady);
-            if (!ok) break;
-          }
-          fence_proxy_async_all();
-          const int next_tile = tile + static_cast<int>(gridDim.x);
-          if (next_tile < num_tiles) seen_rows = ld_acquire_gpu(conv.ready + tile_coord(next_tile, num_m, num_n).m_blk);
-        }
         for (int kb = 0; kb < num_kb; ++kb) {
-          ok = role_wait<FUSED>(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage);
+          ok = mbar_wait_warp(empty0 + stage * 8, phase ^ 1u, env, kTagEmpty | stage);
           if (!ok) break;
-          uint8_t* st = smem + stage * Cfg::kStageBytes;
-          mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          const uint32_t st = smem0 + stage * Cfg::kStageBytes;
+          const uint32_t bar = full0 + stage * 8;
+          mbar_expect_tx_elect(bar, kSplitProducer ? Cfg::kTileA + Cfg::kTileB : Cfg::kStageBytes);
           const int x = kb * (KIND == 0 ? 64 : 128);  // tensor-map elements: halves or bytes
-          tma_load_2d(st, &tm_a, &full_bar[stage], x, tc.m_blk * kBlockM);
-          tma_load_2d(st + Cfg::kTileA, &tm_b, &full_bar[stage], x, tc.n_blk * BLOCK_N);
-          if constexpr (Cfg::kScaled) {
-            uint8_t* sfa_s = st + Cfg::kTileA + Cfg::kTileB;
-            uint8_t* sfb_s = sfa_s + Cfg::kSfa;
-            bulk_load(sfa_s, sfa + (static_cast<long>(tc.m_blk) * katoms + kb * 2) * 512, 1024, &full_bar[stage]);
-#pragma unroll
-            for (int rb = 0; rb < BLOCK_N / 128; ++rb) {
-              const long row_blk = static_cast<long>(tc.n_blk) * (BLOCK_N / 128) + rb;
-              bulk_load(sfb_s + rb * 1024, sfb + (row_blk * katoms + kb * 2) * 512, 1024, &full_bar[stage]);
-            }
-          }
+          tma_load_2d_elect(st, &tm_a, bar, x, tc.m_blk * kBlockM);
+          tma_load_2d_elect(st + Cfg::kTileA, &tm_b, bar, x, tc.n_blk * BLOCK_N);
           if (++stage == Cfg::kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
       }
+    } else {
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        uint32_t seen_rows = 0;  // FUSED: the counter of this tile's row block as read one tile earlier
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+          const TileCoord tc = tile_coord(tile, num_m, num_n);
+          if constexpr (FUSED) {
+            // the row block's operand is being written by the converter warps of all CTAs; its counter was
+            // requested while the previous tile's loads were issued, so a finished block costs no round trip
+            const uint32_t need = static_cast<uint32_t>(min(kBlockM, M - tc.m_blk * kBlockM));
+            if (seen_rows < need) {
+              ok = wait_rows_ready(conv.ready + tc.m_blk, need, env, kTagRowsReady);
+              if (!ok) break;
+            }
+            fence_proxy_async_all();
+            const int next_tile = tile + static_cast<int>(gridDim.x);
+            if (next_tile < num_tiles) seen_rows = ld_acquire_gpu(conv.ready + tile_coord(next_tile, num_m, num_n).m_blk);
+          }
+          for (int kb = 0; kb < num_kb; ++kb) {
+            ok = role_wait<FUSED>(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage);
+            if (!ok) break;
+            uint8_t* st = smem + stage * Cfg::kStageBytes;
+            mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+            const int x = kb * (KIND == 0 ? 64 : 128);  // tensor-map elements: halves or bytes
+            tma_load_2d(st, &tm_a, &full_bar[stage], x, tc.m_blk * kBlockM);
+            tma_load_2d(st + Cfg::kTileA, &tm_b, &full_bar[stage], x, tc.n_blk * BLOCK_N);
+            if constexpr (Cfg::kScaled) {
+              uint8_t* sfa_s = st + Cfg::kTileA + Cfg::kTileB;
+              uint8_t* sfb_s = sfa_s + Cfg::kSfa;
+              bulk_load(sfa_s, sfa + (static_cast<long>(tc.m_blk) * katoms + kb * 2) * 512, 1024, &full_bar[stage]);
+#pragma unroll
+              for (int rb = 0; rb < BLOCK_N / 128; ++rb) {
+                const long row_blk = static_cast<long>(tc.n_blk) * (BLOCK_N / 128) + rb;
+                bulk_load(sfb_s + rb * 1024, sfb + (row_blk * katoms + kb * 2) * 512, 1024, &full_bar[stage]);
+              }
+            }
+            if (++stage == Cfg::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -----------------------------------------------
-    if (lane == 0) {
+    if constexpr (!FUSED) {
+      // converged warp, one elected lane per instruction
       int stage = 0;
       uint32_t phase = 0;
       int local_tile = 0;
       bool ok = true;
+      const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+      const uint32_t sf_full0 = smem_u32(sf_full_bar), tfull0 = smem_u32(tmem_full_bar), tempty0 = smem_u32(tmem_empty_bar);
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
         const int acc = local_tile % Cfg::kAccStages;
         const uint32_t acc_phase = static_cast<uint32_t>(local_tile / Cfg::kAccStages) & 1u;
-        ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, env, kTagTmemEmpty | acc);
+        ok = mbar_wait_warp(tempty0 + acc * 8, acc_phase ^ 1u, env, kTagTmemEmpty | acc);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
         for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | stage);
+          ok = mbar_wait_warp(full0 + stage * 8, phase, env, kTagFull | stage);
           if (!ok) break;
-          tc_fence_after();
-          const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t st = smem0 + stage * Cfg::kStageBytes;
           const uint64_t adesc = make_desc_sw128(st);
           const uint64_t bdesc = make_desc_sw128(st + Cfg::kTileA);
           if constexpr (Cfg::kScaled) {
-            ok = mbar_wait(&sf_full_bar[stage], phase, env, kTagSfFull | stage);
+            ok = mbar_wait_warp(sf_full0 + stage * 8, phase, env, kTagSfFull | stage);
             if (!ok) break;
             tc_fence_after();
             const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
@@ -277,36 +307,123 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             for (int ks = 0; ks < 4; ++ks) {
               const uint32_t sf_id = (ks & 1) * 2;
               const uint32_t idesc = make_idesc_mxf4(kBlockM, BLOCK_N, sf_id, sf_id);
-              umma_mxf4(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u,
-                        sfa_t + (ks >> 1) * 4, sfb_t + (ks >> 1) * (BLOCK_N / 32));
+              umma_mxf4_elect(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u,
+                              sfa_t + (ks >> 1) * 4, sfb_t + (ks >> 1) * (BLOCK_N / 32));
             }
           } else {
+            tc_fence_after();
             if constexpr (KIND == 1) {
               constexpr uint32_t idesc = make_idesc(2, kFmtS8, kFmtS8, kBlockM, BLOCK_N);
 #pragma unroll
-              for (int ks = 0; ks < 4; ++ks) {
-                umma_i8(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
-              }
+              for (int ks = 0; ks < 4; ++ks) umma_i8_elect(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
             } else {
               constexpr uint32_t idesc = make_idesc(1, kFmtF16, kFmtF16, kBlockM, BLOCK_N);
 #pragma unroll
-              for (int ks = 0; ks < 4; ++ks) {
-                umma_f16(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
-              }
+              for (int ks = 0; ks < 4; ++ks) umma_f16_elect(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
             }
           }
-          umma_commit(&empty_bar[stage]);  // the stage may be refilled once these MMAs have read it
+          umma_commit_elect(empty0 + stage * 8);  // the stage may be refilled once these MMAs have read it
           if (++stage == Cfg::kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit(&tmem_full_bar[acc]);
+        if (ok) umma_commit_elect(tfull0 + acc * 8);
+      }
+    } else {
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        int local_tile = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+          const int acc = local_tile % Cfg::kAccStages;
+          const uint32_t acc_phase = static_cast<uint32_t>(local_tile / Cfg::kAccStages) & 1u;
+          ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, env, kTagTmemEmpty | acc);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+          for (int kb = 0; kb < num_kb; ++kb) {
+            ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | stage);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
+            const uint64_t adesc = make_desc_sw128(st);
+            const uint64_t bdesc = make_desc_sw128(st + Cfg::kTileA);
+            if constexpr (Cfg::kScaled) {
+              ok = mbar_wait(&sf_full_bar[stage], phase, env, kTagSfFull | stage);
+              if (!ok) break;
+              tc_fence_after();
+              const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
+              const uint32_t sfb_t = sfa_t + 8;
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks) {
+                const uint32_t sf_id = (ks & 1) * 2;
+                const uint32_t idesc = make_idesc_mxf4(kBlockM, BLOCK_N, sf_id, sf_id);
+                umma_mxf4(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u,
+                          sfa_t + (ks >> 1) * 4, sfb_t + (ks >> 1) * (BLOCK_N / 32));
+              }
+            } else {
+              if constexpr (KIND == 1) {
+                constexpr uint32_t idesc = make_idesc(2, kFmtS8, kFmtS8, kBlockM, BLOCK_N);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                  umma_i8(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
+                }
+              } else {
+                constexpr uint32_t idesc = make_idesc(1, kFmtF16, kFmtF16, kBlockM, BLOCK_N);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                  umma_f16(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
+                }
+              }
+            }
+            umma_commit(&empty_bar[stage]);  // the stage may be refilled once these MMAs have read it
+            if (++stage == Cfg::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          if (ok) umma_commit(&tmem_full_bar[acc]);
+        }
       }
     }
   } else if (warp == kSfWarp) {
     // ------------------------------- scale-factor copier (O2) -----------------------------------
-    if constexpr (Cfg::kScaled) {
+    if constexpr (Cfg::kScaled && !FUSED) {
+      // converged warp, one elected lane per instruction
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(full_bar), sf_full0 = smem_u32(sf_full_bar);
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          // the stage's data has landed; its tensor-memory scale columns were last read by MMAs
+          // that completed before the stage was handed back to the producer
+          ok = mbar_wait_warp(full0 + stage * 8, phase, env, kTagFull | 0x80 | stage);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sfa_s = smem0 + stage * Cfg::kStageBytes + Cfg::kTileA + Cfg::kTileB;
+          const uint32_t sfb_s = sfa_s + Cfg::kSfa;
+          const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
+          const uint32_t sfb_t = sfa_t + 8;
+#pragma unroll
+          for (int ka = 0; ka < 2; ++ka) {
+            tmem_cp_32x128b_warpx4_elect(sfa_t + ka * 4, make_desc_sf(sfa_s + ka * 512));
+#pragma unroll
+            for (int rb = 0; rb < BLOCK_N / 128; ++rb) {
+              tmem_cp_32x128b_warpx4_elect(sfb_t + ka * (BLOCK_N / 32) + rb * 4, make_desc_sf(sfb_s + rb * 1024 + ka * 512));
+            }
+          }
+          umma_commit_elect(sf_full0 + stage * 8);
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    if constexpr (Cfg::kScaled && FUSED) {
       if (lane == 0) {
         int stage = 0;
         uint32_t phase = 0;
@@ -341,6 +458,33 @@ gemm_acc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       }
     }
   } else if (warp == kPublishWarp) {
+    if constexpr (kSplitProducer) {
+      // ------------------------------- scale-factor producer (O2) -------------------------------
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, num_m, num_n);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait_warp(empty0 + stage * 8, phase ^ 1u, env, kTagEmpty | 0x40 | stage);
+          if (!ok) break;
+          const uint32_t sfa_s = smem0 + stage * Cfg::kStageBytes + Cfg::kTileA + Cfg::kTileB;
+          const uint32_t bar = full0 + stage * 8;
+          mbar_expect_tx_elect(bar, Cfg::kSfa + Cfg::kSfb);
+          bulk_load_elect(sfa_s, sfa + (static_cast<long>(tc.m_blk) * katoms + kb * 2) * 512, 1024, bar);
+#pragma unroll
+          for (int rb = 0; rb < BLOCK_N / 128; ++rb) {
+            const long row_blk = static_cast<long>(tc.n_blk) * (BLOCK_N / 128) + rb;
+            bulk_load_elect(sfa_s + Cfg::kSfa + rb * 1024, sfb + (row_blk * katoms + kb * 2) * 512, 1024, bar);
+          }
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
     // ------------------------------- row publisher (FUSED) -------------------------------------
     if constexpr (FUSED) {
       if (lane == 0 && !publish_rows_role(conv, M, blockIdx.x, gridDim.x, smem_u32(conv_done_slot), abort_flag, kWaitTimeoutNs)) {

@@ -29,7 +29,7 @@ constexpr int kTileA = kMaxM * 128;
 constexpr int kSf = 1024;       // two 512-byte atoms (8 K32 blocks) for each side
 constexpr int kStageBytes = kTileW + kTileA + 2 * kSf;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
-constexpr int kThreads = 224;   // warp 0 producer, warp 1 MMA, warps 2-5 epilogue, warp 6 scale-factor copier
+constexpr int kThreads = 256;   // warps 0 and 7 producers (W side, A side), warp 1 MMA, warps 2-5 epilogue, warp 6 scale-factor copier
 constexpr int kAccCols = 64;
 constexpr int kSfColBase = kAccCols;
 constexpr int kSfColsPerStage = 16;  // per K-atom: 4 (W side) + 4 (A side); two K-atoms per stage
@@ -87,7 +87,7 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], 2);  // one arrival per producer warp
       mbar_init(&empty_bar[s], 1);
       mbar_init(&sf_full_bar[s], 1);
     }
@@ -108,79 +108,83 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
-  if (warp == 0) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage)) break;
-        uint8_t* st = smem + stage * kStageBytes;
-        mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
-        tma_load_2d(st, &tm_w, &full_bar[stage], kb * 128, nb * kRows);
-        tma_load_2d(st + kTileW, &tm_a, &full_bar[stage], kb * 128, 0);
-        bulk_load(st + kTileW + kTileA, sf_w + (static_cast<long>(nb) * katoms + kb * 2) * 512, kSf, &full_bar[stage]);
-        bulk_load(st + kTileW + kTileA + kSf, sf_a + static_cast<long>(kb * 2) * 512, kSf, &full_bar[stage]);
-        if (++stage == kStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
+  // The one-instruction-at-a-time roles run as converged warps with one elected lane per instruction:
+  // a lone thread inside a divergent branch needs 100 - 160 cycles per copy or MMA instruction, which
+  // made the producer (four copies per stage) the slowest link of the chain.  The copies of a stage
+  // are split over two warps for the same reason.
+  const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+  const uint32_t sf_full0 = smem_u32(sf_full_bar);
+  if (warp == 0 || warp == 7) {
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int kb = kb0; kb < kb1; ++kb) {
+      if (!mbar_wait_warp(empty0 + stage * 8, phase ^ 1u, env, kTagEmpty | stage)) break;
+      const uint32_t st = smem0 + stage * kStageBytes;
+      const uint32_t bar = full0 + stage * 8;
+      if (warp == 0) {
+        mbar_expect_tx_elect(bar, kTileW + kSf);
+        tma_load_2d_elect(st, &tm_w, bar, kb * 128, nb * kRows);
+        bulk_load_elect(st + kTileW + kTileA, sf_w + (static_cast<long>(nb) * katoms + kb * 2) * 512, kSf, bar);
+      } else {
+        mbar_expect_tx_elect(bar, kTileA + kSf);
+        tma_load_2d_elect(st + kTileW, &tm_a, bar, kb * 128, 0);
+        bulk_load_elect(st + kTileW + kTileA + kSf, sf_a + static_cast<long>(kb * 2) * 512, kSf, bar);
+      }
+      if (++stage == kStages) {
+        stage = 0;
+        phase ^= 1u;
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int kb = kb0; kb < kb1; ++kb) {
-        // the scale-factor warp has copied this stage's scales into tensor memory (which also
-        // means the stage's operand tiles have landed)
-        ok = mbar_wait(&sf_full_bar[stage], phase, env, kTagSfFull | stage);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t st = smem_u32(smem + stage * kStageBytes);
-        const uint64_t wdesc = make_desc_sw128(st);
-        const uint64_t adesc = make_desc_sw128(st + kTileW);
-        const uint32_t sfw_t = tmem_base + kSfColBase + stage * kSfColsPerStage;  // MMA A-side scales (W)
-        const uint32_t sfa_t = sfw_t + 8;                                          // MMA B-side scales (A)
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int kb = kb0; kb < kb1; ++kb) {
+      // the scale-factor warp has copied this stage's scales into tensor memory (which also
+      // means the stage's operand tiles have landed)
+      ok = mbar_wait_warp(sf_full0 + stage * 8, phase, env, kTagSfFull | stage);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t st = smem0 + stage * kStageBytes;
+      const uint64_t wdesc = make_desc_sw128(st);
+      const uint64_t adesc = make_desc_sw128(st + kTileW);
+      const uint32_t sfw_t = tmem_base + kSfColBase + stage * kSfColsPerStage;  // MMA A-side scales (W)
+      const uint32_t sfa_t = sfw_t + 8;                                          // MMA B-side scales (A)
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint32_t sf_id = (ks & 1) * 2;
-          const uint32_t idesc = make_idesc_mxf4(kRows, m_pad, sf_id, sf_id);
-          umma_mxf4(tmem_base, wdesc + ks * 2, adesc + ks * 2, idesc, (kb != kb0 || ks != 0) ? 1u : 0u,
-                    sfw_t + (ks >> 1) * 4, sfa_t + (ks >> 1) * 4);
-        }
-        umma_commit(&empty_bar[stage]);
-        if (++stage == kStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
+      for (int ks = 0; ks < 4; ++ks) {
+        const uint32_t sf_id = (ks & 1) * 2;
+        const uint32_t idesc = make_idesc_mxf4(kRows, m_pad, sf_id, sf_id);
+        umma_mxf4_elect(tmem_base, wdesc + ks * 2, adesc + ks * 2, idesc, (kb != kb0 || ks != 0) ? 1u : 0u,
+                        sfw_t + (ks >> 1) * 4, sfa_t + (ks >> 1) * 4);
       }
-      if (ok) umma_commit(acc_bar);
+      umma_commit_elect(empty0 + stage * 8);
+      if (++stage == kStages) {
+        stage = 0;
+        phase ^= 1u;
+      }
     }
+    if (ok) umma_commit_elect(smem_u32(acc_bar));
   } else if (warp == 6) {
-    // scale-factor copier: one thread per tcgen05 instruction costs the issuing thread about a
-    // hundred cycles, so the four copies per stage are kept off the MMA thread
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
-        // the stage's tensor-memory scale columns were last read by MMAs that completed before the
-        // stage was handed back to the producer
-        if (!mbar_wait(&full_bar[stage], phase, env, kTagFull | 0x80 | stage)) break;
-        tc_fence_after();
-        const uint32_t st = smem_u32(smem + stage * kStageBytes);
-        const uint32_t sfw_t = tmem_base + kSfColBase + stage * kSfColsPerStage;
-        const uint32_t sfa_t = sfw_t + 8;
+    // scale-factor copier: the four copies per stage are kept off the MMA warp
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int kb = kb0; kb < kb1; ++kb) {
+      // the stage's tensor-memory scale columns were last read by MMAs that completed before the
+      // stage was handed back to the producers
+      if (!mbar_wait_warp(full0 + stage * 8, phase, env, kTagFull | 0x80 | stage)) break;
+      tc_fence_after();
+      const uint32_t st = smem0 + stage * kStageBytes;
+      const uint32_t sfw_t = tmem_base + kSfColBase + stage * kSfColsPerStage;
+      const uint32_t sfa_t = sfw_t + 8;
 #pragma unroll
-        for (int ka = 0; ka < 2; ++ka) {
-          tmem_cp_32x128b_warpx4(sfw_t + ka * 4, make_desc_sf(st + kTileW + kTileA + ka * 512));
-          tmem_cp_32x128b_warpx4(sfa_t + ka * 4, make_desc_sf(st + kTileW + kTileA + kSf + ka * 512));
-        }
-        umma_commit(&sf_full_bar[stage]);
-        if (++stage == kStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
+      for (int ka = 0; ka < 2; ++ka) {
+        tmem_cp_32x128b_warpx4_elect(sfw_t + ka * 4, make_desc_sf(st + kTileW + kTileA + ka * 512));
+        tmem_cp_32x128b_warpx4_elect(sfa_t + ka * 4, make_desc_sf(st + kTileW + kTileA + kSf + ka * 512));
+      }
+      umma_commit_elect(sf_full0 + stage * 8);
+      if (++stage == kStages) {
+        stage = 0;
+        phase ^= 1u;
       }
     }
   }
