@@ -44,6 +44,8 @@ REQUIRED = {
     "gemm_o2_skinny_kernel": ([r"cp\.async\.bulk\.tensor\.2d\.shared::cluster\.global",
                                r"tcgen05\.mma\.cta_group::1\.kind::mxf4\.block_scale"],
                               "O2 decode GEMM: TMA loads, block-scaled MXFP4 MMA"),
+    "gemm_o1_decode_kernel": ([r"cp\.async\.bulk\.tensor\.2d\.shared::cluster\.global", r"dp4a\.s32\.s32", r"elect\.sync"],
+                              "O1 decode GEMM for M <= 16: TMA loads issued by an elected lane, dp4a dot products"),
     "gemm_o1_skinny_kernel": ([r"cp\.async\.bulk\.tensor\.2d\.shared::cluster\.global", r"tcgen05\.mma\.cta_group::1\.kind::i8"],
                               "O1 decode GEMM: TMA loads, kind::i8 MMA"),
     r"gemm_acc_kernelILi1E": ([r"cp\.async\.bulk\.tensor\.2d\.shared::cluster\.global", r"tcgen05\.mma\.cta_group::1\.kind::i8",

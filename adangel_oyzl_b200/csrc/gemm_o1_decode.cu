@@ -1,22 +1,28 @@
-// O1 for decode-sized activations (M <= 64): warp-level INT8 MMAs with the per-K32 FP32 rescale in
-// registers, on 32-row blocks of W so that the whole GPU streams the weights.
+// O1 for the smallest activations (decode, M <= 16): the integer dot products on dp4a, the FP32
+// rescale chain handed round a ring of warps, on 32-row blocks of W so that the whole GPU streams
+// the weights.
 //
 // Semantics are those of gemm_o1_kernel (reference/o1.py:16-20, csrc/sm120/o1_gemm.cu:167-333):
 // for every output element and every K32 group g, in ascending g,
 //     P   = sum_{k in g} A_int8[m,k] * W_int8[n,k]                        (INT32, exact)
-//     acc = fma(RN(float(P) * A_scale[m]), 2**(W_scale[n,g]-128), acc)   (FP32)
+//     t   = RN(float(P) * A_scale[m])
+//     acc = fma(t, 2**(W_scale[n,g]-128), acc)                            (FP32)
 // which equals the reference's acc + float(P) * ((A_scale*2**(W_scale-127))*0.5) bit for bit: P is
 // exact in any order, and the FP32 steps are the same operations in the same order.
 //
-// One K32 group of 16 rows of W against 8 activation rows is exactly one mma.sync m16n8k32 (s8 x s8 ->
-// s32) with the rows of W as the MMA's M dimension; its four results per thread are rescaled and added
-// to accumulators that stay in registers over all of K.  Nothing passes through tensor memory, so a
-// group costs one shared-memory fragment load, one MMA and twelve FP32 instructions instead of the
-// issue / commit / tensor-memory-load / hand-over chain of the tcgen05 formulation, whose fixed costs
-// dominate when there are only a few activation rows.  A CTA owns 32 rows of W (N = 4096 gives 128
-// CTAs) and all activation rows; two producer warps (even and odd stages) feed a ring of shared-memory
-// stages by TMA, each stage one 128-byte K slab of W (32 rows) and of A (128-byte swizzle, so that
-// the fragment loads are conflict-free).
+// Only the last line is a chain; P and t of different groups are independent.  With a handful of
+// activation rows the tensor-core formulation spends its time on fixed costs per K slab (issue, commit,
+// tensor-memory load, hand-over between warps: about 1100 cycles per 128-byte slab whatever M is), and a
+// single warp that does everything for its rows needs 650 cycles per slab because a lone warp issues
+// one dependent instruction every few cycles.  Here a CTA owns 32 rows of W (lane = row, N = 4096 gives
+// 128 CTAs) and its eight warps take the K slabs in turn: warp w computes P and t of slabs w, w + 8, ...
+// ahead of time, then waits for the accumulators from the warp of the previous slab, applies its four
+// fma per output and passes them on through shared memory.  The chain costs one hand-over and 4 fma
+// per slab instead of the whole slab's arithmetic.
+//
+// Loads: every warp refills the shared-memory slot it has just read with the slab 16 further on (TMA,
+// 128-byte swizzle so that the 32 rows of a warp fall into different banks; the slot count is a multiple
+// of the ring, so a slot always belongs to the same warp and needs no "empty" barrier).
 #include "codecs.cuh"
 #include "common.cuh"
 #include "launch.h"
@@ -25,262 +31,275 @@ namespace adg {
 
 namespace {
 
-constexpr int kRowsD = 32;              // W rows per CTA: two 16-row MMA tiles
-constexpr int kTileWD = kRowsD * 128;   // bytes of W per stage
-constexpr int kMaxStagesD = 12;
-constexpr int kRingBytesD = 72 * 1024;  // three CTAs per SM
-constexpr int kProducerWarps = 2;
-constexpr int kMaxComputeWarps = 8;
-constexpr int kMaxThreadsD = (kProducerWarps + kMaxComputeWarps) * 32;
-constexpr int kSmemBytesD = kRingBytesD + 1024 + 256;
+constexpr int kRowsD = 32;             // W rows per CTA: one per lane
+constexpr int kTileWD = kRowsD * 128;  // bytes of W per slab
 
-enum : uint32_t { kTagEmptyD = 0x3500, kTagFullD = 0x3600 };
+enum : uint32_t { kTagFullD = 0x3600, kTagTokenD = 0x3700 };
 
-__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x2(uint32_t addr, uint32_t (&r)[2]) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
-}
-// D (16 x 8, s32) = A (16 x 32, s8, row-major) * B (32 x 8, s8, column-major)
-__device__ __forceinline__ void mma_s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
-      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+// MT activation rows per thread, T slabs per turn, RING warps.  Every warp owns T shared-memory slots.
+__host__ __device__ constexpr int a_rows_for(int mt) { return mt < 8 ? 8 : mt; }  // whole 8-row swizzle atoms
+__host__ __device__ constexpr int slot_bytes_for(int mt) { return kTileWD + a_rows_for(mt) * 128; }
+__host__ __device__ constexpr int smem_bytes_for(int mt, int t, int ring) {
+  return t * ring * slot_bytes_for(mt) + ring * mt * 32 * 4 + 1024 + 512;
 }
 
-int stages_for(int stage_bytes) {
-  int s = kRingBytesD / stage_bytes;
-  s = s > kMaxStagesD ? kMaxStagesD : s;
-  return s & ~1;  // even: the two producer warps alternate
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ int dot32(const uint4& w0, const uint4& w1, const uint4& a0, const uint4& a1) {
+  int p = __dp4a(static_cast<int>(w0.x), static_cast<int>(a0.x), 0);
+  p = __dp4a(static_cast<int>(w0.y), static_cast<int>(a0.y), p);
+  p = __dp4a(static_cast<int>(w0.z), static_cast<int>(a0.z), p);
+  p = __dp4a(static_cast<int>(w0.w), static_cast<int>(a0.w), p);
+  p = __dp4a(static_cast<int>(w1.x), static_cast<int>(a1.x), p);
+  p = __dp4a(static_cast<int>(w1.y), static_cast<int>(a1.y), p);
+  p = __dp4a(static_cast<int>(w1.z), static_cast<int>(a1.z), p);
+  p = __dp4a(static_cast<int>(w1.w), static_cast<int>(a1.w), p);
+  return p;
 }
 
-// NT = 8-row activation tiles per compute warp.  a_rows = rows of the A box (a multiple of 8 * NT).
-template <int NT>
-__global__ void __launch_bounds__(kMaxThreadsD)
+// Wait for the accumulators of the previous turn.  Every lane probes by itself (no vote per probe: the
+// hand-over is the chain's critical path) and the warp agrees on the outcome once at the end.  Bounded
+// by a probe count instead of the timer.
+__device__ __forceinline__ bool token_wait(uint32_t bar, uint32_t parity, const WaitEnv& env, uint32_t tag) {
+  bool ok = true;
+  uint32_t spins = 0;
+  while (!mbar_test_wait_a(bar, parity)) {
+    if ((++spins & 0xFFFu) == 0) {
+      if (*env.abort) {
+        ok = false;
+        break;
+      }
+      if (spins >= (1u << 25)) {  // seconds: nothing is coming
+        *env.abort = 1;
+        if (atomicCAS(env.status, 0u, static_cast<uint32_t>(kStatusWaitTimeout)) == 0u) {
+          env.status[1] = tag;
+          env.status[2] = blockIdx.x;
+          env.status[3] = parity;
+        }
+        ok = false;
+        break;
+      }
+    }
+  }
+  return __all_sync(0xFFFFFFFFu, ok);
+}
+
+// MT = activation rows held per thread (M <= MT; rows past M are read as zero and never stored);
+// T = K slabs per turn of a warp; RING = warps.  Turn u covers slabs u*T .. u*T + T - 1 and belongs to
+// warp u % RING, which keeps those slabs in its own T shared-memory slots.
+template <int MT, int T, int RING>
+__global__ void __launch_bounds__(RING * 32, RING == 4 ? 3 : (MT <= 4 ? 2 : 1))
 gemm_o1_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
                       const float* __restrict__ a_scale, const uint8_t* __restrict__ w_scale, float* __restrict__ y,
-                      int M, int N, int K, int ldy, int a_rows, int stages, uint32_t* status) {
+                      int M, int N, int K, int ldy, uint32_t* status) {
+  constexpr int kSlotBytes = slot_bytes_for(MT);
+  constexpr int kSlots = T * RING;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int stage_bytes = kTileWD + a_rows * 128;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kRingBytesD);
-  uint64_t* empty_bar = full_bar + kMaxStagesD;
-  volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(empty_bar + kMaxStagesD);
+  float* handoff = reinterpret_cast<float*>(smem + kSlots * kSlotBytes);  // [RING][MT][32]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(handoff + RING * MT * 32);
+  uint64_t* token_bar = full_bar + kSlots;
+  volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(token_bar + RING);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int compute_warps = static_cast<int>(blockDim.x >> 5) - kProducerWarps;
   const WaitEnv env{status, abort_flag};
   const int nb = blockIdx.x;
   const int groups = K / 32;
   const int num_kb = (groups + 3) / 4;
+  const int num_turns = (num_kb + T - 1) / T;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], static_cast<uint32_t>(compute_warps));
-    }
+    for (int s = 0; s < kSlots; ++s) mbar_init(&full_bar[s], 1);
+    for (int w = 0; w < RING; ++w) mbar_init(&token_bar[w], 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_a);
   }
   __syncthreads();
-  const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+  const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(full_bar), token0 = smem_u32(token_bar);
 
-  if (warp < kProducerWarps) {
-    // producers: warp p takes the stages of parity p; the warp stays converged and one elected lane
-    // issues each copy
-    int stage = warp;
-    uint32_t phase = 0;
-    for (int kb = warp; kb < num_kb; kb += kProducerWarps) {
-      if (!mbar_wait_warp(empty0 + stage * 8, phase ^ 1u, env, kTagEmptyD | stage)) break;
-      const uint32_t st = smem0 + stage * stage_bytes;
-      const uint32_t bar = full0 + stage * 8;
-      mbar_expect_tx_elect(bar, static_cast<uint32_t>(stage_bytes));
-      tma_load_2d_elect(st, &tm_w, bar, kb * 128, nb * kRowsD);
-      tma_load_2d_elect(st + kTileWD, &tm_a, bar, kb * 128, 0);
-      stage += kProducerWarps;
-      if (stage >= stages) {
-        stage -= stages;
-        phase ^= 1u;
-      }
-    }
-    return;
-  }
-
-  // ------------------------------- compute warps ------------------------------------------------
-  const int cw = warp - kProducerWarps;
-  const int rt = cw & 1;          // which 16 of the CTA's 32 rows of W
-  const int t0 = (cw >> 1) * NT;  // first of this warp's 8-row activation tiles
-  const int lrow = lane >> 2, lcol = (lane & 3) * 2;
-  // this thread's results: rows n_lo and n_lo + 8 of W, activation rows m, m + 1 of each tile
-  const int n_lo = nb * kRowsD + rt * 16 + lrow;
-  const int n_hi = n_lo + 8;
-  const uint8_t* sc_lo = w_scale + static_cast<long>(n_lo < N ? n_lo : 0) * groups;
-  const uint8_t* sc_hi = w_scale + static_cast<long>(n_hi < N ? n_hi : 0) * groups;
-  const bool vec16 = (groups & 15) == 0;
-
-  float asc[NT][2], acc[NT][4];
-#pragma unroll
-  for (int t = 0; t < NT; ++t) {
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      const int m = (t0 + t) * 8 + lcol + c;
-      asc[t][c] = m < M ? __ldg(a_scale + m) : 0.0f;
-    }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) acc[t][c] = 0.0f;
-  }
-  // the 16 UE8M0 codes of stages 4*sb .. 4*sb+3 of one row; absent groups read as 0 and are never used
-  auto load_codes = [&](const uint8_t* row, int sb) -> uint4 {
-    const int g0 = sb * 16;
-    if (g0 >= groups) return make_uint4(0u, 0u, 0u, 0u);
-    if (vec16) return __ldg(reinterpret_cast<const uint4*>(row + g0));
-    uint32_t w[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-      if (g0 + i < groups) w[i >> 2] |= static_cast<uint32_t>(__ldg(row + g0 + i)) << (8 * (i & 3));
-    return make_uint4(w[0], w[1], w[2], w[3]);
+  // slab kb into slot `slot` of this warp (converged warp, one elected lane issues)
+  auto load_slab = [&](int kb, int slot) {
+    const uint32_t st = smem0 + slot * kSlotBytes;
+    const uint32_t bar = full0 + slot * 8;
+    mbar_expect_tx_elect(bar, kSlotBytes);
+    tma_load_2d_elect(st, &tm_w, bar, kb * 128, nb * kRowsD);
+    tma_load_2d_elect(st + kTileWD, &tm_a, bar, kb * 128, 0);
   };
-
-  // fragment-load addresses inside a stage: lane -> (8 x 8 matrix, row r of it); the 16-byte chunk index is
-  // XORed with the row's position in its 8-row swizzle atom
-  const int mat = lane >> 3, r = lane & 7;
-  const uint32_t w_base = static_cast<uint32_t>((rt * 16 + (mat & 1) * 8 + r) * 128);
-  const uint32_t w_chunk = static_cast<uint32_t>(mat >> 1);
-  // A: x4 covers two tiles (matrices: tile 0 chunk 0, tile 0 chunk 1, tile 1 chunk 0, tile 1 chunk 1);
-  // x2 uses the addresses of lanes 0-15 only
-  const uint32_t a_base = static_cast<uint32_t>(kTileWD + ((t0 + (NT == 2 ? (mat >> 1) : 0)) * 8 + r) * 128);
-  const uint32_t a_chunk = static_cast<uint32_t>(mat & 1);
-  const uint32_t rx = static_cast<uint32_t>(r);
-
-  int stage = 0;
-  uint32_t phase = 0;
-  bool ok = true;
-  // Fragment loads and MMAs of stage kb (partials of its up to four K32 groups into `p`), then the
-  // stage is handed back: its bytes are in registers once the MMAs have been issued.
-  auto issue = [&](int kb, int (&p)[4][NT][4]) {
-    ok = mbar_wait_warp(full0 + stage * 8, phase, env, kTagFullD | stage);
-    if (!ok) return;
-    const uint32_t st = smem0 + static_cast<uint32_t>(stage * stage_bytes);
-    const int ng = min(4, groups - kb * 4);
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      if (g < ng) {
-        uint32_t wf[4];
-        ldsm_x4(st + w_base + (((static_cast<uint32_t>(2 * g) + w_chunk) ^ rx) << 4), wf);
-        if constexpr (NT == 2) {
-          uint32_t af[4];
-          ldsm_x4(st + a_base + (((static_cast<uint32_t>(2 * g) + a_chunk) ^ rx) << 4), af);
-          mma_s8(p[g][0], wf, af[0], af[1]);
-          mma_s8(p[g][1], wf, af[2], af[3]);
-        } else {
-          uint32_t af[2];
-          ldsm_x2(st + a_base + (((static_cast<uint32_t>(2 * g) + a_chunk) ^ rx) << 4), af);
-          mma_s8(p[g][0], wf, af[0], af[1]);
-        }
-      }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive_a(empty0 + stage * 8);
-    if (++stage == stages) {
-      stage = 0;
-      phase ^= 1u;
-    }
+  for (int i = 0; i < T; ++i)
+    if (warp * T + i < num_kb) load_slab(warp * T + i, warp * T + i);
+
+  const int n = nb * kRowsD + lane;
+  const bool n_ok = n < N;
+  const uint8_t* sc_row = w_scale + static_cast<long>(n_ok ? n : 0) * groups;
+  const bool vec4 = (groups & 3) == 0;
+  // the four UE8M0 codes of slab kb for this thread's row (absent groups read as 0 and are never used)
+  auto load_codes = [&](int kb) -> uint32_t {
+    if (kb >= num_kb) return 0u;
+    if (vec4) return __ldg(reinterpret_cast<const uint32_t*>(sc_row + kb * 4));
+    uint32_t c = 0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      if (kb * 4 + g < groups) c |= static_cast<uint32_t>(__ldg(sc_row + kb * 4 + g)) << (8 * g);
+    return c;
   };
-  auto accumulate = [&](int kb, const int (&p)[4][NT][4], uint32_t c_lo, uint32_t c_hi) {
-    const int ng = min(4, groups - kb * 4);
+  float asc[MT];
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      if (g < ng) {
-        const float s_lo = ue8m0_half_to_float((c_lo >> (8 * g)) & 0xFFu);
-        const float s_hi = ue8m0_half_to_float((c_hi >> (8 * g)) & 0xFFu);
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          acc[t][0] = __fmaf_rn(__fmul_rn(__int2float_rn(p[g][t][0]), asc[t][0]), s_lo, acc[t][0]);
-          acc[t][1] = __fmaf_rn(__fmul_rn(__int2float_rn(p[g][t][1]), asc[t][1]), s_lo, acc[t][1]);
-          acc[t][2] = __fmaf_rn(__fmul_rn(__int2float_rn(p[g][t][2]), asc[t][0]), s_hi, acc[t][2]);
-          acc[t][3] = __fmaf_rn(__fmul_rn(__int2float_rn(p[g][t][3]), asc[t][1]), s_hi, acc[t][3]);
-        }
-      }
-    }
-  };
+  for (int j = 0; j < MT; ++j) asc[j] = j < M ? __ldg(a_scale + j) : 0.0f;
 
-  // software pipeline: the MMAs of stage kb + 1 are in flight while stage kb is rescaled and added
-  int pa[4][NT][4], pb[4][NT][4];
-  uint4 next_lo = load_codes(sc_lo, 0), next_hi = load_codes(sc_hi, 0);
-  if (num_kb > 0) issue(0, pa);
-  for (int sb = 0; ok && sb * 4 < num_kb; ++sb) {
-    const uint32_t code_lo[4] = {next_lo.x, next_lo.y, next_lo.z, next_lo.w};
-    const uint32_t code_hi[4] = {next_hi.x, next_hi.y, next_hi.z, next_hi.w};
-    next_lo = load_codes(sc_lo, sb + 1);
-    next_hi = load_codes(sc_hi, sb + 1);
+  const uint32_t w_off = static_cast<uint32_t>(lane * 128);
+  const uint32_t w_xor = static_cast<uint32_t>(lane & 7);
+  const int prev = (warp + RING - 1) % RING;
+  float* my_handoff = handoff + (warp * MT) * 32 + lane;
+  const float* prev_handoff = handoff + (prev * MT) * 32 + lane;
+
+  uint32_t codes[T];
 #pragma unroll
-    for (int b = 0; b < 4; ++b) {
-      const int kb = sb * 4 + b;
-      if (kb >= num_kb) break;
-      if (kb + 1 < num_kb) {
-        if (b & 1) issue(kb + 1, pa);
-        else issue(kb + 1, pb);
+  for (int i = 0; i < T; ++i) codes[i] = load_codes(warp * T + i);
+  int it = 0;
+  for (int u = warp; u < num_turns; u += RING, ++it) {
+    uint32_t codes_next[T];
+#pragma unroll
+    for (int i = 0; i < T; ++i) codes_next[i] = load_codes((u + RING) * T + i);
+    // ---- ahead of the chain: P and t of this turn's groups
+    float t[T][4][MT], sc[T][4];
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < T; ++i) {
+      const int kb = u * T + i;
+      if (kb < num_kb) {
+        const int slot = warp * T + i;
+        ok = mbar_wait_warp(full0 + slot * 8, static_cast<uint32_t>(it) & 1u, env, kTagFullD | slot);
         if (!ok) break;
-      }
-      if (b & 1) accumulate(kb, pb, code_lo[b], code_hi[b]);
-      else accumulate(kb, pa, code_lo[b], code_hi[b]);
-    }
-  }
-  if (ok) {
+        const uint32_t st = smem0 + slot * kSlotBytes;
+        const int ng = min(4, groups - kb * 4);
 #pragma unroll
-    for (int t = 0; t < NT; ++t) {
+        for (int g = 0; g < 4; ++g) sc[i][g] = ue8m0_half_to_float((codes[i] >> (8 * g)) & 0xFFu);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int m = (t0 + t) * 8 + lcol + (c & 1);
-        const int n = (c & 2) ? n_hi : n_lo;
-        if (m < M && n < N) y[static_cast<long>(m) * ldy + n] = acc[t][c];
+        for (int g = 0; g < 4; ++g) {
+          if (g < ng) {
+            const uint4 w0 = lds128(st + w_off + ((static_cast<uint32_t>(2 * g) ^ w_xor) << 4));
+            const uint4 w1 = lds128(st + w_off + ((static_cast<uint32_t>(2 * g + 1) ^ w_xor) << 4));
+#pragma unroll
+            for (int j = 0; j < MT; ++j) {
+              const uint32_t a_row = st + kTileWD + j * 128;
+              const uint4 a0 = lds128(a_row + ((static_cast<uint32_t>(2 * g) ^ static_cast<uint32_t>(j & 7)) << 4));
+              const uint4 a1 = lds128(a_row + ((static_cast<uint32_t>(2 * g + 1) ^ static_cast<uint32_t>(j & 7)) << 4));
+              t[i][g][j] = __fmul_rn(__int2float_rn(dot32(w0, w1, a0, a1)), asc[j]);
+            }
+          }
+        }
+        // the slot's bytes are in registers: refill it with the slab of this warp's next turn
+        __syncwarp();
+        if ((u + RING) * T + i < num_kb) {
+          fence_proxy_async_smem();
+          load_slab((u + RING) * T + i, slot);
+        }
       }
     }
+    if (!ok) break;
+    // ---- the chain: accumulators from the warp of the previous turn, four fma per group, pass them on
+    float acc[MT];
+    if (u > 0) {
+      const uint32_t parity = static_cast<uint32_t>(warp == 0 ? it - 1 : it) & 1u;
+      if (!token_wait(token0 + prev * 8, parity, env, kTagTokenD | prev)) break;
+#pragma unroll
+      for (int j = 0; j < MT; ++j) acc[j] = prev_handoff[j * 32];
+    } else {
+#pragma unroll
+      for (int j = 0; j < MT; ++j) acc[j] = 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < T; ++i) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if ((u * T + i) * 4 + g < groups) {
+#pragma unroll
+          for (int j = 0; j < MT; ++j) acc[j] = __fmaf_rn(t[i][g][j], sc[i][g], acc[j]);
+        }
+      }
+    }
+    if (u == num_turns - 1) {
+      if (n_ok) {
+#pragma unroll
+        for (int j = 0; j < MT; ++j)
+          if (j < M) y[static_cast<long>(j) * ldy + n] = acc[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < MT; ++j) my_handoff[j * 32] = acc[j];
+      __syncwarp();
+      if (lane == 0) mbar_arrive_a(token0 + warp * 8);
+    }
+#pragma unroll
+    for (int i = 0; i < T; ++i) codes[i] = codes_next[i];
   }
 }
 
-template <int NT>
+// Configurations.  Two slabs per turn halve the hand-overs where the registers allow it (MT <= 8).
+// A ring of eight keeps 16 slabs in flight per CTA (80 KB; two CTAs per SM up to MT = 4, one above);
+// grids too large for that run rings of four (8 slabs, 40 KB, three CTAs per SM), so that all CTAs
+// are resident at once.
+struct DecodeCfg {
+  int mt, t, ring;
+};
+DecodeCfg choose_cfg(int M, int N, int sm_count) {
+  const int mt = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : 16;
+  if (mt == 16) return {16, 1, 8};
+  const int ctas = (N + kRowsD - 1) / kRowsD;
+  return {mt, 2, ctas <= (mt <= 4 ? 2 : 1) * sm_count ? 8 : 4};
+}
+
+template <int MT, int T, int RING>
 int launch_decode(const GemmPlan& p, cudaStream_t stream) {
-  const int a_rows = p.block_n;
-  const int warps = 2 * (a_rows / (8 * NT));
-  gemm_o1_decode_kernel<NT><<<p.grid, (kProducerWarps + warps) * 32, kSmemBytesD, stream>>>(
+  gemm_o1_decode_kernel<MT, T, RING><<<p.grid, RING * 32, smem_bytes_for(MT, T, RING), stream>>>(
       p.tm_b, p.tm_a, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y, p.M, p.N, p.K,
-      p.ldy, a_rows, stages_for(kTileWD + a_rows * 128), p.status);
+      p.ldy, p.status);
   return check_cuda(cudaGetLastError(), "gemm_o1_decode_kernel launch");
 }
-
-// 8-row activation tiles per warp: one up to 16 rows (two or four compute warps), two above.
-int tiles_per_warp(int M) { return M <= 16 ? 1 : 2; }
-int a_box_rows(int M) {
-  const int unit = 8 * tiles_per_warp(M);
-  return (M + unit - 1) / unit * unit;
+template <int MT, int T, int RING>
+int set_smem_attribute() {
+  return check_cuda(cudaFuncSetAttribute(gemm_o1_decode_kernel<MT, T, RING>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         smem_bytes_for(MT, T, RING)),
+                    "cudaFuncSetAttribute(gemm_o1_decode_kernel)");
+}
+template <int MT>
+int set_smem_attributes() {
+  if (int rc = set_smem_attribute<MT, 2, 8>()) return rc;
+  return set_smem_attribute<MT, 2, 4>();
+}
+template <int MT>
+int launch_for_ring(const GemmPlan& p, int ring, cudaStream_t stream) {
+  return ring == 8 ? launch_decode<MT, 2, 8>(p, stream) : launch_decode<MT, 2, 4>(p, stream);
 }
 
 }  // namespace
 
-int init_gemm_o1_decode_attributes() {
-  if (int rc = check_cuda(cudaFuncSetAttribute(gemm_o1_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               kSmemBytesD),
-                          "cudaFuncSetAttribute(gemm_o1_decode_kernel<1>)"))
-    return rc;
-  return check_cuda(
-      cudaFuncSetAttribute(gemm_o1_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesD),
-      "cudaFuncSetAttribute(gemm_o1_decode_kernel<2>)");
+// Up to 8 activation rows always; 9 - 16 rows (one CTA per SM) while the 32-row blocks of W fit the GPU once.
+bool o1_decode_applies(int M, int N, int sm_count) {
+  return M <= 8 || (M <= 16 && (N + kRowsD - 1) / kRowsD <= sm_count);
 }
 
-// Plan for the decode-shape O1 GEMM: tm_b = W map (32-row boxes), tm_a = A map (all activation rows,
-// rounded up to whole tiles; rows past M read as zero).
+int init_gemm_o1_decode_attributes() {
+  if (int rc = set_smem_attributes<1>()) return rc;
+  if (int rc = set_smem_attributes<2>()) return rc;
+  if (int rc = set_smem_attributes<4>()) return rc;
+  if (int rc = set_smem_attributes<8>()) return rc;
+  return set_smem_attribute<16, 1, 8>();
+}
+
+// Plan for the decode-shape O1 GEMM: tm_b = W map (32-row boxes), tm_a = A map (all activation rows in one
+// box, rounded up to whole 8-row swizzle atoms; rows past M read as zero).
 int plan_o1_decode(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale,
                    float* y, int M, int N, int K, int ldy) {
   DeviceCtx* ctx = nullptr;
   if (int rc = device_ctx(&ctx)) return rc;
-  if (M <= 0 || M > 64) return fail("plan_o1_decode: M must be in [1, 64]");
+  if (M <= 0 || M > 16) return fail("plan_o1_decode: M must be in [1, 16]");
   *plan = GemmPlan{};
   plan->variant = 1;
   plan->skinny = 2;
@@ -289,28 +308,35 @@ int plan_o1_decode(GemmPlan* plan, const void* a_int8, const void* a_scale, cons
   plan->w_scale = w_scale;
   plan->y = y;
   plan->status = ctx->status;
-  plan->block_n = a_box_rows(M);
+  const DecodeCfg cfg = choose_cfg(M, N, ctx->sm_count);
+  plan->block_n = cfg.mt;
   if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_int8, N, K, K, kRowsD, 128)) return rc;
-  if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_int8, M, K, K, plan->block_n, 128))
+  if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_int8, M, K, K,
+                                    a_rows_for(plan->block_n), 128))
     return rc;
   plan->tm_y = plan->tm_a;
   plan->grid = (N + kRowsD - 1) / kRowsD;
-  plan->grid_y = 1;
+  plan->grid_y = cfg.ring;  // the ring size travels in grid_y; the grid is one-dimensional
   return 0;
 }
 
 int run_gemm_o1_decode(const GemmPlan& p, cudaStream_t stream) {
-  return tiles_per_warp(p.M) == 1 ? launch_decode<1>(p, stream) : launch_decode<2>(p, stream);
+  switch (p.block_n) {
+    case 1: return launch_for_ring<1>(p, p.grid_y, stream);
+    case 2: return launch_for_ring<2>(p, p.grid_y, stream);
+    case 4: return launch_for_ring<4>(p, p.grid_y, stream);
+    case 8: return launch_for_ring<8>(p, p.grid_y, stream);
+    default: return launch_decode<16, 1, 8>(p, stream);
+  }
 }
 
-void describe_gemm_o1_decode(int M, PlanInfo* info) {
-  const int nt = tiles_per_warp(M);
-  const int a_rows = a_box_rows(M);
-  info->symbol = nt == 1 ? "gemm_o1_decode_kernel<1>" : "gemm_o1_decode_kernel<2>";
-  info->mma_family = "mma.sync.m16n8k32.s8";
-  info->tile_m = a_rows, info->tile_n = kRowsD, info->stages = stages_for(kTileWD + a_rows * 128), info->acc_stages = 0;
-  info->threads = (kProducerWarps + 2 * (a_rows / (8 * nt))) * 32, info->cluster = 1;
-  info->mma_m = 16, info->mma_n = 8, info->mma_k = 32;
+void describe_gemm_o1_decode(int M, int N, int sm_count, PlanInfo* info) {
+  const DecodeCfg cfg = choose_cfg(M, N, sm_count);
+  info->symbol = "gemm_o1_decode_kernel";
+  info->mma_family = "dp4a";
+  info->tile_m = cfg.mt, info->tile_n = kRowsD, info->stages = cfg.t * cfg.ring, info->acc_stages = 0;
+  info->threads = cfg.ring * 32, info->cluster = 1;
+  info->mma_m = 1, info->mma_n = 1, info->mma_k = 4;
   info->persistent = 0;
 }
 

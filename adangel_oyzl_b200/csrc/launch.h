@@ -152,7 +152,7 @@ void describe_gemm_pair(int variant, bool fused, PlanInfo* info);
 void describe_gemm_o1(PlanInfo* info);
 void describe_gemm_o1_bf16(PlanInfo* info);
 void describe_gemm_o1_skinny(PlanInfo* info);
-void describe_gemm_o1_decode(int M, PlanInfo* info);
+void describe_gemm_o1_decode(int M, int N, int sm_count, PlanInfo* info);
 void describe_gemm_o2_skinny(int M, PlanInfo* info);
 
 int plan_o0(GemmPlan* plan, const void* a_fp16, const void* w_fp16, float* y, int M, int N, int K, int ldy);
@@ -197,6 +197,7 @@ int plan_o1_skinny(GemmPlan* plan, const void* a_int8, const void* a_scale, cons
                    float* y, int M, int N, int K, int ldy);
 int run_gemm_o1_skinny(const GemmPlan& plan, cudaStream_t stream);
 int init_gemm_o1_decode_attributes();
+bool o1_decode_applies(int M, int N, int sm_count);
 int plan_o1_decode(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale,
                    float* y, int M, int N, int K, int ldy);
 int run_gemm_o1_decode(const GemmPlan& plan, cudaStream_t stream);

@@ -240,19 +240,12 @@ int plan_o0(GemmPlan* plan, const void* a_fp16, const void* w_fp16, float* y, in
   return finish_plan(plan, block_n);
 }
 
-// Largest M served by the dot-product-unit O1 kernel; above it the tensor-core decode kernel runs.
-static int o1_decode_max_m() {
-  static const int v = [] {
-    const char* e = getenv("ADG_O1_DECODE_MAX_M");
-    return e ? atoi(e) : 16;
-  }();
-  return v;
-}
-
 int plan_o1(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale, float* y,
             int32_t* partial_dump, int M, int N, int K, int ldy) {
   if (int rc = check_shape(M, N, K, ldy)) return rc;
-  if (M <= o1_decode_max_m() && partial_dump == nullptr)
+  DeviceCtx* ctx = nullptr;
+  if (int rc = device_ctx(&ctx)) return rc;
+  if (partial_dump == nullptr && o1_decode_applies(M, N, ctx->sm_count))
     return plan_o1_decode(plan, a_int8, a_scale, w_int8, w_scale, y, M, N, K, ldy);
   if (M <= 64 && partial_dump == nullptr) return plan_o1_skinny(plan, a_int8, a_scale, w_int8, w_scale, y, M, N, K, ldy);
   return plan_o1_tiled(plan, a_int8, a_scale, w_int8, w_scale, y, partial_dump, M, N, K, ldy);
@@ -398,7 +391,7 @@ int plan_info(int variant, int flags, int M, int N, int K, PlanInfo* info) {
   const bool fused = (flags & kPlanFusedActivation) != 0 && M > 64 && (variant == 0 || variant == 2);
   const int block_n = N > 128 ? 256 : 128;
   if (variant == 1) {
-    if (M <= o1_decode_max_m() && !(flags & kPlanPartialDump)) describe_gemm_o1_decode(M, info);
+    if (!(flags & kPlanPartialDump) && o1_decode_applies(M, N, sm_count)) describe_gemm_o1_decode(M, N, sm_count, info);
     else if (M <= 64 && !(flags & kPlanPartialDump)) describe_gemm_o1_skinny(info);
     else if ((flags & kPlanO1Bf16) && !(flags & kPlanPartialDump)) describe_gemm_o1_bf16(info);
     else describe_gemm_o1(info);

@@ -93,6 +93,22 @@ def test_decode_shapes(K, shape):
     _compare(K, *orc.canonical_inputs(m, n, k, seed=13), dump=False)
 
 
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (2, 100, 192), (3, 9600, 256), (4, 352, 4160), (7, 4800, 640),
+                                   (8, 64, 2048), (9, 4736, 192), (13, 31, 1088), (16, 4704, 4096)])
+def test_o1_decode_ring_shapes(K, shape):
+    # M <= 16: the dp4a kernel whose warps take the K slabs in turn -- every rows-per-thread variant, both
+    # ring sizes (N / 32 above and below what is resident at once), one, few and many turns, ragged K and N
+    import torch
+
+    m, n, k = shape
+    a_int8, a_scale, w_mx, w_sc = orc.canonical_inputs(m, n, k, seed=29)
+    da, ds, dw, dws = to_cuda(a_int8, a_scale, w_mx, w_sc)
+    y = torch.full((m, n), float("nan"), device="cuda")
+    K.gemm_o1(da, ds, K.mxfp4_to_int8(dw), dws, out=y)
+    K.check_status()
+    np.testing.assert_array_equal(y.cpu().numpy(), orc.run_o1(a_int8, a_scale, w_mx, w_sc)["output"])
+
+
 def test_decode_matches_prefill_rows(K):
     # the decode kernels and the 128-row-tile kernels give the same bits for the same activation rows
     a_int8, a_scale, w_mx, w_sc = orc.canonical_inputs(160, 512, 1024, seed=17)

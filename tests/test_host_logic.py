@@ -139,7 +139,10 @@ def test_plan_info_follows_the_planner():
     assert _sm100.plan_info("o0", 2048, 128, 4096)["tile"] == [128, 128]
     assert _sm100.plan_info("o1", 4096, 4096, 4096)["kernel_symbol"] == "gemm_o1_kernel"
     assert _sm100.plan_info("o1", 4096, 4096, 4096, o1_bf16=True)["kernel_symbol"] == "gemm_o1_bf16_kernel"
-    assert _sm100.plan_info("o1", 16, 4096, 4096, o1_bf16=True)["kernel_symbol"] == "gemm_o1_skinny_kernel"
+    assert _sm100.plan_info("o1", 16, 4096, 4096, o1_bf16=True)["kernel_symbol"] == "gemm_o1_decode_kernel"
+    assert _sm100.plan_info("o1", 16, 11008, 4096, o1_bf16=True)["kernel_symbol"] == "gemm_o1_skinny_kernel"
+    assert _sm100.plan_info("o1", 8, 11008, 4096, o1_bf16=True)["threads"] == 128
+    assert _sm100.plan_info("o1", 64, 4096, 4096, o1_bf16=True)["kernel_symbol"] == "gemm_o1_skinny_kernel"
     assert _sm100.plan_info("o2", 64, 4096, 4096, fused=True)["kernel_symbol"] == "gemm_o2_skinny_kernel"
     assert _sm100.plan_info("o1x", 4096, 4096, 4096)["mma_shape"] == [128, 256, 32]
     with pytest.raises(RuntimeError, match="K must be divisible by 64"):
