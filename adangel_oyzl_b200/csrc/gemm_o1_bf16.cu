@@ -33,7 +33,8 @@
 // elements per instruction), which frees issue slots for the hand-over instructions.  Measured at 4096^3: 375 us with two-group buffers and
 // one issuer, 365 us with per-group buffers, 342 us with the second issuer, 335 us with the early
 // request, 326 us with the next buffer released in the middle of the arithmetic, 323 us with the
-// one-thread roles waiting suspended, 283 us with packed arithmetic; the kernel (before packing)
+// one-thread roles waiting suspended, 283 us with packed arithmetic, 274 us with the role warps converged
+// and one elected lane per copy / MMA instruction; the kernel (before packing)
 // without the arithmetic takes 199 us, so the hand-over chain
 // (MMA -> commit -> load -> release, about a thousand cycles, over four buffers) and the arithmetic
 // (137 us, near the FP32 pipe's rate) add up instead of overlapping.
@@ -168,58 +169,61 @@ gemm_o1_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   if (warp < kFirstEpiWarp) {
     reg_dealloc<EpiCfg<CW>::kRoleRegs>();  // what this warp group returns is what the epilogue warps gain below
+    // The one-instruction roles run as converged warps with one elected lane per instruction: a lone thread
+    // inside a divergent branch needs 100 - 160 cycles per copy or MMA instruction.  All lanes wait
+    // suspended on the same barrier and see the same outcome; a vote per probe would cost the arithmetic
+    // warps of the scheduler more issue slots than the elected issue saves (308 us instead of 274 us).
     if (warp == 0) {
       // ------------------------------- TMA producer -------------------------------------------
-      if (lane == 0) {
-        int stage = 0;
-        uint32_t phase = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-          const TileCoord tc = tile_coord(tile, num_m, num_n);
-          for (int kb = 0; kb < num_pairs; ++kb) {
-            ok = ADG_ROLE_WAIT(empty_a + stage * 8, phase ^ 1u, status, abort_a, kTagEmpty | stage);
-            if (!ok) break;
-            uint8_t* st = smem + stage * kStageBytes;
-            mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
-            tma_load_2d(st, &tm_a, &full_bar[stage], kb * 64, tc.m_blk * kBlockM);
-            tma_load_2d(st + kTile, &tm_b, &full_bar[stage], kb * 64, tc.n_blk * kBlockN);
-            if (++stage == kStages) {
-              stage = 0;
-              phase ^= 1u;
-            }
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const uint32_t smem0 = smem_u32(smem);
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, num_m, num_n);
+        for (int kb = 0; kb < num_pairs; ++kb) {
+          ok = mbar_wait_suspended_a(empty_a + stage * 8, phase ^ 1u, status, abort_a, kTagEmpty | stage);
+          if (!ok) break;
+          const uint32_t st = smem0 + stage * kStageBytes;
+          const uint32_t bar = full_a + stage * 8;
+          mbar_expect_tx_elect(bar, kStageBytes);
+          tma_load_2d_elect(st, &tm_a, bar, kb * 64, tc.m_blk * kBlockM);
+          tma_load_2d_elect(st + kTile, &tm_b, bar, kb * 64, tc.n_blk * kBlockN);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
       }
     } else if (warp == 1 || warp == 2) {
       // ------------------------------- two MMA issuers: warp 1 takes the even K32 groups, warp 2 the odd
-      if (lane == 0) {
-        const int id = warp - 1;
-        int stage = 0, buf = id;
-        uint32_t phase = 0, buf_phase = 0;
-        bool ok = true;
-        constexpr uint32_t idesc = make_idesc(1, kFmtBF16, kFmtBF16, kBlockM, kBlockN);
-        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-          for (int kb = 0; ok && kb < num_pairs; ++kb) {
-            ok = ADG_ROLE_WAIT(full_a + stage * 8, phase, status, abort_a, kTagFull | stage);
-            if (!ok) break;
-            ok = ADG_ROLE_WAIT(tmem_empty_a + buf * 8, buf_phase ^ 1u, status, abort_a, kTagTmemEmpty | buf);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t st = smem_u32(smem + stage * kStageBytes);
-            const uint64_t adesc = make_desc_sw128(st) + id * 4;
-            const uint64_t bdesc = make_desc_sw128(st + kTile) + id * 4;
-            const uint32_t d = tmem_base + static_cast<uint32_t>(buf * kBlockN);
-            // one K32 group: two K16 MMAs into a fresh buffer
-            umma_f16(d, adesc, bdesc, idesc, 0u);
-            umma_f16(d, adesc + 2, bdesc + 2, idesc, 1u);
-            umma_commit_a(tmem_full_a + buf * 8);
-            umma_commit_a(empty_a + stage * 8);
-            buf ^= 2;
-            if (buf == id) buf_phase ^= 1u;
-            if (++stage == kStages) {
-              stage = 0;
-              phase ^= 1u;
-            }
+      const int id = warp - 1;
+      int stage = 0, buf = id;
+      uint32_t phase = 0, buf_phase = 0;
+      bool ok = true;
+      constexpr uint32_t idesc = make_idesc(1, kFmtBF16, kFmtBF16, kBlockM, kBlockN);
+      const uint32_t smem0 = smem_u32(smem);
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        for (int kb = 0; ok && kb < num_pairs; ++kb) {
+          ok = mbar_wait_suspended_a(full_a + stage * 8, phase, status, abort_a, kTagFull | stage);
+          if (!ok) break;
+          ok = mbar_wait_suspended_a(tmem_empty_a + buf * 8, buf_phase ^ 1u, status, abort_a, kTagTmemEmpty | buf);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t st = smem0 + stage * kStageBytes;
+          const uint64_t adesc = make_desc_sw128(st) + id * 4;
+          const uint64_t bdesc = make_desc_sw128(st + kTile) + id * 4;
+          const uint32_t d = tmem_base + static_cast<uint32_t>(buf * kBlockN);
+          // one K32 group: two K16 MMAs into a fresh buffer
+          umma_f16_elect(d, adesc, bdesc, idesc, 0u);
+          umma_f16_elect(d, adesc + 2, bdesc + 2, idesc, 1u);
+          umma_commit_elect(tmem_full_a + buf * 8);
+          umma_commit_elect(empty_a + stage * 8);
+          buf ^= 2;
+          if (buf == id) buf_phase ^= 1u;
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
       }
