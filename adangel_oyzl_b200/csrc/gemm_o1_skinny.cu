@@ -87,43 +87,42 @@ gemm_o1_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
-  // The one-instruction-at-a-time roles run as converged warps with one elected lane per instruction: a
-  // lone thread inside a divergent branch needs 100 - 160 cycles per copy or MMA instruction.
-  const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
-  const uint32_t slot_full0 = smem_u32(slot_full_bar), slot_empty0 = smem_u32(slot_empty_bar);
   if (warp == 0) {
-    int stage = 0;
-    uint32_t phase = 0;
-    for (int kb = 0; kb < num_kb; ++kb) {
-      if (!mbar_wait_warp(empty0 + stage * 8, phase ^ 1u, env, kTagEmpty | stage)) break;
-      const uint32_t st = smem0 + stage * kStageBytes;
-      const uint32_t bar = full0 + stage * 8;
-      mbar_expect_tx_elect(bar, kStageBytes);
-      tma_load_2d_elect(st, &tm_w, bar, kb * 128, nb * kRows);
-      tma_load_2d_elect(st + kTileW, &tm_a, bar, kb * 128, m0);
-      if (++stage == kStages) {
-        stage = 0;
-        phase ^= 1u;
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage)) break;
+        uint8_t* st = smem + stage * kStageBytes;
+        mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+        tma_load_2d(st, &tm_w, &full_bar[stage], kb * 128, nb * kRows);
+        tma_load_2d(st + kTileW, &tm_a, &full_bar[stage], kb * 128, m0);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
     }
   } else if (warp == 1 || warp == 2) {
-    constexpr uint32_t idesc = make_idesc(2, kFmtS8, kFmtS8, kRows, kCols);
-    for (int kb = warp - 1; kb < num_kb; kb += 2) {
-      const int stage = kb % kStages;
-      const uint32_t phase = static_cast<uint32_t>(kb / kStages) & 1u;
-      const int slot = kb % kSlots;
-      const uint32_t slot_phase = static_cast<uint32_t>(kb / kSlots) & 1u;
-      if (!mbar_wait_warp(full0 + stage * 8, phase, env, kTagFull | stage)) break;
-      if (!mbar_wait_warp(slot_empty0 + slot * 8, slot_phase ^ 1u, env, kTagSlotEmpty | slot)) break;
-      tc_fence_after();
-      const uint32_t st = smem0 + stage * kStageBytes;
-      const uint64_t wdesc = make_desc_sw128(st);
-      const uint64_t adesc = make_desc_sw128(st + kTileW);
-      const uint32_t d = tmem_base + static_cast<uint32_t>(slot * kSlotCols);
-      const int ng = min(4, groups - kb * 4);
-      for (int g = 0; g < ng; ++g) umma_i8_elect(d + g * kCols, wdesc + g * 2, adesc + g * 2, idesc, 0u);
-      umma_commit_elect(slot_full0 + slot * 8);
-      umma_commit_elect(empty0 + stage * 8);
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(2, kFmtS8, kFmtS8, kRows, kCols);
+      for (int kb = warp - 1; kb < num_kb; kb += 2) {
+        const int stage = kb % kStages;
+        const uint32_t phase = static_cast<uint32_t>(kb / kStages) & 1u;
+        const int slot = kb % kSlots;
+        const uint32_t slot_phase = static_cast<uint32_t>(kb / kSlots) & 1u;
+        if (!mbar_wait(&full_bar[stage], phase, env, kTagFull | stage)) break;
+        if (!mbar_wait(&slot_empty_bar[slot], slot_phase ^ 1u, env, kTagSlotEmpty | slot)) break;
+        tc_fence_after();
+        const uint32_t st = smem_u32(smem + stage * kStageBytes);
+        const uint64_t wdesc = make_desc_sw128(st);
+        const uint64_t adesc = make_desc_sw128(st + kTileW);
+        const uint32_t d = tmem_base + static_cast<uint32_t>(slot * kSlotCols);
+        const int ng = min(4, groups - kb * 4);
+        for (int g = 0; g < ng; ++g) umma_i8(d + g * kCols, wdesc + g * 2, adesc + g * 2, idesc, 0u);
+        umma_commit(&slot_full_bar[slot]);
+        umma_commit(&empty_bar[stage]);
+      }
     }
   } else if (warp >= kFirstEpiWarp) {
     // ------------------------------- epilogue ---------------------------------------------------
@@ -162,30 +161,22 @@ gemm_o1_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 #pragma unroll
       for (int g = 0; g < 4; ++g) tmem_wait_ld_for(p[g]);
     };
-    // convert, multiply and accumulate as separate in-place passes: runs of independent instructions.
-    // Only the columns that hold activation rows are touched (nvalid is the same for the whole warp):
-    // with one or two activation rows the arithmetic of the padding columns would dominate the chain.
-    const int nvalid = min(kColsPerWarp, max(0, M - mc));
+    // convert, multiply and accumulate as separate in-place passes: runs of independent instructions
     auto accumulate = [&](uint32_t (&p)[4][kColsPerWarp], uint32_t codes, int ng) {
 #pragma unroll
-      for (int j = 0; j < kColsPerWarp; ++j)
-        if (j < nvalid) {
+      for (int g = 0; g < 4; ++g)
 #pragma unroll
-          for (int g = 0; g < 4; ++g) p[g][j] = __float_as_uint(__int2float_rn(static_cast<int>(p[g][j])));
-        }
+        for (int j = 0; j < kColsPerWarp; ++j) p[g][j] = __float_as_uint(__int2float_rn(static_cast<int>(p[g][j])));
 #pragma unroll
-      for (int j = 0; j < kColsPerWarp; ++j)
-        if (j < nvalid) {
+      for (int g = 0; g < 4; ++g)
 #pragma unroll
-          for (int g = 0; g < 4; ++g) p[g][j] = __float_as_uint(__fmul_rn(__uint_as_float(p[g][j]), asc[j]));
-        }
+        for (int j = 0; j < kColsPerWarp; ++j) p[g][j] = __float_as_uint(__fmul_rn(__uint_as_float(p[g][j]), asc[j]));
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         if (g < ng) {
           const float s = ue8m0_half_to_float((codes >> (8 * g)) & 0xFFu);
 #pragma unroll
-          for (int j = 0; j < kColsPerWarp; ++j)
-            if (j < nvalid) acc[j] = __fmaf_rn(__uint_as_float(p[g][j]), s, acc[j]);
+          for (int j = 0; j < kColsPerWarp; ++j) acc[j] = __fmaf_rn(__uint_as_float(p[g][j]), s, acc[j]);
         }
       }
     };
