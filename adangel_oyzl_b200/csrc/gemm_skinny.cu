@@ -5,9 +5,11 @@
 // Y^T[n, m] = W[n, :] . A[m, :]^T with the 128 MMA rows taken from W and the MMA N extent equal to M
 // rounded up to 16.  A 128-row block of W is handled by a cluster of S CTAs (S = 1, 2 or 4, chosen so
 // that the grid covers the GPU once): each walks 1/S of K, accumulates in its tensor memory, and the
-// partial sums meet in the first CTA's shared memory (distributed shared memory: plain remote stores
-// into the stage buffers that its finished MMAs no longer need), which adds them in rank order --
-// deterministic -- and writes the block of Y.  For O2 the accumulation order is free, so the split
+// partial sums meet in the first CTA's shared memory (distributed shared memory: plain remote stores),
+// which adds them in rank order -- deterministic -- and writes the block of Y.  Up to 16 activation rows
+// the partials land in the part of the stage buffers that no copy ever writes (the TMA box of A is 16
+// rows of the 64-row tile) and are announced by remote mbarrier arrivals; above that they land in the
+// stage buffers proper, between two cluster-wide meetings (after the first one every CTA's MMAs are done).  For O2 the accumulation order is free, so the split
 // changes results only within the rounding of the FP32 sums.  (A launch of this kernel costs about
 // 6.5 us before the first K slab is consumed and 0.3 us per slab after that; an earlier split over
 // independent CTAs with a last-arriver reduction through global memory cost more than it saved.)
@@ -62,7 +64,7 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t local_addr, uint32_t rank
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
                       const uint8_t* __restrict__ sf_w, const uint8_t* __restrict__ sf_a, float* __restrict__ y,
-                      int M, int N, int K, int ldy, uint32_t* status) {
+                      int M, int N, int K, int ldy, int a_box, uint32_t* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -70,7 +72,8 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   uint64_t* empty_bar = bars + kStages;
   uint64_t* acc_bar = bars + 2 * kStages;
   uint64_t* sf_full_bar = acc_bar + 1;
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sf_full_bar + kStages);
+  uint64_t* reduce_bar = sf_full_bar + kStages;  // first CTA of a cluster: the other ranks' partial sums have landed
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(reduce_bar + 1);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -92,6 +95,7 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       mbar_init(&sf_full_bar[s], 1);
     }
     mbar_init(acc_bar, 1);
+    mbar_init(reduce_bar, static_cast<uint32_t>((split - 1) * 128));
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -107,6 +111,9 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
+  // every CTA's barriers exist before another CTA of the cluster signals one: arrive now, wait where the first
+  // remote access is made (long after, so the wait costs nothing)
+  if (split > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
   // The one-instruction-at-a-time roles run as converged warps with one elected lane per instruction:
   // a lone thread inside a divergent branch needs 100 - 160 cycles per copy or MMA instruction, which
@@ -126,7 +133,7 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         tma_load_2d_elect(st, &tm_w, bar, kb * 128, nb * kRows);
         bulk_load_elect(st + kTileW + kTileA, sf_w + (static_cast<long>(nb) * katoms + kb * 2) * 512, kSf, bar);
       } else {
-        mbar_expect_tx_elect(bar, kTileA + kSf);
+        mbar_expect_tx_elect(bar, static_cast<uint32_t>(a_box * 128 + kSf));
         tma_load_2d_elect(st + kTileW, &tm_a, bar, kb * 128, 0);
         bulk_load_elect(st + kTileW + kTileA + kSf, sf_a + static_cast<long>(kb * 2) * 512, kSf, bar);
       }
@@ -189,7 +196,7 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     }
   }
 
-  // ---- every thread: the cluster meets twice (a cluster of one passes straight through) ----------------
+  // ---- every thread: the partial sums of a cluster meet in its first CTA (a cluster of one passes straight through)
   // epilogue warps 2-5: lane = one row n of W, registers = the M outputs of that row
   const bool epi = warp >= 2 && warp < 6;
   uint32_t r[2][32];
@@ -211,7 +218,78 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       }
     }
   }
-  if (split > 1) {
+  // Up to 16 activation rows: the TMA box of A covers 16 rows, so rows 16..63 of every stage's A tile (6 KB per
+  // stage, 24 KB) are never written by a copy.  The other ranks store their partial sums there and arrive on the
+  // first CTA's barrier: no cluster-wide meeting after the K loop (two of them cost 2000 cycles of a 9000-cycle CTA).
+  // A unit = 128 rows x 4 floats of one (rank, group of four activation rows) = 2 KB; three units per stage.
+  const bool direct = a_box <= 16;
+  if (split > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (split > 1 && direct) {
+    const int row = q * 32 + lane;
+    const uint32_t m_groups = (static_cast<uint32_t>(M) + 3u) / 4u;
+    auto unit_offset = [&](int rank_m1, int g) -> uint32_t {
+      const int u = rank_m1 * 4 + g;
+      return static_cast<uint32_t>((u / 3) * kStageBytes + kTileW + 16 * 128 + (u % 3) * 2048);
+    };
+    if (epi && rank != 0) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (static_cast<uint32_t>(g) < m_groups) {
+          const uint32_t v[4] = {r[0][g * 4], r[0][g * 4 + 1], r[0][g * 4 + 2], r[0][g * 4 + 3]};
+          st_cluster_v4(smem_u32(smem) + unit_offset(rank - 1, g) + static_cast<uint32_t>(row) * 16u, 0u, v);
+        }
+      }
+      // release at cluster scope: the stores above are visible to whoever sees this arrival
+      uint32_t remote_bar;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(smem_u32(reduce_bar)), "r"(0u));
+      asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+    }
+    if (epi && rank == 0 && have) {
+      // bounded wait, acquire at cluster scope
+      const uint32_t bar = smem_u32(reduce_bar);
+      const unsigned long long t0 = global_timer_ns();
+      uint32_t done = 0, spins = 0;
+      while (true) {
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(0u)
+            : "memory");
+        if (done) break;
+        if ((++spins & 0x3FFu) == 0 && (*abort_flag || global_timer_ns() - t0 > kWaitTimeoutNs)) {
+          if (!*abort_flag) {
+            *abort_flag = 1;
+            if (atomicCAS(status, 0u, static_cast<uint32_t>(kStatusWaitTimeout)) == 0u) {
+              status[1] = kTagAcc | 0x80u;
+              status[2] = blockIdx.x;
+              status[3] = 0;
+            }
+          }
+          have = false;
+          break;
+        }
+      }
+      if (have) {
+        for (int other = 1; other < split; ++other) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (static_cast<uint32_t>(g) < m_groups) {
+              const float4 p = *reinterpret_cast<const float4*>(smem + unit_offset(other - 1, g) + row * 16);
+              uint32_t* dst = &r[0][g * 4];
+              dst[0] = __float_as_uint(__uint_as_float(dst[0]) + p.x);
+              dst[1] = __float_as_uint(__uint_as_float(dst[1]) + p.y);
+              dst[2] = __float_as_uint(__uint_as_float(dst[2]) + p.z);
+              dst[3] = __float_as_uint(__uint_as_float(dst[3]) + p.w);
+            }
+          }
+        }
+      }
+    }
+  } else if (split > 1) {
     // 1st meeting: every CTA's MMAs are done (its epilogue warps have seen the accumulator complete), so the
     // first CTA's stage buffers are free to receive the partials.  (__syncthreads first: the one-thread roles'
     // warps arrive reconverged.)
@@ -252,9 +330,17 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   if (epi && have && rank == 0) {
     const int n = nb * kRows + q * 32 + lane;
     if (n < N) {
+      // guards in blocks of eight rows: a lone warp pays a few cycles for every instruction it issues
 #pragma unroll
-      for (int m = 0; m < kMaxM; ++m)
-        if (m < M) y[static_cast<long>(m) * ldy + n] = __uint_as_float(r[m >> 5][m & 31]);
+      for (int blk = 0; blk < kMaxM / 8; ++blk) {
+        if (blk * 8 < M) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int m = blk * 8 + j;
+            if (m < M) y[static_cast<long>(m) * ldy + n] = __uint_as_float(r[m >> 5][m & 31]);
+          }
+        }
+      }
     }
   }
 
@@ -289,7 +375,9 @@ int plan_o2_skinny(GemmPlan* plan, const void* a_mxfp4, const void* sfa_tiled, c
   const uint64_t kbytes = static_cast<uint64_t>(K) / 2;
   if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_mxfp4, N, kbytes, kbytes, kRows, 128))
     return rc;
-  if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_mxfp4, M, kbytes, kbytes, kMaxM, 128))
+  // up to 16 activation rows: a 16-row box, which leaves the rest of every stage's A tile to the partial sums
+  plan->block_n = M <= 16 ? 16 : kMaxM;
+  if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_mxfp4, M, kbytes, kbytes, plan->block_n, 128))
     return rc;
   plan->tm_y = plan->tm_a;
   // split K over a cluster of 1, 2 or 4 CTAs: as many as keep the grid within what the GPU holds at once (two
@@ -317,7 +405,7 @@ int run_gemm_o2_skinny(const GemmPlan& p, cudaStream_t stream) {
   config.attrs = &attr;
   config.numAttrs = 1;
   return check_cuda(cudaLaunchKernelEx(&config, gemm_o2_skinny_kernel, p.tm_b, p.tm_a, static_cast<const uint8_t*>(p.sfb),
-                                       static_cast<const uint8_t*>(p.sfa), p.y, p.M, p.N, p.K, p.ldy, p.status),
+                                       static_cast<const uint8_t*>(p.sfa), p.y, p.M, p.N, p.K, p.ldy, p.block_n, p.status),
                     "gemm_o2_skinny_kernel launch");
 }
 
