@@ -93,7 +93,7 @@ struct DeviceBuffer {
 
 extern "C" {
 
-int adg_abi_version(void) { return 102; }
+int adg_abi_version(void) { return 103; }
 
 const char* adg_last_error(void) { return last_error_cstr(); }
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_uint32, c_void_p
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_uint32, c_uint64, c_void_p
 from pathlib import Path
 
 _LIB_PATH = Path(__file__).resolve().parents[1] / "lib" / "libadangel_b200.so"
@@ -58,6 +58,17 @@ class PlanDesc(ctypes.Structure):
     ]
 
 
+MAX_PEER_BLOCKS = 16
+PEER_HANDLE_BYTES = 64
+
+
+class PeerBlocks(ctypes.Structure):
+    """``adg_peer_blocks`` of include/adangel_b200.h."""
+
+    _fields_ = [("src", c_void_p * MAX_PEER_BLOCKS), ("col0", c_int * MAX_PEER_BLOCKS), ("width", c_int * MAX_PEER_BLOCKS),
+                ("count", c_int)]
+
+
 _SIGNATURES = {
     "adg_abi_version": (c_int, []),
     "adg_last_error": (c_char_p, []),
@@ -92,6 +103,10 @@ _SIGNATURES = {
     "adg_o2_linear_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int]),
     "adg_benchmark": (c_int, [POINTER(BenchArgs)]),
     "adg_verify_layout": (c_int, [POINTER(c_int), POINTER(c_float)]),
+    "adg_peer_export": (c_int, [c_void_p, c_void_p, POINTER(c_uint64)]),
+    "adg_peer_open": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "adg_peer_close": (c_int, [c_void_p]),
+    "adg_gather_columns_pull": (c_int, [POINTER(PeerBlocks), c_void_p, c_int, c_int64, c_void_p]),
     "adg_session_create": (c_int, [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "adg_session_run": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "adg_session_submit": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),

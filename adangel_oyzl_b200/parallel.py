@@ -74,6 +74,111 @@ def gather_columns(y_local, n: int, group=None, align: int = TILE_ALIGN):
     return torch.cat([p[:, : n1 - n0] for p, (n0, n1) in zip(pieces, ranges)], dim=1)
 
 
+class PeerGather:
+    """Column blocks gathered by this rank's own kernel reading the other ranks' memory over NVLink.
+
+    One process per GPU on one node.  Every rank owns ``block`` (``[M, width_r]`` FP32, the ``out=`` of its
+    sharded GEMM); the allocations are exchanged once as CUDA IPC handles, and ``gather()`` runs ONE kernel
+    (``adg_gather_columns_pull``) that copies every block from where it lies -- the peers' memory included --
+    to its columns of a contiguous ``[M, N]``: no staging buffer and no permute pass, unlike
+    ``gather_columns`` (one NCCL all-gather plus a local permute of the whole matrix).  A tiny all-reduce on
+    the stream before the kernel orders it after every rank's producer, one after it keeps the blocks
+    unchanged until every rank has read them."""
+
+    def __init__(self, m: int, n: int, device, group=None, align: int = TILE_ALIGN):
+        import ctypes
+
+        import torch
+        import torch.distributed as dist
+
+        from .ops import _sm100
+
+        self._lib = _sm100.library()
+        self._sm100 = _sm100
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > _sm100.MAX_PEER_BLOCKS:
+            raise RuntimeError(f"at most {_sm100.MAX_PEER_BLOCKS} ranks")
+        self.m, self.n = m, n
+        self.ranges = all_ranges(n, self.world, align)
+        n0, n1 = self.ranges[self.rank]
+        self.device = torch.device(device)
+        self.block = torch.empty((m, n1 - n0), dtype=torch.float32, device=self.device)
+        self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
+        handle = (ctypes.c_ubyte * _sm100.PEER_HANDLE_BYTES)()
+        offset = ctypes.c_uint64(0)
+        with torch.cuda.device(self.device):
+            _sm100._check(self._lib.adg_peer_export(self.block.data_ptr(), handle, ctypes.byref(offset)))
+        mine = (bytes(handle), int(offset.value))
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+        self._bases = {}
+        self._ptrs = []
+        failure = None
+        for r, (peer_handle, peer_offset) in enumerate(everyone):
+            if r == self.rank:
+                self._ptrs.append(self.block.data_ptr())
+                continue
+            base = ctypes.c_void_p()
+            buf = (ctypes.c_ubyte * _sm100.PEER_HANDLE_BYTES).from_buffer_copy(peer_handle)
+            with torch.cuda.device(self.device):
+                if failure is None and self._lib.adg_peer_open(buf, ctypes.byref(base)) != 0:
+                    failure = self._lib.adg_last_error().decode("utf-8", "replace")
+            self._bases[r] = base.value
+            self._ptrs.append((base.value or 0) + peer_offset)
+        # all ranks agree on the outcome before anyone enters a collective that the others would not join
+        ok = torch.tensor([0.0 if failure else 1.0], device=self.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if float(ok.item()) == 0.0:
+            for base in self._bases.values():
+                if base:
+                    self._lib.adg_peer_close(base)
+            self._bases = {}
+            raise RuntimeError(failure or "a peer could not map this rank's memory")
+        # every rank starts with its right-hand neighbour, so that the links are used evenly
+        order = [(self.rank + 1 + i) % self.world for i in range(self.world)]
+        blocks = _sm100.PeerBlocks()
+        for i, r in enumerate(order):
+            blocks.src[i] = self._ptrs[r]
+            blocks.col0[i] = self.ranges[r][0]
+            blocks.width[i] = self.ranges[r][1] - self.ranges[r][0]
+        blocks.count = self.world
+        self._blocks = blocks
+
+    def _fence(self):
+        import torch.distributed as dist
+
+        dist.all_reduce(self._token, group=self.group)
+
+    def gather(self, out=None):
+        """``[M, N]`` on every rank from the ranks' ``block`` buffers.  Stream-ordered, asynchronous."""
+        import ctypes
+
+        import torch
+
+        full = out if out is not None else torch.empty((self.m, self.n), dtype=torch.float32, device=self.device)
+        if full.shape != (self.m, self.n) or full.dtype != torch.float32 or full.stride(1) != 1:
+            raise RuntimeError("out must be an [M, N] float32 matrix with unit column stride")
+        self._fence()
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            self._sm100._check(self._lib.adg_gather_columns_pull(ctypes.byref(self._blocks), full.data_ptr(), self.m,
+                                                                 full.stride(0), stream))
+        self._fence()
+        return full
+
+    def close(self):
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)  # nobody unmaps while a peer may still be reading
+        for base in self._bases.values():
+            self._lib.adg_peer_close(base)
+        self._bases = {}
+
+
 @dataclass
 class ShardedWeights:
     """One rank's slice of the weights in the forms the three variants consume."""

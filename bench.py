@@ -330,6 +330,31 @@ def sharded_block(dist, world: int, rank: int, dev) -> dict:
         out["gather_received_gb_per_gpu"] = 4.0 * m * (n - (n1 - n0)) / 1e9
         out["gather_tb_per_s_received"] = out["gather_received_gb_per_gpu"] / out["gather_ms"]
         assert tuple(full.shape) == (m, n)
+        # the same gather by this rank's own kernel reading the peers' blocks over NVLink (no staging, no permute)
+        try:
+            peers = parallel.PeerGather(m, n, dev)
+        except RuntimeError as exc:  # raised on every rank or on none
+            out["gather_peer_ms"] = None
+            out["gather_peer_error"] = str(exc)[:200]
+            peers = None
+        if peers is not None:
+            peers.block.copy_(y)
+            peers.gather(out=full)  # warm-up
+            times = []
+            for _ in range(3):
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                peers.gather(out=full)
+                e1.record()
+                barrier()
+                times.append(max_over_ranks(e0.elapsed_time(e1)))
+            out["gather_peer_ms"] = min(times)
+            out["gather_peer_ms_all"] = times
+            out["gather_peer_tb_per_s_received"] = out["gather_received_gb_per_gpu"] / out["gather_peer_ms"]
+            out["gather_peer_path"] = ("adg_gather_columns_pull: one kernel per rank, 16-byte loads from the peers' memory (CUDA IPC), "
+                                       "a one-element all-reduce before and after it inside the timed region")
+            peers.close()
         del full
     kernels.check_status(dev)
     return out

@@ -328,6 +328,37 @@ int adg_benchmark(adg_bench_args* args);
  * (csrc/sm120/o2_microkernel.cu:49-115).  Synchronises. */
 int adg_verify_layout(int* passed, float* max_abs_error);
 
+/* ---- gathering N-sharded results over NVLink ----------------------------------------------------- */
+/* One process per GPU on one node, W sharded along N: rank r holds Y[:, n0_r:n1_r] as a contiguous
+ * [M, width_r] FP32 buffer.  The reference is single-GPU and has no counterpart; these entry points
+ * replace a library all-gather plus a local permute by ONE kernel that reads the other ranks' blocks
+ * from their memory (CUDA IPC mappings, plain loads over NVLink) and writes them to their columns of a
+ * contiguous [M, N] on this rank. */
+
+#define ADG_PEER_HANDLE_BYTES 64
+#define ADG_MAX_PEER_BLOCKS 16
+
+/* Exports the allocation that contains `ptr` (device memory from cudaMalloc, e.g. a torch tensor's
+ * storage): 64 opaque bytes to send to the other processes, and ptr's offset inside the allocation. */
+int adg_peer_export(const void* ptr, void* handle64, uint64_t* offset);
+/* Maps an allocation exported by another process of this node; *base + offset is the peer's `ptr`.
+ * Enables peer access between the two devices.  One open per handle per process. */
+int adg_peer_open(const void* handle64, void** base);
+int adg_peer_close(void* base);
+
+typedef struct adg_peer_blocks {
+  const float* src[ADG_MAX_PEER_BLOCKS]; /* contiguous [M, width] blocks: own memory or adg_peer_open mappings */
+  int col0[ADG_MAX_PEER_BLOCKS];         /* first destination column; a multiple of 4 */
+  int width[ADG_MAX_PEER_BLOCKS];        /* columns; a multiple of 4 */
+  int count;
+} adg_peer_blocks;
+
+/* y[row, col0_b + c] = src_b[row, c] for every block, on `stream`; y is [M, ldy] FP32, 16-byte
+ * aligned, ldy a multiple of 4.  The kernel waits for nobody: order it after every rank's producer of
+ * its block (a collective or barrier on the stream), and keep the blocks unchanged until every rank's
+ * gather has finished.  Asynchronous. */
+int adg_gather_columns_pull(const adg_peer_blocks* blocks, float* y, int M, int64_t ldy, void* stream);
+
 /* ---- host-buffer sessions ---------------------------------------------------------------------- */
 /* A session keeps one weight matrix resident on the device in the form a variant's GEMM consumes
  * (the steady-state case: weights converted once, activations arriving from the host each call). */

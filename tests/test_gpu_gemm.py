@@ -86,9 +86,9 @@ def test_ragged_shapes(K, shape):
 
 
 @pytest.mark.parametrize("shape", [(1, 128, 64), (16, 256, 192), (17, 200, 320), (64, 384, 320), (5, 4096, 1024),
-                                   (48, 136, 2048), (33, 128, 4096), (64, 1024, 4096)])
+                                   (48, 136, 2048), (33, 128, 4096), (64, 1024, 4096), (64, 4992, 256), (33, 9600, 128)])
 def test_decode_shapes(K, shape):
-    # M <= 64 without the partial dump: the operand-swapped O1 and O2 kernels
+    # M <= 64 without the partial dump: the operand-swapped O1 and O2 kernels (the last two shapes: more CTAs than SMs)
     m, n, k = shape
     _compare(K, *orc.canonical_inputs(m, n, k, seed=13), dump=False)
 

@@ -40,10 +40,18 @@ def _worker(rank, world, port, shape, queue):
         parallel.broadcast_activations(ta, ts, src=0)
         shard = parallel.shard_weights(torch.from_numpy(w_mx), torch.from_numpy(w_sc), world, rank, device=dev)
         out = {}
+        peers = parallel.PeerGather(m, n, dev)
         for variant in ("o0", "o1", "o2"):
             block = parallel.sharded_gemm(variant, ta, ts, shard)
             kernels.check_status(dev)
             out[variant] = parallel.gather_columns(block, n).cpu().numpy()
+            # the same blocks gathered by this rank's own kernel from the peers' memory: identical bytes
+            parallel.sharded_gemm(variant, ta, ts, shard, out=peers.block)
+            kernels.check_status(dev)
+            pulled = peers.gather()
+            torch.cuda.synchronize(dev)
+            out[variant + "_pulled_equal"] = bool((pulled.cpu().numpy() == out[variant]).all())
+        peers.close()
         if rank == 0:
             queue.put(out)
     finally:
@@ -80,6 +88,7 @@ def test_two_gpu_sharded_equals_single_gpu_and_oracle():
     K.check_status()
     for variant in ("o0", "o1", "o2"):
         np.testing.assert_array_equal(sharded[variant], single[variant])
+        assert sharded[variant + "_pulled_equal"], f"{variant}: the peer-memory gather differs from the NCCL gather"
     np.testing.assert_array_equal(sharded["o1"], orc.run_o1(a_int8, a_scale, w_mx, w_sc)["output"])
     np.testing.assert_allclose(sharded["o0"], orc.run_o0(a_int8, a_scale, w_mx, w_sc)["output"], rtol=1e-3, atol=1e-3)
     np.testing.assert_allclose(sharded["o2"], orc.run_o2(a_int8, a_scale, w_mx, w_sc)["output"], rtol=1e-3, atol=1e-3)
