@@ -118,8 +118,6 @@ int adg_gather_columns_pull(const adg_peer_blocks* blocks, float* y, int M, int6
   if (blocks->count <= 0 || blocks->count > ADG_MAX_PEER_BLOCKS) return fail("adg_gather_columns_pull: bad block count");
   if (M <= 0 || ldy <= 0 || (ldy & 3) != 0 || (reinterpret_cast<uintptr_t>(y) & 15u) != 0)
     return fail("adg_gather_columns_pull: y must be 16-byte aligned with ldy a multiple of 4");
-  DeviceCtx* ctx = nullptr;
-  if (int rc = device_ctx(&ctx)) return rc;
   GatherBlocks g{};
   g.count = blocks->count;
   uint64_t most = 0;
@@ -137,6 +135,8 @@ int adg_gather_columns_pull(const adg_peer_blocks* blocks, float* y, int M, int6
     g.magic[b] = width == 4 ? 0xFFFFFFFFu : fast_div_magic(static_cast<uint32_t>(width / 4));
     most = total > most ? total : most;
   }
+  DeviceCtx* ctx = nullptr;
+  if (int rc = device_ctx(&ctx)) return rc;
   const uint64_t per_wave = static_cast<uint64_t>(kGatherThreads) * kGatherUnroll;
   uint64_t grid = (most + per_wave - 1) / per_wave;
   uint64_t cap = static_cast<uint64_t>(ctx->sm_count) * kGatherCtasPerSm / static_cast<uint64_t>(blocks->count);

@@ -225,3 +225,22 @@ def test_c_abi_rejects_misaligned_and_null_pointers():
     for fn, args, message in cases:
         assert fn(*args) != 0, message
         assert message in lib.adg_last_error().decode(), (message, lib.adg_last_error())
+    # the gather over peer memory: block geometry is checked before any CUDA call
+    import ctypes
+
+    def blocks(src, col0, width, count=1):
+        b = _sm100.PeerBlocks()
+        b.src[0], b.col0[0], b.width[0], b.count = src, col0, width, count
+        return ctypes.byref(b)
+
+    gather_cases = [
+        ((blocks(base, 0, 64), base + 4, 8, 128, None), "y must be 16-byte aligned"),
+        ((blocks(base, 0, 64), base, 8, 126, None), "ldy a multiple of 4"),
+        ((blocks(base + 8, 0, 64), base, 8, 128, None), "block pointers must be non-NULL and 16-byte aligned"),
+        ((blocks(base, 2, 64), base, 8, 128, None), "block columns must be multiples of 4"),
+        ((blocks(base, 96, 64), base, 8, 128, None), "inside the row"),
+        ((blocks(base, 0, 64, count=0), base, 8, 128, None), "bad block count"),
+    ]
+    for args, message in gather_cases:
+        assert lib.adg_gather_columns_pull(*args) != 0, message
+        assert message in lib.adg_last_error().decode(), (message, lib.adg_last_error())
