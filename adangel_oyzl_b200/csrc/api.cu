@@ -93,7 +93,7 @@ struct DeviceBuffer {
 
 extern "C" {
 
-int adg_abi_version(void) { return 103; }
+int adg_abi_version(void) { return 104; }
 
 const char* adg_last_error(void) { return last_error_cstr(); }
 
@@ -228,6 +228,16 @@ int adg_gemm_o1(const void* a_int8, const void* a_scale, const void* w_int8, con
   return run_plan(plan, as_stream(stream));
 }
 
+int adg_gemm_o1_packed(const void* a_int8, const void* a_scale, const void* w_mxfp4, const void* w_scale, float* y, int M, int N,
+                       int K, int ldy, void* stream) {
+  if (check_ptr(a_int8, 16, "A_int8") || check_ptr(a_scale, 4, "A_scale") || check_ptr(w_mxfp4, 16, "W_mxfp4") ||
+      check_ptr(w_scale, 4, "W_scale") || check_ptr(y, 4, "Y"))
+    return 1;
+  GemmPlan plan;
+  if (int rc = plan_o1_packed(&plan, a_int8, a_scale, w_mxfp4, w_scale, y, M, N, K, ldy)) return rc;
+  return run_plan(plan, as_stream(stream));
+}
+
 int adg_gemm_o1_bf16(const void* a_bf16, const void* a_scale, const void* w_bf16, float* y, const void* range_flag, int M,
                      int N, int K, int ldy, void* stream) {
   GemmPlan plan;
@@ -358,6 +368,8 @@ int adg_benchmark(adg_bench_args* a) {
       // conversion is part of this build's GEMM stage; ADG_BENCH_O1_SPLIT_ACTIVATION reports it on its own
       has_a = (a->flags & ADG_BENCH_O1_SPLIT_ACTIVATION) != 0;
     } else {
+      // (the decode kernel can also read the packed weights themselves, adg_gemm_o1_packed: half the bytes, but
+      // 5 - 10 % slower because every thread expands its own nibbles; the reference's contract is the INT8 image)
       if (int rc = plan_o1(&plan, a->a_int8, a->a_scale, a->conv_weight, a->w_scale, a->output, nullptr, M, N, K, N))
         return rc;
       conv_w = [&]() { return launch_mxfp4_to_int8(a->w_mxfp4, a->conv_weight, N, K, stream); };

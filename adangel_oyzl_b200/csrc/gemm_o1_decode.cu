@@ -32,15 +32,16 @@ namespace adg {
 namespace {
 
 constexpr int kRowsD = 32;             // W rows per CTA: one per lane
-constexpr int kTileWD = kRowsD * 128;  // bytes of W per slab
+// bytes of W per slab (128 K elements): INT8 image, or the packed MXFP4 nibbles themselves
+__host__ __device__ constexpr int tile_w_bytes(bool packed) { return kRowsD * (packed ? 64 : 128); }
 
 enum : uint32_t { kTagFullD = 0x3600, kTagTokenD = 0x3700 };
 
 // MT activation rows per thread, T slabs per turn, RING warps.  Every warp owns T shared-memory slots.
 __host__ __device__ constexpr int a_rows_for(int mt) { return mt < 8 ? 8 : mt; }  // whole 8-row swizzle atoms
-__host__ __device__ constexpr int slot_bytes_for(int mt) { return kTileWD + a_rows_for(mt) * 128; }
-__host__ __device__ constexpr int smem_bytes_for(int mt, int t, int ring) {
-  return t * ring * slot_bytes_for(mt) + ring * mt * 32 * 4 + 1024 + 512;
+__host__ __device__ constexpr int slot_bytes_for(int mt, bool packed) { return tile_w_bytes(packed) + a_rows_for(mt) * 128; }
+__host__ __device__ constexpr int smem_bytes_for(int mt, int t, int ring, bool packed) {
+  return t * ring * slot_bytes_for(mt, packed) + ring * mt * 32 * 4 + 1024 + 512;
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -90,12 +91,13 @@ __device__ __forceinline__ bool token_wait(uint32_t bar, uint32_t parity, const 
 // MT = activation rows held per thread (M <= MT; rows past M are read as zero and never stored);
 // T = K slabs per turn of a warp; RING = warps.  Turn u covers slabs u*T .. u*T + T - 1 and belongs to
 // warp u % RING, which keeps those slabs in its own T shared-memory slots.
-template <int MT, int T, int RING>
+template <int MT, int T, int RING, bool PACKED>
 __global__ void __launch_bounds__(RING * 32, RING == 4 ? 3 : (MT <= 4 ? 2 : 1))
 gemm_o1_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
                       const float* __restrict__ a_scale, const uint8_t* __restrict__ w_scale, float* __restrict__ y,
                       int M, int N, int K, int ldy, uint32_t* status) {
-  constexpr int kSlotBytes = slot_bytes_for(MT);
+  constexpr int kSlotBytes = slot_bytes_for(MT, PACKED);
+  constexpr int kTileWD = tile_w_bytes(PACKED);
   constexpr int kSlots = T * RING;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -127,7 +129,7 @@ gemm_o1_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     const uint32_t st = smem0 + slot * kSlotBytes;
     const uint32_t bar = full0 + slot * 8;
     mbar_expect_tx_elect(bar, kSlotBytes);
-    tma_load_2d_elect(st, &tm_w, bar, kb * 128, nb * kRowsD);
+    tma_load_2d_elect(st, &tm_w, bar, kb * (PACKED ? 64 : 128), nb * kRowsD);
     tma_load_2d_elect(st + kTileWD, &tm_a, bar, kb * 128, 0);
   };
 #pragma unroll
@@ -152,8 +154,9 @@ gemm_o1_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 #pragma unroll
   for (int j = 0; j < MT; ++j) asc[j] = j < M ? __ldg(a_scale + j) : 0.0f;
 
-  const uint32_t w_off = static_cast<uint32_t>(lane * 128);
-  const uint32_t w_xor = static_cast<uint32_t>(lane & 7);
+  // INT8 rows: 128 bytes, 128-byte swizzle (chunk ^ row % 8); packed rows: 64 bytes, 64-byte swizzle (chunk ^ (row / 2) % 4)
+  const uint32_t w_off = static_cast<uint32_t>(lane * (PACKED ? 64 : 128));
+  const uint32_t w_xor = static_cast<uint32_t>(PACKED ? (lane >> 1) & 3 : lane & 7);
   const int prev = (warp + RING - 1) % RING;
   float* my_handoff = handoff + (warp * MT) * 32 + lane;
   const float* prev_handoff = handoff + (prev * MT) * 32 + lane;
@@ -183,8 +186,18 @@ gemm_o1_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           if (g < ng) {
-            const uint4 w0 = lds128(st + w_off + ((static_cast<uint32_t>(2 * g) ^ w_xor) << 4));
-            const uint4 w1 = lds128(st + w_off + ((static_cast<uint32_t>(2 * g + 1) ^ w_xor) << 4));
+            uint4 w0, w1;
+            if constexpr (PACKED) {
+              // 32 nibbles of this row's group -> their INT8 images 2 * E2M1, in K order
+              const uint4 c = lds128(st + w_off + ((static_cast<uint32_t>(g) ^ w_xor) << 4));
+              e2m1x8_to_int8x8(c.x, w0.x, w0.y);
+              e2m1x8_to_int8x8(c.y, w0.z, w0.w);
+              e2m1x8_to_int8x8(c.z, w1.x, w1.y);
+              e2m1x8_to_int8x8(c.w, w1.z, w1.w);
+            } else {
+              w0 = lds128(st + w_off + ((static_cast<uint32_t>(2 * g) ^ w_xor) << 4));
+              w1 = lds128(st + w_off + ((static_cast<uint32_t>(2 * g + 1) ^ w_xor) << 4));
+            }
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
               const uint32_t a_row = st + kTileWD + j * 128;
@@ -255,27 +268,35 @@ DecodeCfg choose_cfg(int M, int N, int sm_count) {
   return {mt, 2, ctas <= (mt <= 4 ? 2 : 1) * sm_count ? 8 : 4};
 }
 
-template <int MT, int T, int RING>
+template <int MT, int T, int RING, bool PACKED>
 int launch_decode(const GemmPlan& p, cudaStream_t stream) {
-  gemm_o1_decode_kernel<MT, T, RING><<<p.grid, RING * 32, smem_bytes_for(MT, T, RING), stream>>>(
+  gemm_o1_decode_kernel<MT, T, RING, PACKED><<<p.grid, RING * 32, smem_bytes_for(MT, T, RING, PACKED), stream>>>(
       p.tm_b, p.tm_a, static_cast<const float*>(p.a_scale), static_cast<const uint8_t*>(p.w_scale), p.y, p.M, p.N, p.K,
       p.ldy, p.status);
   return check_cuda(cudaGetLastError(), "gemm_o1_decode_kernel launch");
 }
 template <int MT, int T, int RING>
 int set_smem_attribute() {
-  return check_cuda(cudaFuncSetAttribute(gemm_o1_decode_kernel<MT, T, RING>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         smem_bytes_for(MT, T, RING)),
-                    "cudaFuncSetAttribute(gemm_o1_decode_kernel)");
+  if (int rc = check_cuda(cudaFuncSetAttribute(gemm_o1_decode_kernel<MT, T, RING, false>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_for(MT, T, RING, false)),
+                          "cudaFuncSetAttribute(gemm_o1_decode_kernel)"))
+    return rc;
+  return check_cuda(cudaFuncSetAttribute(gemm_o1_decode_kernel<MT, T, RING, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         smem_bytes_for(MT, T, RING, true)),
+                    "cudaFuncSetAttribute(gemm_o1_decode_kernel, packed W)");
 }
 template <int MT>
 int set_smem_attributes() {
   if (int rc = set_smem_attribute<MT, 2, 8>()) return rc;
   return set_smem_attribute<MT, 2, 4>();
 }
+template <int MT, int T, int RING>
+int launch_either(const GemmPlan& p, cudaStream_t stream) {
+  return p.packed_w ? launch_decode<MT, T, RING, true>(p, stream) : launch_decode<MT, T, RING, false>(p, stream);
+}
 template <int MT>
 int launch_for_ring(const GemmPlan& p, int ring, cudaStream_t stream) {
-  return ring == 8 ? launch_decode<MT, 2, 8>(p, stream) : launch_decode<MT, 2, 4>(p, stream);
+  return ring == 8 ? launch_either<MT, 2, 8>(p, stream) : launch_either<MT, 2, 4>(p, stream);
 }
 
 }  // namespace
@@ -293,13 +314,15 @@ int init_gemm_o1_decode_attributes() {
   return set_smem_attribute<16, 1, 8>();
 }
 
-// Plan for the decode-shape O1 GEMM: tm_b = W map (32-row boxes), tm_a = A map (all activation rows in one
+// Plan for the decode-shape O1 GEMM: tm_b = W map (32-row boxes; the INT8 image or, packed_w, the MXFP4 nibbles), tm_a = A map (all activation rows in one
 // box, rounded up to whole 8-row swizzle atoms; rows past M read as zero).
-int plan_o1_decode(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale,
-                   float* y, int M, int N, int K, int ldy) {
+int plan_o1_decode(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w, const void* w_scale, float* y,
+                   int M, int N, int K, int ldy, bool packed_w) {
   DeviceCtx* ctx = nullptr;
   if (int rc = device_ctx(&ctx)) return rc;
   if (M <= 0 || M > 16) return fail("plan_o1_decode: M must be in [1, 16]");
+  if ((reinterpret_cast<uintptr_t>(w_scale) & 3u) != 0 || (reinterpret_cast<uintptr_t>(a_scale) & 3u) != 0)
+    return fail("W_scale and A_scale must be 4-byte aligned");
   *plan = GemmPlan{};
   plan->variant = 1;
   plan->skinny = 2;
@@ -310,7 +333,11 @@ int plan_o1_decode(GemmPlan* plan, const void* a_int8, const void* a_scale, cons
   plan->status = ctx->status;
   const DecodeCfg cfg = choose_cfg(M, N, ctx->sm_count);
   plan->block_n = cfg.mt;
-  if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_int8, N, K, K, kRowsD, 128)) return rc;
+  plan->packed_w = packed_w ? 1 : 0;
+  // W: [N, K] INT8 in 128-byte boxes, or [N, K/2] packed nibbles in 64-byte boxes (64-byte swizzle)
+  const uint64_t w_pitch = packed_w ? static_cast<uint64_t>(K) / 2 : static_cast<uint64_t>(K);
+  if (int rc = encode_tensor_map_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w, N, w_pitch, w_pitch, kRowsD, packed_w ? 64 : 128))
+    return rc;
   if (int rc = encode_tensor_map_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_int8, M, K, K,
                                     a_rows_for(plan->block_n), 128))
     return rc;
@@ -326,7 +353,7 @@ int run_gemm_o1_decode(const GemmPlan& p, cudaStream_t stream) {
     case 2: return launch_for_ring<2>(p, p.grid_y, stream);
     case 4: return launch_for_ring<4>(p, p.grid_y, stream);
     case 8: return launch_for_ring<8>(p, p.grid_y, stream);
-    default: return launch_decode<16, 1, 8>(p, stream);
+    default: return launch_either<16, 1, 8>(p, stream);
   }
 }
 

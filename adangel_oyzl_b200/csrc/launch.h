@@ -120,6 +120,7 @@ struct GemmPlan {
   // decode-sized O1/O2 (M <= 64): operand-swapped kernels; tm_a = A map, tm_b = W map; `grid_y`
   // is the number of 16-row slices of A (O1) or the number of CTAs that share a W row block's K extent (O2)
   int skinny = 0, grid_y = 1;
+  int packed_w = 0;  // O1 decode kernel: W is the packed MXFP4 matrix itself, not its INT8 image
   int o1_bf16 = 0;                       // O1 with BF16 operands (weight scale folded into W)
   const uint32_t* range_flag = nullptr;  // O1 BF16: device word set by the operand conversions
   const uint32_t* only_if_flag = nullptr;  // O1 INT8: run only when this device word is non-zero
@@ -198,8 +199,10 @@ int plan_o1_skinny(GemmPlan* plan, const void* a_int8, const void* a_scale, cons
 int run_gemm_o1_skinny(const GemmPlan& plan, cudaStream_t stream);
 int init_gemm_o1_decode_attributes();
 bool o1_decode_applies(int M, int N, int sm_count);
-int plan_o1_decode(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale,
-                   float* y, int M, int N, int K, int ldy);
+int plan_o1_decode(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w, const void* w_scale, float* y,
+                   int M, int N, int K, int ldy, bool packed_w);
 int run_gemm_o1_decode(const GemmPlan& plan, cudaStream_t stream);
+int plan_o1_packed(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_mxfp4, const void* w_scale, float* y,
+                   int M, int N, int K, int ldy);
 
 }  // namespace adg

@@ -240,13 +240,25 @@ int plan_o0(GemmPlan* plan, const void* a_fp16, const void* w_fp16, float* y, in
   return finish_plan(plan, block_n);
 }
 
+// O1 straight from the packed MXFP4 weights (no INT8 image): only the decode kernel expands nibbles itself.
+int plan_o1_packed(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_mxfp4, const void* w_scale, float* y,
+                   int M, int N, int K, int ldy) {
+  if (int rc = check_shape(M, N, K, ldy)) return rc;
+  DeviceCtx* ctx = nullptr;
+  if (int rc = device_ctx(&ctx)) return rc;
+  if (!o1_decode_applies(M, N, ctx->sm_count))
+    return fail("O1 on packed weights is the decode kernel's form (M <= 8, or M <= 16 while N/32 does not exceed the SM "
+                "count); convert W with adg_mxfp4_to_int8 and use adg_gemm_o1 for this shape");
+  return plan_o1_decode(plan, a_int8, a_scale, w_mxfp4, w_scale, y, M, N, K, ldy, true);
+}
+
 int plan_o1(GemmPlan* plan, const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale, float* y,
             int32_t* partial_dump, int M, int N, int K, int ldy) {
   if (int rc = check_shape(M, N, K, ldy)) return rc;
   DeviceCtx* ctx = nullptr;
   if (int rc = device_ctx(&ctx)) return rc;
   if (partial_dump == nullptr && o1_decode_applies(M, N, ctx->sm_count))
-    return plan_o1_decode(plan, a_int8, a_scale, w_int8, w_scale, y, M, N, K, ldy);
+    return plan_o1_decode(plan, a_int8, a_scale, w_int8, w_scale, y, M, N, K, ldy, false);
   if (M <= 64 && partial_dump == nullptr) return plan_o1_skinny(plan, a_int8, a_scale, w_int8, w_scale, y, M, N, K, ldy);
   return plan_o1_tiled(plan, a_int8, a_scale, w_int8, w_scale, y, partial_dump, M, N, K, ldy);
 }

@@ -246,6 +246,26 @@ def gemm_o1(a_int8, a_scale, w_int8, w_scale, out=None, dump_partials=False):
     return (out, partials) if dump_partials else out
 
 
+def gemm_o1_packed(a_int8, a_scale, w_mxfp4, w_scale, out=None):
+    """O1 for decode-sized activations straight from the packed MXFP4 weights (same bits as :func:`gemm_o1`;
+    M <= 8, or M <= 16 while N/32 does not exceed the SM count -- other shapes raise)."""
+    import torch
+
+    m, k = a_int8.shape
+    n = w_mxfp4.shape[0]
+    dev = a_int8.device
+    _operand(a_int8, "A_int8", torch.int8)
+    _operand(a_scale, "A_scale", torch.float32, (m,), dev)
+    _operand(w_mxfp4, "W_mxfp4", torch.uint8, (n, k // 2), dev)
+    _operand(w_scale, "W_scale", torch.uint8, (n, k // 32), dev)
+    out, ldy = _output(out, m, n, a_int8.device)
+    with torch.cuda.device(a_int8.device):
+        _sm100._check(_lib().adg_gemm_o1_packed(
+            a_int8.data_ptr(), a_scale.data_ptr(), w_mxfp4.data_ptr(), w_scale.data_ptr(), out.data_ptr(), m, n, k, ldy,
+            _stream(out)))
+    return out
+
+
 def gemm_o1_bf16(a_bf16, a_scale, w_bf16, range_flag, out=None):
     """O1 on BF16 operands (same bits as :func:`gemm_o1` while ``range_flag`` stays zero; otherwise the
     kernel refuses and the next status check raises)."""

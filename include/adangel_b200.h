@@ -147,6 +147,16 @@ int adg_gemm_o0(const void* a_fp16, const void* w_fp16, float* y, int M, int N, 
 int adg_gemm_o1(const void* a_int8, const void* a_scale, const void* w_int8, const void* w_scale, float* y,
                 int32_t* partial_dump, int M, int N, int K, int ldy, void* stream);
 
+/* O1 for decode-sized activations straight from the packed weights: the same recurrence and the same bits
+ * as adg_gemm_o1, with W read as MXFP4 nibbles (N*K/2 bytes instead of the N*K of its INT8 image) and
+ * expanded to 2*E2M1 inside the kernel.  M <= 8, or M <= 16 while N/32 does not exceed the SM count;
+ * other shapes are refused with an error (use adg_mxfp4_to_int8 + adg_gemm_o1).  Half the DRAM traffic of
+ * adg_gemm_o1 and no INT8 image to keep resident, for 5 - 10 % more time (every thread expands its own
+ * nibbles): the form for servers that hold only the packed weights.  No reference
+ * counterpart: the reference's O1 always consumes the INT8 image (csrc/sm120/o1_gemm.cu:367-392). */
+int adg_gemm_o1_packed(const void* a_int8, const void* a_scale, const void* w_mxfp4, const void* w_scale, float* y, int M, int N,
+                       int K, int ldy, void* stream);
+
 /* O1 GEMM on BF16 operands: the same recurrence and the same bits as adg_gemm_o1, computed with the
  * weight's power-of-two scale folded into the tensor-core operand (tcgen05 kind::f16, BF16 x BF16,
  * FP32 accumulate): each K32 partial leaves the tensor core as float(P) * 2^(W_scale-128), exact, and

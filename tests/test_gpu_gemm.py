@@ -106,7 +106,22 @@ def test_o1_decode_ring_shapes(K, shape):
     y = torch.full((m, n), float("nan"), device="cuda")
     K.gemm_o1(da, ds, K.mxfp4_to_int8(dw), dws, out=y)
     K.check_status()
-    np.testing.assert_array_equal(y.cpu().numpy(), orc.run_o1(a_int8, a_scale, w_mx, w_sc)["output"])
+    want = orc.run_o1(a_int8, a_scale, w_mx, w_sc)["output"]
+    np.testing.assert_array_equal(y.cpu().numpy(), want)
+    # the same kernel reading the packed MXFP4 weights themselves
+    y.fill_(float("nan"))
+    K.gemm_o1_packed(da, ds, dw, dws, out=y)
+    K.check_status()
+    np.testing.assert_array_equal(y.cpu().numpy(), want)
+
+
+def test_o1_packed_refuses_shapes_of_the_tile_kernels(K):
+    import torch
+
+    a_int8, a_scale, w_mx, w_sc = orc.canonical_inputs(40, 128, 128, seed=2)
+    da, ds, dw, dws = to_cuda(a_int8, a_scale, w_mx, w_sc)
+    with pytest.raises(RuntimeError, match="decode kernel"):
+        K.gemm_o1_packed(da, ds, dw, dws)
 
 
 def test_decode_matches_prefill_rows(K):

@@ -23,7 +23,7 @@ def test_library_exports_declared_symbols():
     for name in sorted(declared):
         assert hasattr(lib, name), f"{name} is declared but not exported"
     assert declared == set(_sm100.EXPORTED_SYMBOLS)
-    assert lib.adg_abi_version() == 103
+    assert lib.adg_abi_version() == 104
     caps = _sm100.capabilities()
     for key in ("compiled_sm100a", "o0_fp16_tc", "o1_int8_tc", "o2_mxf4_block_scale", "o2_cutlass_tiled"):
         assert caps[key] is True
