@@ -171,6 +171,60 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// ---- the same instructions issued by a converged warp (all 32 lanes call, one elected lane issues): a lone
+// thread inside a divergent branch needs 100 - 160 cycles per copy or MMA instruction
+__device__ __forceinline__ void tma_load_2d_pair_elect(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "@P cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      "}\n" ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                    uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, P;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "@P tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_mxf4_pair_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                     uint32_t accumulate, uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, P;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "@P tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_cp_pair_32x128b_warpx4_elect(uint32_t taddr, uint64_t sdesc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "@P tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;\n"
+      "}\n" ::"r"(taddr), "l"(sdesc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair_elect(uint32_t cluster_addr) {
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "@P tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+      "}\n" ::"r"(cluster_addr)
+      : "memory");
+}
+
 struct TileCoord {
   int m_pair, n_blk;
 };
@@ -261,114 +315,246 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   }
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs) ---------------------------------
-    if (lane == 0) {
+    if constexpr (!FUSED) {
+      // converged warp, one elected lane per instruction
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      const uint32_t full_leader = map_to_cta(smem_u32(full_bar), 0);
-      uint32_t seen_rows = 0;  // FUSED: the counter of this tile's row block as read one tile earlier
+      const uint32_t smem0 = smem_u32(smem), full_own = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+      const uint32_t full_leader = map_to_cta(full_own, 0);
       for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
         const TileCoord tc = tile_coord(tile, num_mp, num_n);
         const int m_blk = tc.m_pair * 2 + static_cast<int>(rank);
         const int row0 = m_blk * kBlockM;
         const int wrow0 = tc.n_blk * kBlockN + static_cast<int>(rank) * kHalfN;
-        if constexpr (FUSED) {
-          // this CTA's 128 rows of the operand are being written by the converter warps of all CTAs
-          // (a pair's second row block may lie wholly beyond M: nothing to wait for, the loads read zeros)
-          const int rows_left = M - row0;
-          if (rows_left > 0 && seen_rows < static_cast<uint32_t>(min(kBlockM, rows_left))) {
-            ok = wait_rows_ready(conv.ready + m_blk, static_cast<uint32_t>(min(kBlockM, rows_left)), env, kTagRowsReady);
-            if (!ok) break;
-          }
-          fence_proxy_async_all();
-          // request the next tile's counter now: it arrives while this tile's loads are issued
-          const int next_tile = tile + num_clusters;
-          seen_rows = 0;
-          if (next_tile < num_tiles) {
-            const int next_blk = tile_coord(next_tile, num_mp, num_n).m_pair * 2 + static_cast<int>(rank);
-            if (next_blk * kBlockM < M) seen_rows = ld_acquire_gpu(conv.ready + next_blk);
-          }
-        }
         for (int kb = 0; kb < num_kb; ++kb) {
-          ok = role_wait<FUSED>(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage);
+          ok = mbar_wait_warp(empty0 + stage * 8, phase ^ 1u, env, kTagEmpty | stage);
           if (!ok) break;
-          uint8_t* st = smem + stage * Cfg::kStageBytes;
-          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
+          const uint32_t st = smem0 + stage * Cfg::kStageBytes;
+          if (rank == 0) mbar_expect_tx_elect(full_own + stage * 8, 2 * Cfg::kStageBytes);
           const uint32_t bar = full_leader + stage * 8;
           const int x = kb * (KIND == 0 ? 64 : 128);  // tensor-map elements: halves or bytes
-          tma_load_2d_pair(st, &tm_a, bar, x, row0);
-          tma_load_2d_pair(st + kTileA, &tm_b, bar, x, wrow0);
+          tma_load_2d_pair_elect(st, &tm_a, bar, x, row0);
+          tma_load_2d_pair_elect(st + kTileA, &tm_b, bar, x, wrow0);
           if constexpr (Cfg::kScaled) {
             // the scale maps are [row block][32-bit words of the block's atoms]: 256 words = the two
             // atoms of this 256-element K slab
-            tma_load_2d_pair(st + kTileA + kTileB, &tm_sfa, bar, kb * 256, m_blk);
-            tma_load_2d_pair(st + kTileA + kTileB + Cfg::kSfa, &tm_sfb, bar, kb * 256, tc.n_blk * 2);
+            tma_load_2d_pair_elect(st + kTileA + kTileB, &tm_sfa, bar, kb * 256, m_blk);
+            tma_load_2d_pair_elect(st + kTileA + kTileB + Cfg::kSfa, &tm_sfb, bar, kb * 256, tc.n_blk * 2);
           }
           if (++stage == Cfg::kStages) {
             stage = 0;
             phase ^= 1u;
+          }
+        }
+      }
+    } else {
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const uint32_t full_leader = map_to_cta(smem_u32(full_bar), 0);
+        uint32_t seen_rows = 0;  // FUSED: the counter of this tile's row block as read one tile earlier
+        for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+          const TileCoord tc = tile_coord(tile, num_mp, num_n);
+          const int m_blk = tc.m_pair * 2 + static_cast<int>(rank);
+          const int row0 = m_blk * kBlockM;
+          const int wrow0 = tc.n_blk * kBlockN + static_cast<int>(rank) * kHalfN;
+          if constexpr (FUSED) {
+            // this CTA's 128 rows of the operand are being written by the converter warps of all CTAs
+            // (a pair's second row block may lie wholly beyond M: nothing to wait for, the loads read zeros)
+            const int rows_left = M - row0;
+            if (rows_left > 0 && seen_rows < static_cast<uint32_t>(min(kBlockM, rows_left))) {
+              ok = wait_rows_ready(conv.ready + m_blk, static_cast<uint32_t>(min(kBlockM, rows_left)), env, kTagRowsReady);
+              if (!ok) break;
+            }
+            fence_proxy_async_all();
+            // request the next tile's counter now: it arrives while this tile's loads are issued
+            const int next_tile = tile + num_clusters;
+            seen_rows = 0;
+            if (next_tile < num_tiles) {
+              const int next_blk = tile_coord(next_tile, num_mp, num_n).m_pair * 2 + static_cast<int>(rank);
+              if (next_blk * kBlockM < M) seen_rows = ld_acquire_gpu(conv.ready + next_blk);
+            }
+          }
+          for (int kb = 0; kb < num_kb; ++kb) {
+            ok = role_wait<FUSED>(&empty_bar[stage], phase ^ 1u, env, kTagEmpty | stage);
+            if (!ok) break;
+            uint8_t* st = smem + stage * Cfg::kStageBytes;
+            if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
+            const uint32_t bar = full_leader + stage * 8;
+            const int x = kb * (KIND == 0 ? 64 : 128);  // tensor-map elements: halves or bytes
+            tma_load_2d_pair(st, &tm_a, bar, x, row0);
+            tma_load_2d_pair(st + kTileA, &tm_b, bar, x, wrow0);
+            if constexpr (Cfg::kScaled) {
+              // the scale maps are [row block][32-bit words of the block's atoms]: 256 words = the two
+              // atoms of this 256-element K slab
+              tma_load_2d_pair(st + kTileA + kTileB, &tm_sfa, bar, kb * 256, m_blk);
+              tma_load_2d_pair(st + kTileA + kTileB + Cfg::kSfa, &tm_sfb, bar, kb * 256, tc.n_blk * 2);
+            }
+            if (++stage == Cfg::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (leader CTA only) -----------------------------
-    if (lane == 0 && rank == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int local_tile = 0;
-      bool ok = true;
-      const uint32_t empty_own = smem_u32(empty_bar), empty_peer = map_to_cta(empty_own, peer);
-      const uint32_t tfull_own = smem_u32(tmem_full_bar), tfull_peer = map_to_cta(tfull_own, peer);
-      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++local_tile) {
-        const int acc = local_tile % Cfg::kAccStages;
-        const uint32_t acc_phase = static_cast<uint32_t>(local_tile / Cfg::kAccStages) & 1u;
-        ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, env, kTagTmemEmpty | acc);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBlockN);
-        for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | stage);
+    if constexpr (!FUSED) {
+      if (rank == 0) {
+        // converged warp, one elected lane per instruction
+        int stage = 0;
+        uint32_t phase = 0;
+        int local_tile = 0;
+        bool ok = true;
+        const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(full_bar), sf_full0 = smem_u32(sf_full_bar);
+        const uint32_t tempty0 = smem_u32(tmem_empty_bar);
+        const uint32_t empty_own = smem_u32(empty_bar), empty_peer = map_to_cta(empty_own, peer);
+        const uint32_t tfull_own = smem_u32(tmem_full_bar), tfull_peer = map_to_cta(tfull_own, peer);
+        for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++local_tile) {
+          const int acc = local_tile % Cfg::kAccStages;
+          const uint32_t acc_phase = static_cast<uint32_t>(local_tile / Cfg::kAccStages) & 1u;
+          ok = mbar_wait_warp(tempty0 + acc * 8, acc_phase ^ 1u, env, kTagTmemEmpty | acc);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
-          const uint64_t adesc = make_desc_sw128(st);
-          const uint64_t bdesc = make_desc_sw128(st + kTileA);
-          if constexpr (Cfg::kScaled) {
-            ok = mbar_wait(&sf_full_bar[stage], phase, env, kTagSfFull | stage);
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBlockN);
+          for (int kb = 0; kb < num_kb; ++kb) {
+            ok = mbar_wait_warp(full0 + stage * 8, phase, env, kTagFull | stage);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
-            const uint32_t sfb_t = sfa_t + 8;
+            const uint32_t st = smem0 + stage * Cfg::kStageBytes;
+            const uint64_t adesc = make_desc_sw128(st);
+            const uint64_t bdesc = make_desc_sw128(st + kTileA);
+            if constexpr (Cfg::kScaled) {
+              ok = mbar_wait_warp(sf_full0 + stage * 8, phase, env, kTagSfFull | stage);
+              if (!ok) break;
+              tc_fence_after();
+              const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
+              const uint32_t sfb_t = sfa_t + 8;
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              const uint32_t sf_id = (ks & 1) * 2;
-              const uint32_t idesc = make_idesc_mxf4(2 * kBlockM, kBlockN, sf_id, sf_id);
-              umma_mxf4_pair(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u,
-                             sfa_t + (ks >> 1) * 4, sfb_t + (ks >> 1) * (kBlockN / 32));
+              for (int ks = 0; ks < 4; ++ks) {
+                const uint32_t sf_id = (ks & 1) * 2;
+                const uint32_t idesc = make_idesc_mxf4(2 * kBlockM, kBlockN, sf_id, sf_id);
+                umma_mxf4_pair_elect(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u,
+                                     sfa_t + (ks >> 1) * 4, sfb_t + (ks >> 1) * (kBlockN / 32));
+              }
+            } else {
+              constexpr uint32_t idesc = make_idesc(1, kFmtF16, kFmtF16, 2 * kBlockM, kBlockN);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks)
+                umma_f16_pair_elect(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
             }
-          } else {
-            constexpr uint32_t idesc = make_idesc(1, kFmtF16, kFmtF16, 2 * kBlockM, kBlockN);
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) umma_f16_pair(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
+            // both CTAs' copies of the stage may be refilled once these MMAs have read them
+            umma_commit_pair_elect(empty_own + stage * 8);
+            umma_commit_pair_elect(empty_peer + stage * 8);
+            if (++stage == Cfg::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
-          // both CTAs' copies of the stage may be refilled once these MMAs have read them
-          umma_commit_pair(empty_own + stage * 8);
-          umma_commit_pair(empty_peer + stage * 8);
-          if (++stage == Cfg::kStages) {
-            stage = 0;
-            phase ^= 1u;
+          if (ok) {
+            umma_commit_pair_elect(tfull_own + acc * 8);
+            umma_commit_pair_elect(tfull_peer + acc * 8);
           }
         }
-        if (ok) {
-          umma_commit_pair(tfull_own + acc * 8);
-          umma_commit_pair(tfull_peer + acc * 8);
+      }
+    } else {
+      if (lane == 0 && rank == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        int local_tile = 0;
+        bool ok = true;
+        const uint32_t empty_own = smem_u32(empty_bar), empty_peer = map_to_cta(empty_own, peer);
+        const uint32_t tfull_own = smem_u32(tmem_full_bar), tfull_peer = map_to_cta(tfull_own, peer);
+        for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++local_tile) {
+          const int acc = local_tile % Cfg::kAccStages;
+          const uint32_t acc_phase = static_cast<uint32_t>(local_tile / Cfg::kAccStages) & 1u;
+          ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, env, kTagTmemEmpty | acc);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBlockN);
+          for (int kb = 0; kb < num_kb; ++kb) {
+            ok = mbar_wait(&full_bar[stage], phase, env, kTagFull | stage);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
+            const uint64_t adesc = make_desc_sw128(st);
+            const uint64_t bdesc = make_desc_sw128(st + kTileA);
+            if constexpr (Cfg::kScaled) {
+              ok = mbar_wait(&sf_full_bar[stage], phase, env, kTagSfFull | stage);
+              if (!ok) break;
+              tc_fence_after();
+              const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
+              const uint32_t sfb_t = sfa_t + 8;
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks) {
+                const uint32_t sf_id = (ks & 1) * 2;
+                const uint32_t idesc = make_idesc_mxf4(2 * kBlockM, kBlockN, sf_id, sf_id);
+                umma_mxf4_pair(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u,
+                               sfa_t + (ks >> 1) * 4, sfb_t + (ks >> 1) * (kBlockN / 32));
+              }
+            } else {
+              constexpr uint32_t idesc = make_idesc(1, kFmtF16, kFmtF16, 2 * kBlockM, kBlockN);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks) umma_f16_pair(d_tmem, adesc + ks * 2, bdesc + ks * 2, idesc, (kb | ks) != 0 ? 1u : 0u);
+            }
+            // both CTAs' copies of the stage may be refilled once these MMAs have read them
+            umma_commit_pair(empty_own + stage * 8);
+            umma_commit_pair(empty_peer + stage * 8);
+            if (++stage == Cfg::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          if (ok) {
+            umma_commit_pair(tfull_own + acc * 8);
+            umma_commit_pair(tfull_peer + acc * 8);
+          }
         }
       }
     }
   } else if (warp == kSfWarp) {
     // ------------------------------- scale-factor copier (O2, leader CTA only) ----------------
-    if constexpr (Cfg::kScaled) {
+    if constexpr (Cfg::kScaled && !FUSED) {
+      if (rank == 0) {
+        // converged warp, one elected lane per instruction
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(full_bar), sf_full_own = smem_u32(sf_full_bar);
+        for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            // both CTAs' scale factors of the stage have landed; the stage's tensor-memory scale
+            // columns were last read by MMAs that completed before the stage was handed back
+            ok = mbar_wait_warp(full0 + stage * 8, phase, env, kTagFull | 0x80 | stage);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t st = smem0 + stage * Cfg::kStageBytes;
+            const uint32_t sfa_s = st + kTileA + kTileB;
+            const uint32_t sfb_s = sfa_s + Cfg::kSfa;
+            const uint32_t sfa_t = tmem_base + Cfg::kSfColBase + stage * Cfg::kSfColsPerStage;
+            const uint32_t sfb_t = sfa_t + 8;
+#pragma unroll
+            for (int ka = 0; ka < 2; ++ka) {
+              tmem_cp_pair_32x128b_warpx4_elect(sfa_t + ka * 4, make_desc_sf(sfa_s + ka * 512));
+#pragma unroll
+              for (int rb = 0; rb < kBlockN / 128; ++rb) {
+                tmem_cp_pair_32x128b_warpx4_elect(sfb_t + ka * (kBlockN / 32) + rb * 4,
+                                                  make_desc_sf(sfb_s + rb * 1024 + ka * 512));
+              }
+            }
+            umma_commit_pair_elect(sf_full_own + stage * 8);
+            if (++stage == Cfg::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    }
+    if constexpr (Cfg::kScaled && FUSED) {
       if (lane == 0 && rank == 0) {
         int stage = 0;
         uint32_t phase = 0;
