@@ -151,12 +151,13 @@ int encode_word_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
 // O0/O2 run on CTA pairs (cta_group::2, 256 x 256 tiles, bit-identical to the single-CTA kernels) where
 // that was measured to pay: the shape must hold a full pair tile and pair up its 128-row blocks with
 // little waste (an even number of them, or so many that the padded half block is under 3 %), and be
-// large -- at least two waves of pair tiles and K >= 2048 for O0 (3 - 7 % faster from there; from one wave on when
-// K >= 8192, where a long K loop amortises the pair's hand-overs: 125 vs 139 us at 2048 x 4096 x 11008), at least
-// seven waves and K >= 4096 for O2 (3 - 7 %; below that its single accumulator stage and the longer
-// hand-overs between two CTAs cost more than the halved W traffic saves: -2 % at 2048 x 11008 x 4096,
-// -17 % at K = 512).  ADG_TWO_CTA in the environment (read at every plan): 0 = never, 1 = whenever the
-// shape holds a full pair tile.
+// large -- for O0 at least two waves of pair tiles and K >= 2048, or one wave and K >= 4096 (5 - 12 % faster from
+// there: 47.9 vs 50.7 us at 2048 x 4096 x 4096, 119 vs 137 us at 2048 x 11008 x 4096; below one wave the single-CTA
+// kernel wins, 27.2 vs 28.6 us at 1024 x 4096 x 4096); for O2 at least seven waves and K >= 4096, or one wave and
+// K >= 8192, where a long K loop amortises the pair's hand-overs (39.6 vs 41.4 us at 2048 x 4096 x 11008); below that
+// its single accumulator stage and the longer hand-overs between two CTAs cost what the halved W traffic saves
+// (23.0 vs 22.7 us at 2048 x 4096 x 4096, equal at 4096^3, -17 % at K = 512).  ADG_TWO_CTA in the environment (read
+// at every plan): 0 = never, 1 = whenever the shape holds a full pair tile.
 bool pair_enabled(int variant, int M, int N, int K, int sm_count) {
   if (M < pair_tile_m() || N < pair_tile_n()) return false;
   const char* e = getenv("ADG_TWO_CTA");
@@ -166,8 +167,8 @@ bool pair_enabled(int variant, int M, int N, int K, int sm_count) {
   if (row_blocks % 2 != 0 && row_blocks < 33) return false;
   const long tiles = static_cast<long>((M + pair_tile_m() - 1) / pair_tile_m()) * ((N + pair_tile_n() - 1) / pair_tile_n());
   const long clusters = sm_count / 2;
-  if (variant == 0) return (tiles >= 2 * clusters && K >= 2048) || (tiles >= clusters && K >= 8192);
-  return tiles >= 7 * clusters && K >= 4096;
+  if (variant == 0) return (tiles >= 2 * clusters && K >= 2048) || (tiles >= clusters && K >= 4096);
+  return (tiles >= 7 * clusters && K >= 4096) || (tiles >= clusters && K >= 8192);
 }
 
 int finish_pair_plan(GemmPlan* plan, int sm_count, uint32_t* status) {
