@@ -5,17 +5,21 @@
 // Y^T[n, m] = W[n, :] . A[m, :]^T with the 128 MMA rows taken from W and the MMA N extent equal to M
 // rounded up to 16.  A 128-row block of W is handled by a cluster of S CTAs (S = 1, 2 or 4, chosen so
 // that the grid covers the GPU once): each walks 1/S of K, accumulates in its tensor memory, and the
-// partial sums meet in the first CTA's shared memory (distributed shared memory: plain remote stores),
-// which adds them in rank order -- deterministic -- and writes the block of Y.  Up to 16 activation rows
-// the partials land in the part of the stage buffers that no copy ever writes (the TMA box of A is 16
-// rows of the 64-row tile) and are announced by remote mbarrier arrivals; above that they land in the
-// stage buffers proper, between two cluster-wide meetings (after the first one every CTA's MMAs are done).  For O2 the accumulation order is free, so the split
-// changes results only within the rounding of the FP32 sums.  (A launch of this kernel costs about
-// 6.5 us before the first K slab is consumed and 0.3 us per slab after that; an earlier split over
-// independent CTAs with a last-arriver reduction through global memory cost more than it saved.)
+// partial sums meet in the first CTA's shared memory (distributed shared memory: st.async, whose bytes are
+// counted on the first CTA's barrier as they land), which adds them in rank order -- deterministic -- and
+// writes the block of Y.  Up to 16 activation rows the partials land in the part of the stage buffers that
+// no copy ever writes (the TMA box of A is 16 rows of the 64-row tile); above that they land in the stage
+// buffers proper, once the first CTA has told the senders that its MMAs are done.  For O2 the accumulation
+// order is free, so the split changes results only within the rounding of the FP32 sums.  (Of a CTA's
+// 7600 cycles at M = 1, N = K = 4096 about 900 are set-up, 1400 the first DRAM round trip, 2500 the four
+// K slabs and the rest the hand-over of the partial sums and the store; two cluster-wide meetings instead
+// of the st.async hand-over cost 1600 cycles more, an earlier split over independent CTAs with a
+// last-arriver reduction through global memory more than it saved.)
 //
 // Scale factors: W's tiled scales are the MMA's A-side scales (128-row atoms as stored), A's tiled
 // scales are the B-side scales (row block 0 of A's tiled buffer).
+#include <type_traits>
+
 #include "common.cuh"
 #include "launch.h"
 
@@ -51,14 +55,13 @@ __device__ __forceinline__ uint32_t cluster_size() {
   asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
   return r;
 }
-__device__ __forceinline__ void cluster_barrier() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void st_cluster_v4(uint32_t local_addr, uint32_t rank, const uint32_t (&v)[4]) {
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
-               : "memory");
+  return remote;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 __global__ void __launch_bounds__(kThreads, 2)
@@ -73,7 +76,8 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   uint64_t* acc_bar = bars + 2 * kStages;
   uint64_t* sf_full_bar = acc_bar + 1;
   uint64_t* reduce_bar = sf_full_bar + kStages;  // first CTA of a cluster: the other ranks' partial sums have landed
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(reduce_bar + 1);
+  uint64_t* go_bar = reduce_bar + 1;      // ranks 1..: the first CTA's stage buffers may be written
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(go_bar + 1);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -95,7 +99,8 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       mbar_init(&sf_full_bar[s], 1);
     }
     mbar_init(acc_bar, 1);
-    mbar_init(reduce_bar, static_cast<uint32_t>((split - 1) * 128));
+    mbar_init(reduce_bar, 1);  // the first CTA's own expect_tx arrival; the senders' bytes complete the phase
+    mbar_init(go_bar, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -218,68 +223,53 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       }
     }
   }
-  // Up to 16 activation rows: the TMA box of A covers 16 rows, so rows 16..63 of every stage's A tile (6 KB per
-  // stage, 24 KB) are never written by a copy.  The other ranks store their partial sums there and arrive on the
-  // first CTA's barrier: no cluster-wide meeting after the K loop (two of them cost 2000 cycles of a 9000-cycle CTA).
-  // A unit = 128 rows x 4 floats of one (rank, group of four activation rows) = 2 KB; three units per stage.
+  // The partial sums of ranks 1.. travel to the first CTA with st.async, whose bytes are counted on its barrier as
+  // they land: no cluster-wide meeting after the K loop and no release fence in the senders (two meetings cost 2000
+  // cycles of a 9000-cycle CTA, a release-arrive per sender 1200).  A unit = 128 rows x 4 floats of one (rank, group
+  // of four activation rows) = 2 KB.
+  //  * Up to 16 activation rows the TMA box of A covers 16 rows, so rows 16..63 of every stage's A tile (6 KB per
+  //    stage) are never written by a copy: stage g receives the units of row group g, one per sender, at any time.
+  //  * Above that the units land in the stage buffers proper ([sender][group][row][4 floats]), which the first CTA's
+  //    MMAs must have finished reading: it tells every sender so (one remote arrival each) once its accumulator is
+  //    complete, and the senders wait for that.
   const bool direct = a_box <= 16;
-  if (split > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-  if (split > 1 && direct) {
+  if (split > 1) {
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // the peers' barriers exist (see the prologue)
     const int row = q * 32 + lane;
     const uint32_t m_groups = (static_cast<uint32_t>(M) + 3u) / 4u;
-    auto unit_offset = [&](int rank_m1, int g) -> uint32_t {
-      const int u = rank_m1 * 4 + g;
-      return static_cast<uint32_t>((u / 3) * kStageBytes + kTileW + 16 * 128 + (u % 3) * 2048);
+    auto unit_offset = [&](int sender, int g) -> uint32_t {
+      return direct ? static_cast<uint32_t>(g * kStageBytes + kTileW + 16 * 128 + (sender - 1) * 2048)
+                    : static_cast<uint32_t>((sender - 1) * (kRows * kMaxM * 4) + g * (kRows * 16));
     };
-    if (epi && rank != 0) {
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        if (static_cast<uint32_t>(g) < m_groups) {
-          const uint32_t v[4] = {r[0][g * 4], r[0][g * 4 + 1], r[0][g * 4 + 2], r[0][g * 4 + 3]};
-          st_cluster_v4(smem_u32(smem) + unit_offset(rank - 1, g) + static_cast<uint32_t>(row) * 16u, 0u, v);
-        }
+    if (rank == 0 && threadIdx.x == 64) {  // one thread of the first epilogue warp
+      mbar_arrive_expect_tx(reduce_bar, static_cast<uint32_t>(split - 1) * 128u * m_groups * 16u);
+      if (!direct && have) {
+        for (int p = 1; p < split; ++p) mbar_arrive_cluster(map_to_rank(smem_u32(go_bar), static_cast<uint32_t>(p)));
       }
-      // release at cluster scope: the stores above are visible to whoever sees this arrival
-      uint32_t remote_bar;
-      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(smem_u32(reduce_bar)), "r"(0u));
-      asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
     }
-    if (epi && rank == 0 && have) {
-      // bounded wait, acquire at cluster scope
-      const uint32_t bar = smem_u32(reduce_bar);
-      const unsigned long long t0 = global_timer_ns();
-      uint32_t done = 0, spins = 0;
-      while (true) {
-        asm volatile(
-            "{\n"
-            ".reg .pred p;\n"
-            "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
-            "selp.u32 %0, 1, 0, p;\n"
-            "}\n"
-            : "=r"(done)
-            : "r"(bar), "r"(0u)
-            : "memory");
-        if (done) break;
-        if ((++spins & 0x3FFu) == 0 && (*abort_flag || global_timer_ns() - t0 > kWaitTimeoutNs)) {
-          if (!*abort_flag) {
-            *abort_flag = 1;
-            if (atomicCAS(status, 0u, static_cast<uint32_t>(kStatusWaitTimeout)) == 0u) {
-              status[1] = kTagAcc | 0x80u;
-              status[2] = blockIdx.x;
-              status[3] = 0;
-            }
-          }
-          have = false;
-          break;
+    auto send = [&](auto gmax) {
+      const uint32_t remote_bar = map_to_rank(smem_u32(reduce_bar), 0u);
+      const uint32_t remote_base = map_to_rank(smem_u32(smem), 0u);
+#pragma unroll
+      for (int g = 0; g < decltype(gmax)::value; ++g) {
+        if (static_cast<uint32_t>(g) < m_groups) {
+          asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                       ::"r"(remote_base + unit_offset(rank, g) + static_cast<uint32_t>(row) * 16u), "r"(r[g >> 3][(g & 7) * 4]),
+                       "r"(r[g >> 3][(g & 7) * 4 + 1]), "r"(r[g >> 3][(g & 7) * 4 + 2]), "r"(r[g >> 3][(g & 7) * 4 + 3]),
+                       "r"(remote_bar)
+                       : "memory");
         }
       }
-      if (have) {
-        for (int other = 1; other < split; ++other) {
+    };
+    auto add = [&](auto gmax) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+      for (int other = 1; other < kMaxSplit; ++other) {
+        if (other < split) {
+#pragma unroll
+          for (int g = 0; g < decltype(gmax)::value; ++g) {
             if (static_cast<uint32_t>(g) < m_groups) {
-              const float4 p = *reinterpret_cast<const float4*>(smem + unit_offset(other - 1, g) + row * 16);
-              uint32_t* dst = &r[0][g * 4];
+              const float4 p = *reinterpret_cast<const float4*>(smem + unit_offset(other, g) + row * 16);
+              uint32_t* dst = &r[g >> 3][(g & 7) * 4];
               dst[0] = __float_as_uint(__uint_as_float(dst[0]) + p.x);
               dst[1] = __float_as_uint(__uint_as_float(dst[1]) + p.y);
               dst[2] = __float_as_uint(__uint_as_float(dst[2]) + p.z);
@@ -288,42 +278,20 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
           }
         }
       }
-    }
-  } else if (split > 1) {
-    // 1st meeting: every CTA's MMAs are done (its epilogue warps have seen the accumulator complete), so the
-    // first CTA's stage buffers are free to receive the partials.  (__syncthreads first: the one-thread roles'
-    // warps arrive reconverged.)
-    __syncthreads();
-    cluster_barrier();
-    // layout in the first CTA: [rank - 1][m / 4][row 0..127][4 floats]
-    const int row = q * 32 + lane;
-    const uint32_t m_groups = (static_cast<uint32_t>(M) + 3u) / 4u;
+    };
     if (epi && rank != 0) {
-      const uint32_t base = smem_u32(smem) + static_cast<uint32_t>(rank - 1) * (kRows * kMaxM * 4);
-#pragma unroll
-      for (int g = 0; g < kMaxM / 4; ++g) {
-        if (static_cast<uint32_t>(g) < m_groups) {
-          const uint32_t v[4] = {r[g >> 3][(g & 7) * 4], r[g >> 3][(g & 7) * 4 + 1], r[g >> 3][(g & 7) * 4 + 2], r[g >> 3][(g & 7) * 4 + 3]};
-          st_cluster_v4(base + (static_cast<uint32_t>(g) * kRows + row) * 16u, 0u, v);
-        }
+      if (direct) {
+        send(std::integral_constant<int, 4>{});
+      } else if (mbar_wait(go_bar, 0, env, kTagAcc | 0x40u)) {
+        send(std::integral_constant<int, kMaxM / 4>{});
       }
     }
-    // 2nd meeting: the partials have landed
-    cluster_barrier();
     if (epi && rank == 0 && have) {
-      for (int other = 1; other < split; ++other) {
-        const float4* part = reinterpret_cast<const float4*>(smem + static_cast<size_t>(other - 1) * (kRows * kMaxM * 4));
-#pragma unroll
-        for (int g = 0; g < kMaxM / 4; ++g) {
-          if (static_cast<uint32_t>(g) < m_groups) {
-            const float4 p = part[g * kRows + row];
-            uint32_t* dst = &r[g >> 3][(g & 7) * 4];
-            dst[0] = __float_as_uint(__uint_as_float(dst[0]) + p.x);
-            dst[1] = __float_as_uint(__uint_as_float(dst[1]) + p.y);
-            dst[2] = __float_as_uint(__uint_as_float(dst[2]) + p.z);
-            dst[3] = __float_as_uint(__uint_as_float(dst[3]) + p.w);
-          }
-        }
+      // bounded wait for the senders' bytes
+      if (!mbar_wait(reduce_bar, 0, env, kTagAcc | 0x80u)) have = false;
+      if (have) {
+        if (direct) add(std::integral_constant<int, 4>{});
+        else add(std::integral_constant<int, kMaxM / 4>{});
       }
     }
   }
