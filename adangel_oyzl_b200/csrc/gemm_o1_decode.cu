@@ -113,11 +113,14 @@ gemm_o1_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   const int groups = K / 32;
   const int num_kb = (groups + 3) / 4;
   const int num_turns = (num_kb + T - 1) / T;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kSlots; ++s) mbar_init(&full_bar[s], 1);
-    for (int w = 0; w < RING; ++w) mbar_init(&token_bar[w], 1);
-    *abort_flag = 0;
+  // one barrier per thread (full barriers and token barriers are contiguous): a single thread initialising all
+  // of them one after the other costs several hundred cycles of a kernel that lasts a few thousand
+  if (threadIdx.x < kSlots + RING) {
+    mbar_init(&full_bar[threadIdx.x], 1);
     fence_mbar_init();
+  }
+  if (threadIdx.x == 32) {
+    *abort_flag = 0;
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_a);
   }

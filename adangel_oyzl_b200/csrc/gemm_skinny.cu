@@ -92,18 +92,15 @@ gemm_o2_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   const int katoms = static_cast<int>(((K / 32 + 7) / 8) * 2);
   const uint32_t m_pad = static_cast<uint32_t>((M + 15) / 16 * 16);
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full_bar[s], 2);  // one arrival per producer warp
-      mbar_init(&empty_bar[s], 1);
-      mbar_init(&sf_full_bar[s], 1);
-    }
-    mbar_init(acc_bar, 1);
-    mbar_init(reduce_bar, 1);  // the first CTA's own expect_tx arrival; the senders' bytes complete the phase
-    mbar_init(go_bar, 1);
-    *abort_flag = 0;
+  // one barrier per thread of the last warp (the barriers are contiguous: full, empty, accumulator, scale copies,
+  // reduce, go): a single thread initialising all fifteen one after the other costs several hundred cycles.
+  // Arrival counts: full = one per producer warp; reduce = the first CTA's own expect_tx arrival (the senders'
+  // bytes complete the phase); all others one.
+  if (warp == 7 && lane < 3 * kStages + 3) {
+    mbar_init(&bars[lane], lane < kStages ? 2u : 1u);
     fence_mbar_init();
   }
+  if (threadIdx.x == 0) *abort_flag = 0;
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_a);
